@@ -1,0 +1,151 @@
+/*
+ * ko_b200.h -- C ABI of the B200 (sm_100a) operator library: row softmax, Welford LayerNorm
+ * forward, FP32 FFMA SGEMM and the FP16/BF16-in FP32-accumulate tcgen05 GEMM, plus the
+ * host/device Tensor buffer, seeded fills and host-side comparison metrics.
+ *
+ * The reference project (donglinz/kernel_optimization) has no FFI: its operator API is C++
+ * templates with compile-time shapes launched with <<<>>> from three drivers.  Each entry point
+ * below names the reference interface it stands in for (file:line inside that project).
+ *
+ * Conventions
+ *   - every function returns a ko_status_t (0 = success); nothing prints, exits or aborts;
+ *     ko_last_error_string() gives the calling thread's most recent failure in words;
+ *   - operator entry points take DEVICE pointers valid on the CURRENT device, enqueue on
+ *     `stream` (a cudaStream_t passed as void*, NULL = default stream) and return without
+ *     synchronising; they allocate nothing;
+ *   - matrices are dense (leading dimension = logical width);
+ *   - there is no CPU fallback: without a usable CUDA device the operator calls fail.
+ */
+#ifndef KO_B200_H
+#define KO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ko_status {
+    KO_OK = 0,
+    KO_ERR_INVALID_ARG = 1, /* NULL pointer, negative size, unknown flag */
+    KO_ERR_ALIGN = 2,       /* pointer or row pitch not aligned as the kernel requires */
+    KO_ERR_SHAPE = 3,       /* shape outside what the kernel supports */
+    KO_ERR_CUDA = 4,        /* a CUDA runtime/driver call failed (see ko_last_error_string) */
+    KO_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up (status word set by the kernel) */
+    KO_ERR_NO_DEVICE = 6    /* no sm_100 device is current */
+} ko_status_t;
+
+const char *ko_status_string(int status);
+const char *ko_last_error_string(void);
+/* major*10000 + minor*100 + patch */
+int ko_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Tensor: paired host (pinned) + device byte buffer.
+ * Stands in for class Tensor, common/tensor.h:11-40 and common/tensor.cu:8-42.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct ko_tensor ko_tensor_t;
+
+/* Tensor::Tensor(size_t) tensor.cu:8-11; device < 0 means the current device */
+int ko_tensor_create(size_t size_in_bytes, int device, ko_tensor_t **out);
+/* Tensor::~Tensor tensor.cu:23-26 */
+int ko_tensor_destroy(ko_tensor_t *t);
+/* Tensor::host_ref<T>() tensor.h:20-23 */
+void *ko_tensor_host_ptr(ko_tensor_t *t);
+/* Tensor::device_ref<T>() tensor.h:25-28 */
+void *ko_tensor_device_ptr(ko_tensor_t *t);
+size_t ko_tensor_size_in_bytes(const ko_tensor_t *t);
+int ko_tensor_device(const ko_tensor_t *t);
+/* Tensor::host_to_device / host_to_device_async tensor.cu:28-34 */
+int ko_tensor_host_to_device(ko_tensor_t *t);
+int ko_tensor_host_to_device_async(ko_tensor_t *t, void *stream);
+/* Tensor::device_to_host / device_to_host_async tensor.cu:36-42 */
+int ko_tensor_device_to_host(ko_tensor_t *t);
+int ko_tensor_device_to_host_async(ko_tensor_t *t, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Seeded host fills.  Stand in for the inline fill loops of the reference drivers
+ * (nn_operators/softmax/main.cu:31-36, nn_operators/gemm/main.cu:46-66), which draw from a
+ * default-seeded std::default_random_engine and are not reproducible by specification.
+ * Element i depends only on (seed, tensor_id, elem_offset + i): Philox4x32-10 keyed by
+ * (seed, tensor_id), counter = element index / 4.  Values are generated in float64 and rounded
+ * once to the storage type.  dtype: 0 = f32, 1 = f16, 2 = bf16 (16-bit types as raw uint16).
+ * ---------------------------------------------------------------------------------------- */
+enum { KO_DTYPE_F32 = 0, KO_DTYPE_F16 = 1, KO_DTYPE_BF16 = 2 };
+
+int ko_fill_uniform(void *host_dst, int dtype, int64_t n, uint32_t seed, uint32_t tensor_id,
+                    int64_t elem_offset, float lo, float hi);
+int ko_fill_normal(void *host_dst, int dtype, int64_t n, uint32_t seed, uint32_t tensor_id,
+                   int64_t elem_offset, float mean, float stddev);
+/* rows are numbered row_offset + r; within every `block` consecutive rows, every column
+ * c > (row % block) is overwritten with `value` (FP32 only) */
+int ko_fill_causal_mask_f32(float *host_dst, int64_t rows, int32_t cols, int64_t row_offset,
+                            int32_t block, float value);
+
+/* ------------------------------------------------------------------------------------------
+ * Host-side comparison ("check") of a result against expected values supplied by the caller.
+ * Stands in for the element loop of nn_operators/gemm/main.cu:157-176 (|got - ref| > 1e-3).
+ * These compare buffers; they never compute the operator on the CPU.
+ * ---------------------------------------------------------------------------------------- */
+int ko_check_max_abs_f32(const float *got, const float *want, int64_t n, double *out);
+/* max |got - want| / max(|want|, floor) */
+int ko_check_max_rel_f32(const float *got, const float *want, int64_t n, double floor, double *out);
+/* ||got - want||_F / ||want||_F */
+int ko_check_rel_frobenius_f32(const float *got, const float *want, int64_t n, double *out);
+/* max over rows of |sum(row) - 1| */
+int ko_check_max_rowsum_err_f32(const float *got, int64_t rows, int32_t cols, double *out);
+
+/* ------------------------------------------------------------------------------------------
+ * Row softmax over the last dimension, FP32, row-major [rows, cols].
+ * Stands in for softmax<SoftMaxWarpImpl|SoftMaxBlockImpl|SoftMaxBlockNoCacheImpl<float, vec,
+ * rows, cols>><<<grid, block, smem, stream>>>(in, out): nn_operators/softmax/softmax.h:11-60,
+ * :62-113, :116-166, :168-174 (launched at nn_operators/softmax/main.cu:58-60).
+ * Computes exp(x - rowmax) / sum.  `out` may equal `in`.  Any cols >= 1; the 128-bit path needs
+ * cols % 4 == 0 and 16-byte aligned pointers, other inputs take a scalar path.
+ * ---------------------------------------------------------------------------------------- */
+int ko_softmax_f32(const float *in, float *out, int64_t rows, int32_t cols, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * LayerNorm forward over the last dimension, row-major [rows, cols].
+ * Stands in for layer_normalization<LayerNormWarpImpl|LayerNormBlockImpl|
+ * LayerNormBlockNoCacheImpl<E, vec, rows, cols, affine>><<<...>>>(in, out, eps, gamma, beta):
+ * nn_operators/layernorm/layernorm.h:145-201, :204-252, :254-300, :302-312.
+ * y = (x - mean) * rsqrt(var + eps) [* gamma] [+ beta]; statistics in FP32 by Welford/Chan
+ * merging; var = M2 / (cols - ddof), ddof in {0, 1}.  gamma and beta may each be NULL and have
+ * the I/O element type.  `out` may equal `in`.
+ * ---------------------------------------------------------------------------------------- */
+int ko_layernorm_f32(const float *in, float *out, int64_t rows, int32_t cols, float eps,
+                     const float *gamma, const float *beta, int ddof, void *stream);
+/* BF16 in/out (raw uint16 storage), FP32 statistics */
+int ko_layernorm_bf16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps,
+                      const uint16_t *gamma, const uint16_t *beta, int ddof, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * SGEMM: D[M,N] = A[M,K] * B[K,N] (+ C[M,N] when C != NULL), all row-major FP32, FP32 FFMA.
+ * Stands in for gemm<GemmKernelSimt<float,float,float,GemmShape<64,64,8>,GemmShape<32,32,8>,
+ * 4,4,4>><<<grid, 128, smem, stream>>>(GemmCoord, A, B, C, D): nn_operators/gemm/gemm.h:11-21,
+ * nn_operators/gemm/simt_gemm.h:46-375 (launched at nn_operators/gemm/main.cu:111-117).
+ * Any M, N, K >= 1 (edges are predicated).  D must not alias A or B; D may equal C.
+ * ---------------------------------------------------------------------------------------- */
+int ko_sgemm_f32(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C,
+                 float *D, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Tensor-core GEMM: D[M,N] (FP32, row-major) = A[M,K] (row-major) * B[K,N] (column-major, i.e.
+ * element (k,n) at B[n*K + k]) (+ C[M,N] FP32 when C != NULL); FP16 or BF16 inputs as raw
+ * uint16, FP32 accumulate in tensor memory (tcgen05.mma), TMA-fed.
+ * Stands in for gemm<GemmKernelTensorCore<half,half,half,GemmShape<128,128,32>,
+ * GemmShape<64,64,32>,GemmShape<16,8,8>,8,8,8>>: nn_operators/gemm/tensor_core_gemm.h:101-399
+ * (disabled call at nn_operators/gemm/main.cu:344).
+ * Requires K % 8 == 0, N % 4 == 0 and 16-byte aligned pointers; M, N, K tails are handled.
+ * ---------------------------------------------------------------------------------------- */
+int ko_gemm_f16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
+                    const float *C, float *D, void *stream);
+int ko_gemm_bf16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
+                     const float *C, float *D, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KO_B200_H */

@@ -1,0 +1,235 @@
+// Shared device/host building blocks of the sm_100a operator set.
+//
+// Keeps the names the reference project exposes in common/common.h (checkCudaErrors :25,
+// WarpReduce :37-46, BlockReduce :48-65, AlignedArray :67-130, to_scalar :138-149,
+// limits::numeric_limits :151-178, shape::{GemmCoord,MatrixShape,GemmShape} :180-231) so that
+// code written against that header keeps compiling, and adds the `ko` namespace with what the
+// Blackwell kernels need: butterfly all-reduces, streaming 128-bit accesses, Chan/Welford
+// merging and a cluster-wide exchange.
+//
+// Deliberate differences from the reference:
+//   * BlockReduce is correct for every block size that is a multiple of 32 (the reference
+//     folds stale lanes in unless blockDim.x == 1024, common.h:59-63);
+//   * WarpReduce leaves the result in every lane, not only lane 0.
+#pragma once
+
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <string>
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+// ---------------------------------------------------------------------------------------------
+// error handling for the drivers (the C ABI returns status codes instead)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+void check(T result, char const *const func, const char *const file, int const line) {
+    if (result != 0) {
+        std::fprintf(stderr, "CUDA error at %s:%d code=%d(%s) \"%s\"\n", file, line,
+                     static_cast<int>(result), cudaGetErrorName(static_cast<cudaError_t>(result)), func);
+        std::exit(EXIT_FAILURE);
+    }
+}
+#define checkCudaErrors(val) check((val), #val, __FILE__, __LINE__)
+
+__host__ __device__ constexpr int divide_up(int a, int b) { return (a + b - 1) / b; }
+__host__ __device__ constexpr int const_max(int a, int b) { return a > b ? a : b; }
+
+// ---------------------------------------------------------------------------------------------
+// AlignedArray: N elements of T aligned to the whole vector, so one object moves with a single
+// 32/64/128-bit access.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int N>
+struct alignas(sizeof(T) * N) AlignedArray {
+    using Element = T;
+    static constexpr int kElements = N;
+
+    AlignedArray() = default;
+    __host__ __device__ AlignedArray(const T &fill) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) buffer[i] = fill;
+    }
+    __host__ __device__ T &operator[](int i) { return buffer[i]; }
+    __host__ __device__ const T &operator[](int i) const { return buffer[i]; }
+    __host__ __device__ T &at(int i) { return buffer[i]; }
+    __host__ __device__ const T &at(int i) const { return buffer[i]; }
+    __host__ __device__ void clear() {
+#pragma unroll
+        for (int i = 0; i < N; ++i) buffer[i] = T(0);
+    }
+
+    T buffer[N];
+};
+
+template <typename ReductionOp, typename T, int N>
+__host__ __device__ __forceinline__ T to_scalar(const AlignedArray<T, N> &v) {
+    T acc = v[0];
+#pragma unroll
+    for (int i = 1; i < N; ++i) acc = ReductionOp()(acc, v[i]);
+    return acc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// warp / block reductions
+// ---------------------------------------------------------------------------------------------
+// Butterfly over the 32 lanes: every lane ends with the reduced value (a superset of the
+// reference's contract, which only defines lane 0).
+template <template <typename> typename ReductionOp, typename T>
+__device__ __forceinline__ T WarpReduce(T val) {
+#pragma unroll
+    for (int mask = 16; mask > 0; mask >>= 1) val = ReductionOp<T>()(val, __shfl_xor_sync(0xffffffffu, val, mask));
+    return val;
+}
+
+// Reduce over the whole thread block; the result is valid in warp 0 (all of its lanes).
+// s_reduce_cache needs one T per warp.  Works for any blockDim.x that is a multiple of 32.
+template <template <typename> typename ReductionOp, typename T>
+__device__ __forceinline__ T BlockReduce(T val, T *s_reduce_cache) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    val = WarpReduce<ReductionOp, T>(val);
+    __syncthreads();  // the cache may still be read from a previous reduction
+    if (lane == 0) s_reduce_cache[warp] = val;
+    __syncthreads();
+    if (warp == 0) {
+        // lanes beyond the warp count re-read slot 0: harmless for the idempotent ops, and for
+        // sums they are masked out by the clamped tree below
+        T mine = s_reduce_cache[lane < nwarps ? lane : 0];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            T other = __shfl_down_sync(0xffffffffu, mine, off);
+            if (lane + off < nwarps) mine = ReductionOp<T>()(mine, other);
+        }
+        val = __shfl_sync(0xffffffffu, mine, 0);
+    }
+    return val;
+}
+
+// ---------------------------------------------------------------------------------------------
+// numeric limits used as reduction identities
+// ---------------------------------------------------------------------------------------------
+namespace limits {
+template <typename T>
+struct numeric_limits;
+template <>
+struct numeric_limits<float> {
+    __host__ __device__ static constexpr float max() { return 3.402823466e+38f; }
+};
+template <>
+struct numeric_limits<int32_t> {
+    __host__ __device__ static constexpr int32_t max() { return 2147483647; }
+};
+template <>
+struct numeric_limits<half> {
+    __host__ __device__ static half max() { return __ushort_as_half((unsigned short)0x7bffu); }  // 65504
+};
+template <>
+struct numeric_limits<__nv_bfloat16> {
+    __host__ __device__ static __nv_bfloat16 max() { return __ushort_as_bfloat16((unsigned short)0x7f7fu); }
+};
+}  // namespace limits
+
+// ---------------------------------------------------------------------------------------------
+// GEMM shapes
+// ---------------------------------------------------------------------------------------------
+namespace shape {
+class GemmCoord {
+public:
+    __host__ __device__ GemmCoord(size_t m, size_t n, size_t k) : m_(m), n_(n), k_(k) {}
+    __host__ __device__ size_t m() const { return m_; }
+    __host__ __device__ size_t n() const { return n_; }
+    __host__ __device__ size_t k() const { return k_; }
+    __host__ __device__ size_t mk() const { return m_ * k_; }
+    __host__ __device__ size_t kn() const { return k_ * n_; }
+    __host__ __device__ size_t mn() const { return m_ * n_; }
+    __host__ __device__ size_t mnk() const { return m_ * n_ * k_; }
+    std::string to_string() const {
+        return "{" + std::to_string(m_) + "," + std::to_string(n_) + "," + std::to_string(k_) + "}";
+    }
+
+private:
+    size_t m_, n_, k_;
+};
+
+template <int M_, int N_>
+struct MatrixShape {
+    static constexpr int kM = M_, kN = N_;
+};
+
+template <int M_, int N_, int K_>
+struct GemmShape {
+    static constexpr int kM = M_, kN = N_, kK = K_;
+    static constexpr int kMN = M_ * N_, kMK = M_ * K_, kKN = K_ * N_, kMNK = M_ * N_ * K_;
+    static std::string to_string() {
+        return "{" + std::to_string(kM) + "," + std::to_string(kN) + "," + std::to_string(kK) + "}";
+    }
+};
+}  // namespace shape
+
+// ---------------------------------------------------------------------------------------------
+// ko:: device helpers for the Blackwell kernels
+// ---------------------------------------------------------------------------------------------
+namespace ko {
+
+constexpr unsigned kFullMask = 0xffffffffu;
+
+__device__ __forceinline__ float warp_allreduce_max(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, m));
+    return v;
+}
+__device__ __forceinline__ float warp_allreduce_sum(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(kFullMask, v, m);
+    return v;
+}
+
+// Streaming (evict-first) 128-bit global accesses: row ops touch every byte exactly once.
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+__device__ __forceinline__ uint4 ld_stream(const uint4 *p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
+__device__ __forceinline__ void st_stream(uint4 *p, uint4 v) { __stcs(p, v); }
+
+// Running (count, mean, M2) triple; M2 is the sum of squared deviations from the mean.
+struct Welford {
+    float n, mean, m2;
+};
+
+// Chan et al. pairwise combination of two partial statistics.  M2 stays a sum of squared
+// deviations through every level (the reference divides it by n-1 at each merge,
+// layernorm.h:48); the caller divides once at the end.
+__device__ __forceinline__ Welford welford_merge(const Welford &a, const Welford &b) {
+    Welford r;
+    r.n = a.n + b.n;
+    const float w = r.n > 0.f ? b.n / r.n : 0.f;
+    const float delta = b.mean - a.mean;
+    r.mean = fmaf(delta, w, a.mean);
+    r.m2 = a.m2 + b.m2 + delta * delta * a.n * w;
+    return r;
+}
+
+__device__ __forceinline__ Welford warp_allreduce_welford(Welford w) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        Welford o;
+        o.n = __shfl_xor_sync(kFullMask, w.n, m);
+        o.mean = __shfl_xor_sync(kFullMask, w.mean, m);
+        o.m2 = __shfl_xor_sync(kFullMask, w.m2, m);
+        w = welford_merge(w, o);
+    }
+    // merge(a,b) and merge(b,a) can differ in the last bit, so make the lanes agree
+    w.mean = __shfl_sync(kFullMask, w.mean, 0);
+    w.m2 = __shfl_sync(kFullMask, w.m2, 0);
+    return w;
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+}  // namespace ko

@@ -1,0 +1,376 @@
+// LayerNorm forward over the last dimension for sm_100a, FP32 or BF16 I/O, FP32 statistics.
+//
+// Statistics are Welford/Chan triples (count, mean, M2): every thread forms the exact triple of
+// the elements it holds in registers (mean first, then squared deviations from it), and triples
+// are merged pairwise across lanes by shuffle and across warps through shared memory.  M2 stays
+// a sum of squared deviations through all merge levels and is divided once, by (cols - ddof).
+// (The reference's WelfordMerge divides by n-1 at every level, layernorm.h:48, and its
+// normalisation adds the mean through the Subtract functor, functors.h:168; neither is kept.)
+//
+// Tiers by row length (the reference's warp / block-cached / block-no-cache split,
+// nn_operators/layernorm/layernorm.h:145-201, :204-252, :254-300):
+//   warp tier    one warp owns kRows consecutive rows per step, rows in registers;
+//   block tier   one thread block per row, row in registers, one shared-memory exchange;
+//   stream tier  one thread block per row, two passes over global memory, scalar accesses, any
+//                column count and alignment.
+// y = ((x - mean) * rstd) * gamma + beta, gamma/beta optional, in the I/O element type.
+//
+// The reference's LayerNormWarpImpl / LayerNormBlockImpl / LayerNormBlockNoCacheImpl templates and
+// the layer_normalization<Kernel> __global__ wrapper keep their names and parameters.
+#pragma once
+
+#include "../../common/common.h"
+#include "../../common/functors.h"
+
+namespace ko {
+
+// 16-byte vector of I/O elements, unpacked to FP32
+template <typename T>
+struct RowIo;
+
+template <>
+struct RowIo<float> {
+    static constexpr int kPerVec = 4;
+    using Raw = float4;
+    __device__ __forceinline__ static void unpack(const Raw &r, float (&f)[4]) {
+        f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w;
+    }
+    __device__ __forceinline__ static Raw pack(const float (&f)[4]) { return make_float4(f[0], f[1], f[2], f[3]); }
+    __device__ __forceinline__ static float to_float(float v) { return v; }
+    __device__ __forceinline__ static float from_float(float v) { return v; }
+};
+
+template <>
+struct RowIo<__nv_bfloat16> {
+    static constexpr int kPerVec = 8;
+    using Raw = uint4;
+    __device__ __forceinline__ static void unpack(const Raw &r, float (&f)[8]) {
+        f[0] = bf16_lo(r.x); f[1] = bf16_hi(r.x); f[2] = bf16_lo(r.y); f[3] = bf16_hi(r.y);
+        f[4] = bf16_lo(r.z); f[5] = bf16_hi(r.z); f[6] = bf16_lo(r.w); f[7] = bf16_hi(r.w);
+    }
+    __device__ __forceinline__ static Raw pack(const float (&f)[8]) {
+        return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+    }
+    __device__ __forceinline__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+};
+
+// exact (count, mean, M2) of kCount values held in registers; `valid` masks trailing vectors
+template <int kCount>
+__device__ __forceinline__ Welford welford_of_registers(const float (&v)[kCount], int valid_count) {
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCount; ++i) sum += i < valid_count ? v[i] : 0.f;
+    Welford w;
+    w.n = (float)valid_count;
+    w.mean = valid_count > 0 ? sum / w.n : 0.f;
+    float m2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCount; ++i) {
+        const float d = v[i] - w.mean;
+        m2 = i < valid_count ? fmaf(d, d, m2) : m2;
+    }
+    w.m2 = m2;
+    return w;
+}
+
+__device__ __forceinline__ float rstd_from(const Welford &w, int cols, int ddof, float eps) {
+    const float denom = (float)(cols - ddof);
+    const float var = denom > 0.f ? w.m2 / denom : 0.f;
+    return rsqrtf(var + eps);
+}
+
+// ---------------------------------------------------------------------------------------------
+// warp tier: kVecs 16-byte vectors per lane per row, kRows rows per warp step
+// ---------------------------------------------------------------------------------------------
+template <typename T, int kVecs, int kRows>
+__device__ __forceinline__ void layernorm_warp_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                    const T *gamma, const T *beta, int ddof) {
+    using Io = RowIo<T>;
+    using Raw = typename Io::Raw;
+    constexpr int kPer = Io::kPerVec;
+    const int lane = threadIdx.x & 31;
+    const int nvec = cols / kPer;
+    const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
+    const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const Raw *in_v = reinterpret_cast<const Raw *>(in);
+    Raw *out_v = reinterpret_cast<Raw *>(out);
+    const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma);
+    const Raw *beta_v = reinterpret_cast<const Raw *>(beta);
+
+    // vectors this lane owns in a row: lane, lane+32, ...
+    int my_vecs = 0;
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) my_vecs += (lane + 32 * j < nvec) ? 1 : 0;
+
+    for (long long row0 = warp_global * kRows; row0 < rows; row0 += warps_per_grid * kRows) {
+        float x[kRows][kVecs * kPer];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const bool row_ok = row0 + r < rows;
+            Raw raw[kVecs];
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const int v = lane + 32 * j;
+                if (row_ok && v < nvec) raw[j] = ld_stream(in_v + (row0 + r) * nvec + v);
+                else raw[j] = Raw{};
+            }
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                float f[kPer];
+                Io::unpack(raw[j], f);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) x[r][j * kPer + e] = f[e];
+            }
+        }
+        Welford stats[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) stats[r] = welford_of_registers<kVecs * kPer>(x[r], my_vecs * kPer);
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) stats[r] = warp_allreduce_welford(stats[r]);
+
+        float mean[kRows], rstd[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            mean[r] = stats[r].mean;
+            rstd[r] = rstd_from(stats[r], cols, ddof, eps);
+        }
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = lane + 32 * j;
+            if (v >= nvec) continue;
+            float g[kPer], b[kPer];
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) { g[e] = 1.f; b[e] = 0.f; }
+            if (gamma) Io::unpack(__ldg(gamma_v + v), g);
+            if (beta) Io::unpack(__ldg(beta_v + v), b);
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                if (row0 + r >= rows) continue;
+                float y[kPer];
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) y[e] = fmaf((x[r][j * kPer + e] - mean[r]) * rstd[r], g[e], b[e]);
+                st_stream(out_v + (row0 + r) * nvec + v, Io::pack(y));
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// block tier: one row per thread block, kVecs vectors per thread
+// ---------------------------------------------------------------------------------------------
+// s_exchange: 3 * 32 floats
+__device__ __forceinline__ Welford block_allreduce_welford(Welford w, float *s_exchange) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    w = warp_allreduce_welford(w);
+    __syncthreads();
+    if (lane == 0) {
+        s_exchange[warp] = w.n;
+        s_exchange[32 + warp] = w.mean;
+        s_exchange[64 + warp] = w.m2;
+    }
+    __syncthreads();
+    Welford t;
+    t.n = lane < nwarps ? s_exchange[lane] : 0.f;
+    t.mean = lane < nwarps ? s_exchange[32 + lane] : 0.f;
+    t.m2 = lane < nwarps ? s_exchange[64 + lane] : 0.f;
+    return warp_allreduce_welford(t);
+}
+
+template <typename T, int kVecs>
+__device__ __forceinline__ void layernorm_block_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                     const T *gamma, const T *beta, int ddof, float *s_exchange) {
+    using Io = RowIo<T>;
+    using Raw = typename Io::Raw;
+    constexpr int kPer = Io::kPerVec;
+    const int nvec = cols / kPer;
+    const Raw *in_v = reinterpret_cast<const Raw *>(in);
+    Raw *out_v = reinterpret_cast<Raw *>(out);
+    const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma);
+    const Raw *beta_v = reinterpret_cast<const Raw *>(beta);
+    int my_vecs = 0;
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) my_vecs += ((int)threadIdx.x + (int)blockDim.x * j < nvec) ? 1 : 0;
+
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        float x[kVecs * kPer];
+        Raw raw[kVecs];
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = threadIdx.x + blockDim.x * j;
+            if (v < nvec) raw[j] = ld_stream(in_v + row * nvec + v);
+            else raw[j] = Raw{};
+        }
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            float f[kPer];
+            Io::unpack(raw[j], f);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) x[j * kPer + e] = f[e];
+        }
+        Welford w = welford_of_registers<kVecs * kPer>(x, my_vecs * kPer);
+        w = block_allreduce_welford(w, s_exchange);
+        const float mean = w.mean;
+        const float rstd = rstd_from(w, cols, ddof, eps);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = threadIdx.x + blockDim.x * j;
+            if (v >= nvec) continue;
+            float g[kPer], b[kPer], y[kPer];
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) { g[e] = 1.f; b[e] = 0.f; }
+            if (gamma) Io::unpack(__ldg(gamma_v + v), g);
+            if (beta) Io::unpack(__ldg(beta_v + v), b);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) y[e] = fmaf((x[j * kPer + e] - mean) * rstd, g[e], b[e]);
+            st_stream(out_v + row * nvec + v, Io::pack(y));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// stream tier: any cols / alignment; per-thread running Welford, two passes over global memory
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void layernorm_stream_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                      const T *gamma, const T *beta, int ddof, float *s_exchange) {
+    using Io = RowIo<T>;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T *x = in + row * cols;
+        T *y = out + row * cols;
+        Welford w{0.f, 0.f, 0.f};
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+            // streaming update (the reference's WelfordUpdate, layernorm.h:13-23)
+            const float v = Io::to_float(x[c]);
+            w.n += 1.f;
+            const float d = v - w.mean;
+            w.mean += d / w.n;
+            w.m2 = fmaf(d, v - w.mean, w.m2);
+        }
+        w = block_allreduce_welford(w, s_exchange);
+        const float mean = w.mean;
+        const float rstd = rstd_from(w, cols, ddof, eps);
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float g = gamma ? Io::to_float(gamma[c]) : 1.f;
+            const float b = beta ? Io::to_float(beta[c]) : 0.f;
+            y[c] = Io::from_float(fmaf((Io::to_float(x[c]) - mean) * rstd, g, b));
+        }
+        __syncthreads();
+    }
+}
+
+// runtime-shape kernels used by the C ABI
+template <typename T, int kVecs, int kRows>
+__global__ void __launch_bounds__(256) layernorm_warp_kernel(const T *in, T *out, long long rows, int cols, float eps,
+                                                             const T *gamma, const T *beta, int ddof) {
+    layernorm_warp_tier<T, kVecs, kRows>(in, out, rows, cols, eps, gamma, beta, ddof);
+}
+template <typename T, int kVecs, int kThreads>
+__global__ void __launch_bounds__(kThreads) layernorm_block_kernel(const T *in, T *out, long long rows, int cols,
+                                                                   float eps, const T *gamma, const T *beta, int ddof) {
+    __shared__ float s_exchange[96];
+    layernorm_block_tier<T, kVecs>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
+}
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_stream_kernel(const T *in, T *out, long long rows, int cols, float eps,
+                                                               const T *gamma, const T *beta, int ddof) {
+    __shared__ float s_exchange[96];
+    layernorm_stream_tier<T>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
+}
+
+}  // namespace ko
+
+// ---------------------------------------------------------------------------------------------
+// reference-named Welford helpers (scalar forms), kept for code written against the reference
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+struct WelfordUpdate {
+    __device__ __forceinline__ void operator()(T &count, T &mean, T &m2, const T &new_value) const {
+        count += T(1);
+        const T delta = new_value - mean;
+        mean += delta / count;
+        m2 += delta * (new_value - mean);
+    }
+};
+
+// Merges (count_b, mean_b, m2_b) into the a-triple; m2 is a sum of squared deviations.
+template <typename T>
+struct WelfordMerge {
+    __device__ __forceinline__ void operator()(T &count_a, T &mean_a, T &m2_a, const T &count_b, const T &mean_b,
+                                               const T &m2_b) const {
+        const T count_ab = count_a + count_b;
+        if (count_ab == T(0)) return;
+        const T delta = mean_b - mean_a;
+        const T w = count_b / count_ab;
+        m2_a = m2_a + m2_b + delta * delta * count_a * w;
+        mean_a += delta * w;
+        count_a = count_ab;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// source-level drop-in for the reference's launch syntax (compile-time shapes)
+// ---------------------------------------------------------------------------------------------
+// ddof of the drop-in templates: population variance (divide by cols), as in BERT's LayerNorm.
+template <typename Element_, int vec_len_, int num_row_, int num_column_, bool elementwise_affine_>
+struct LayerNormWarpImpl {
+    using Element = Element_;
+    static constexpr int vec_len = vec_len_, num_row = num_row_, num_column = num_column_;
+    static constexpr bool elementwise_affine = elementwise_affine_;
+    static constexpr int smem_in_bytes = 0;
+    static constexpr int kPer = ko::RowIo<Element>::kPerVec;
+    static_assert(num_column % kPer == 0, "the warp tier moves 128-bit vectors");
+    static constexpr int kVecs = (num_column / kPer + 31) / 32;
+    static_assert(kVecs * kPer <= 64, "row too long for the warp tier; use LayerNormBlockImpl");
+    static constexpr int kRows = kVecs * kPer <= 16 ? 2 : 1;
+    __device__ __forceinline__ static void run(Element *in_data, Element *out_data, Element epsilon,
+                                               Element *gamma = nullptr, Element *beta = nullptr) {
+        ko::layernorm_warp_tier<Element, kVecs, kRows>(in_data, out_data, num_row, num_column,
+                                                       ko::RowIo<Element>::to_float(epsilon),
+                                                       elementwise_affine ? gamma : nullptr,
+                                                       elementwise_affine ? beta : nullptr, 0);
+    }
+};
+
+template <typename Element_, int vec_len_, int num_row_, int num_column_, bool elementwise_affine_>
+struct LayerNormBlockImpl {
+    using Element = Element_;
+    static constexpr int vec_len = vec_len_, num_row = num_row_, num_column = num_column_;
+    static constexpr bool elementwise_affine = elementwise_affine_;
+    static constexpr int smem_in_bytes = 96 * sizeof(float);
+    static constexpr int kPer = ko::RowIo<Element>::kPerVec;
+    __device__ __forceinline__ static void run(Element *in_data, Element *out_data, Element epsilon,
+                                               Element *gamma = nullptr, Element *beta = nullptr) {
+        extern __shared__ float ko_layernorm_dyn_smem[];
+        Element *g = elementwise_affine ? gamma : nullptr, *b = elementwise_affine ? beta : nullptr;
+        const float eps = ko::RowIo<Element>::to_float(epsilon);
+        if (num_column % kPer == 0 && num_column / kPer <= 8 * (int)blockDim.x)
+            ko::layernorm_block_tier<Element, 8>(in_data, out_data, num_row, num_column, eps, g, b, 0, ko_layernorm_dyn_smem);
+        else
+            ko::layernorm_stream_tier<Element>(in_data, out_data, num_row, num_column, eps, g, b, 0, ko_layernorm_dyn_smem);
+    }
+};
+
+template <typename Element_, int vec_len_, int num_row_, int num_column_, bool elementwise_affine_>
+struct LayerNormBlockNoCacheImpl {
+    using Element = Element_;
+    static constexpr int vec_len = vec_len_, num_row = num_row_, num_column = num_column_;
+    static constexpr bool elementwise_affine = elementwise_affine_;
+    static constexpr int smem_in_bytes = 96 * sizeof(float);
+    __device__ __forceinline__ static void run(Element *in_data, Element *out_data, Element epsilon,
+                                               Element *gamma = nullptr, Element *beta = nullptr) {
+        extern __shared__ float ko_layernorm_dyn_smem[];
+        ko::layernorm_stream_tier<Element>(in_data, out_data, num_row, num_column,
+                                           ko::RowIo<Element>::to_float(epsilon), elementwise_affine ? gamma : nullptr,
+                                           elementwise_affine ? beta : nullptr, 0, ko_layernorm_dyn_smem);
+    }
+};
+
+template <typename LayerNormKernel>
+__global__ void layer_normalization(typename LayerNormKernel::Element *in_data,
+                                    typename LayerNormKernel::Element *out_data,
+                                    typename LayerNormKernel::Element epsilon,
+                                    typename LayerNormKernel::Element *gamma = nullptr,
+                                    typename LayerNormKernel::Element *beta = nullptr) {
+    LayerNormKernel::run(in_data, out_data, epsilon, gamma, beta);
+}

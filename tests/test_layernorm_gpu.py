@@ -1,0 +1,143 @@
+"""GPU parity of ko_layernorm_f32 / ko_layernorm_bf16 (through the C ABI) against the float64
+oracle and size-independent properties at the full shapes.
+
+Tolerance (BASELINE): max-rel <= 1e-5 with max-rel = max |y - ref| / max(|ref|, 1).  BF16 output is
+compared with the BF16-rounded oracle: at most a rounding-boundary flip (one BF16 ulp) is allowed
+and only on a small fraction of the elements."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL_REL = 1e-5
+
+
+def _inputs(oracle, rows, cols, seed=1):
+    return (oracle.fill_normal((rows, cols), seed, 0, 0.0, 1.0), oracle.fill_uniform((cols,), seed, 1, 0.5, 1.5),
+            oracle.fill_normal((cols,), seed, 2, 0.0, 0.1))
+
+
+def _run_f32(cuda, lib, x, eps, g=None, b=None, ddof=0, rpw=0, block=0, cap=0, inplace=False):
+    xd = cuda.from_numpy(x).cuda()
+    gd = None if g is None else cuda.from_numpy(g).cuda()
+    bd = None if b is None else cuda.from_numpy(b).cuda()
+    yd = xd if inplace else cuda.empty_like(xd)
+    rows, cols = x.shape
+    rc = lib.ko_layernorm_f32_tuned(xd.data_ptr(), yd.data_ptr(), rows, cols, eps, None if gd is None else gd.data_ptr(),
+                                    None if bd is None else bd.data_ptr(), ddof, rpw, block, cap,
+                                    cuda.cuda.current_stream().cuda_stream)
+    cuda.cuda.synchronize()
+    assert rc == 0, lib.ko_last_error_string()
+    return yd.cpu().numpy()
+
+
+def _dev_bf16(cuda, bits):
+    return cuda.from_numpy(bits.view(np.int16)).cuda().view(cuda.bfloat16)
+
+
+def _run_bf16(cuda, lib, xb, eps, gb=None, bb=None, ddof=0, block=0):
+    xd = _dev_bf16(cuda, xb)
+    gd = None if gb is None else _dev_bf16(cuda, gb)
+    bd = None if bb is None else _dev_bf16(cuda, bb)
+    yd = cuda.empty_like(xd)
+    rows, cols = xb.shape
+    rc = lib.ko_layernorm_bf16_tuned(xd.data_ptr(), yd.data_ptr(), rows, cols, eps, None if gd is None else gd.data_ptr(),
+                                     None if bd is None else bd.data_ptr(), ddof, 0, block, 0,
+                                     cuda.cuda.current_stream().cuda_stream)
+    cuda.cuda.synchronize()
+    assert rc == 0, lib.ko_last_error_string()
+    return yd.view(cuda.int16).cpu().numpy().view(np.uint16)
+
+
+SHAPES = [(1, 1), (3, 1), (5, 4), (7, 100), (5, 131), (100, 128), (33, 256), (1000, 768), (37, 1024), (64, 2048),
+          (9, 2052), (11, 4096), (5, 12288), (2, 32768), (3, 40000), (2, 131072)]
+
+
+@pytest.mark.parametrize("rows,cols", SHAPES)
+def test_f32_against_float64_oracle(cuda, lib, oracle, rows, cols):
+    x, g, b = _inputs(oracle, rows, cols)
+    assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+    assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-5, None, None, 1), oracle.layernorm_f64(x, 1e-5, None, None, 1)) <= TOL_REL
+    assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-5, g, None), oracle.layernorm_f64(x, 1e-5, g, None)) <= TOL_REL
+
+
+def test_f32_is_not_the_reference_kernels_arithmetic(cuda, lib, oracle, golden):
+    """The reference's kernel output on the same input (committed fixture) is not LayerNorm; the
+    product follows the mathematical operator, the documented deviation."""
+    x, _g, _b = _inputs(oracle, 8, 768)
+    y = _run_f32(cuda, lib, x, 1e-4)
+    assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-4)) <= TOL_REL
+    assert np.abs(y - golden["layernorm_8x768_warp"]).max() > 10.0
+
+
+@pytest.mark.parametrize("rpw,block,cap", [(1, 64, 0), (2, 128, 0), (1, 256, 5), (2, 256, 1)])
+def test_f32_launch_geometry_does_not_change_rows(cuda, lib, oracle, rpw, block, cap):
+    for cols in (128, 256, 512, 768, 1024):
+        x, g, b = _inputs(oracle, 77, cols)
+        assert np.array_equal(_run_f32(cuda, lib, x, 1e-12, g, b, 0, rpw, block, cap), _run_f32(cuda, lib, x, 1e-12, g, b))
+
+
+@pytest.mark.parametrize("block", [128, 256, 512, 1024])
+def test_f32_block_tier_thread_counts(cuda, lib, oracle, block):
+    for cols in (2048, 4096, 8192):
+        x, g, b = _inputs(oracle, 19, cols)
+        assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b, 0, 0, block), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+
+
+def test_f32_edge_rows(cuda, lib, oracle):
+    const = np.full((4, 768), 3.25, dtype=np.float32)
+    assert np.array_equal(_run_f32(cuda, lib, const, 1e-12), np.zeros_like(const))      # var = 0
+    x, g, b = _inputs(oracle, 300, 768)
+    x += 1000.0                                                                          # large common offset
+    assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+    y = _run_f32(cuda, lib, x, 1e-12, g, b)
+    assert np.array_equal(_run_f32(cuda, lib, x, 1e-12, g, b, inplace=True), y)
+    assert np.array_equal(_run_f32(cuda, lib, x, 1e-12, g, b), y)
+
+
+def test_f32_full_bert_shape(cuda, lib, oracle, ko):
+    """C2: [16384, 768], x ~ N(0,1), gamma ~ U(0.5,1.5), beta ~ N(0,0.1^2), eps 1e-12, seed 1: the whole
+    tensor against the oracle, plus the property that un-affined output rows have mean 0 / variance 1."""
+    rows, cols = 16384, 768
+    x = ko.fill_normal((rows, cols), 1, 0, 0.0, 1.0)
+    g, b = ko.fill_uniform((cols,), 1, 1, 0.5, 1.5), ko.fill_normal((cols,), 1, 2, 0.0, 0.1)
+    assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+    y = _run_f32(cuda, lib, x, 1e-12).astype(np.float64)
+    assert np.abs(y.mean(1)).max() <= 1e-6 and np.abs(y.var(1) - 1.0).max() <= 1e-5
+
+
+BF16_SHAPES = [(3, 1), (5, 8), (7, 100), (100, 256), (1000, 768), (64, 2048), (9, 2056), (37, 4096), (11, 8192),
+               (3, 40000)]
+
+
+@pytest.mark.parametrize("rows,cols", BF16_SHAPES)
+def test_bf16_against_rounded_oracle(cuda, lib, oracle, rows, cols):
+    x, g, b = _inputs(oracle, rows, cols)
+    xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
+    want = oracle.layernorm_f64(oracle.from_bf16_bits(xb), 1e-12, oracle.from_bf16_bits(gb), oracle.from_bf16_bits(bb))
+    got_bits = _run_bf16(cuda, lib, xb, 1e-12, gb, bb)
+    want_bits = oracle.to_bf16_bits(want.astype(np.float32))
+    got, want_r = oracle.from_bf16_bits(got_bits), oracle.from_bf16_bits(want_bits)
+    assert np.mean(got_bits != want_bits) <= 2e-3, "only rounding-boundary flips may differ"
+    assert np.abs(got - want_r).max() <= np.abs(want_r).max() * 2.0 ** -7      # at most one BF16 ulp
+    assert oracle.max_rel_err(got, want) <= 2.0 ** -8 * 1.01                    # half an ulp of BF16 rounding
+
+
+@pytest.mark.parametrize("block", [128, 256, 512, 1024])
+def test_bf16_block_tier_thread_counts(cuda, lib, oracle, block):
+    x, g, b = _inputs(oracle, 21, 8192)
+    xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
+    base = _run_bf16(cuda, lib, xb, 1e-12, gb, bb)
+    assert np.mean(_run_bf16(cuda, lib, xb, 1e-12, gb, bb, block=block) != base) <= 2e-3
+
+
+def test_bf16_scaled_shard_properties(cuda, lib, oracle, ko):
+    """A slice of C5's LayerNorm: BF16 [32768, 4096] (1/8 of the rows), seed 4: sampled rows against the
+    oracle, every row by mean/variance of the un-affined output."""
+    rows, cols = 32768, 4096
+    xb = ko.fill_normal((rows, cols), 4, 0, 0.0, 1.0, dtype=2)
+    got = oracle.from_bf16_bits(_run_bf16(cuda, lib, xb, 1e-12))
+    assert np.abs(got.mean(1, dtype=np.float64)).max() <= 2e-3 and np.abs(got.var(1, dtype=np.float64) - 1.0).max() <= 1e-2
+    pick = np.r_[0:64, rows - 64:rows, np.random.default_rng(4).integers(0, rows, 512)]
+    want = oracle.layernorm_f64(oracle.from_bf16_bits(xb[pick]), 1e-12)
+    assert oracle.max_rel_err(got[pick], want) <= 2.0 ** -8 * 1.01
