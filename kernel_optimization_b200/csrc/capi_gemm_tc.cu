@@ -1,10 +1,150 @@
-// placeholder until the tcgen05 kernel lands
+// C-ABI launchers of the tcgen05 tensor-core GEMM: build the TMA descriptors, pick the tile width,
+// launch one persistent CTA per SM.
 #include "ko_internal.h"
+#include "ko_tuning.h"
+
+#include <mutex>
+
+#include <cudaTypedefs.h>
+
+#include "../nn_operators/gemm/tensor_core_gemm.h"
+
+namespace {
+
+// Bounded device-side waits report here (first failure wins); read and cleared by
+// ko_gemm_tc_poll_status().
+__device__ unsigned int g_tc_status_word;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn *out) {
+    static std::mutex mu;
+    static EncodeTiledFn cached = nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        KO_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        KO_REQUIRE(qres == cudaDriverEntryPointSuccess && fn != nullptr, KO_ERR_CUDA,
+                   "cuTensorMapEncodeTiled is not available from this driver");
+        cached = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    *out = cached;
+    return KO_OK;
+}
+
+// 2-D map over a K-contiguous 16-bit matrix [rows, K]; box = 64 (K) x box_rows, 128-byte swizzle,
+// out-of-range elements read as zero
+int make_map(EncodeTiledFn encode, CUtensorMap *map, int fmt, const void *base, int64_t rows, int64_t K, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)ko::tc::kBK, (cuuint32_t)box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUtensorMapDataType dt = fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUresult r = encode(map, dt, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KO_REQUIRE(r == CUDA_SUCCESS, KO_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return KO_OK;
+}
+
+template <int BN>
+int launch(const CUtensorMap &ma, const CUtensorMap &mb, const ko::tc::GemmParams &p, int sm_count, cudaStream_t s) {
+    using Cfg = ko::tc::TileConfig<BN>;
+    static std::mutex mu;
+    static bool configured[64] = {};
+    int dev = 0;
+    KO_CUDA(cudaGetDevice(&dev));
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!configured[dev]) {
+            KO_CUDA(cudaFuncSetAttribute(ko::tc::gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes));
+            configured[dev] = true;
+        }
+    }
+    const long long tiles = (long long)((p.M + ko::tc::kBM - 1) / ko::tc::kBM) * ((p.N + BN - 1) / BN);
+    const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
+    ko::tc::gemm_tcgen05_kernel<BN><<<grid, ko::tc::kThreads, Cfg::kSmemBytes, s>>>(ma, mb, p);
+    KO_CHECK_LAUNCH("gemm_tcgen05_kernel");
+    return KO_OK;
+}
+
+double wave_efficiency(long long M, long long N, int bn, int sm_count) {
+    const long long tiles = ((M + 127) / 128) * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sm_count - 1) / sm_count;
+    return (double)(M * N) / (double)(waves * sm_count * 128LL * bn);
+}
+
+}  // namespace
+
 extern "C" {
-int ko_gemm_f16_f32(int64_t, int64_t, int64_t, const uint16_t *, const uint16_t *, const float *, float *, void *) {
-    return ko::fail(KO_ERR_SHAPE, "tensor-core GEMM is not built into this library yet");
+
+// fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns per tile
+int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C,
+                     float *D, int bn, void *stream) {
+    KO_REQUIRE(fmt == 0 || fmt == 1, KO_ERR_INVALID_ARG, "gemm: fmt must be 0 (f16) or 1 (bf16)");
+    KO_REQUIRE(M >= 0 && N >= 0 && K >= 0, KO_ERR_INVALID_ARG, "gemm: negative shape {%lld,%lld,%lld}", (long long)M,
+               (long long)N, (long long)K);
+    if (M == 0 || N == 0) return KO_OK;
+    KO_REQUIRE(M <= 0x7fffffff && N <= 0x7fffffff && K <= 0x7fffffff, KO_ERR_SHAPE, "gemm: dimension exceeds 2^31-1");
+    KO_REQUIRE(K >= 8 && K % 8 == 0, KO_ERR_SHAPE, "gemm: K = %lld must be a positive multiple of 8 (16-byte row pitch)",
+               (long long)K);
+    KO_REQUIRE(A != nullptr && B != nullptr && D != nullptr, KO_ERR_INVALID_ARG, "gemm: NULL pointer");
+    KO_REQUIRE(ko::aligned16(A) && ko::aligned16(B), KO_ERR_ALIGN, "gemm: A and B must be 16-byte aligned");
+    KO_REQUIRE((const void *)D != (const void *)A && (const void *)D != (const void *)B, KO_ERR_INVALID_ARG,
+               "gemm: D must not alias A or B");
+    ko::DeviceInfo info;
+    if (int st = ko::current_device_info(&info)) return st;
+    EncodeTiledFn encode = nullptr;
+    if (int st = get_encode_fn(&encode)) return st;
+
+    if (bn == 0) {
+        const double e256 = wave_efficiency(M, N, 256, info.sm_count);
+        const double e128 = 0.80 * wave_efficiency(M, N, 128, info.sm_count);
+        bn = (N > 128 && e256 >= e128) ? 256 : 128;
+        if (N <= 64) bn = 64;
+    }
+    KO_REQUIRE(bn == 64 || bn == 128 || bn == 256, KO_ERR_INVALID_ARG, "gemm: tile width %d not in {64,128,256}", bn);
+
+    alignas(64) CUtensorMap map_a, map_b;
+    if (int st = make_map(encode, &map_a, fmt, A, M, K, ko::tc::kBM)) return st;
+    if (int st = make_map(encode, &map_b, fmt, B, N, K, bn)) return st;
+
+    ko::tc::GemmParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.C = C; p.D = D; p.fmt = fmt;
+    void *status_ptr = nullptr;
+    KO_CUDA(cudaGetSymbolAddress(&status_ptr, g_tc_status_word));
+    p.status = static_cast<unsigned *>(status_ptr);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (bn) {
+        case 64: return launch<64>(map_a, map_b, p, info.sm_count, s);
+        case 128: return launch<128>(map_a, map_b, p, info.sm_count, s);
+        default: return launch<256>(map_a, map_b, p, info.sm_count, s);
+    }
 }
-int ko_gemm_bf16_f32(int64_t, int64_t, int64_t, const uint16_t *, const uint16_t *, const float *, float *, void *) {
-    return ko::fail(KO_ERR_SHAPE, "tensor-core GEMM is not built into this library yet");
+
+int ko_gemm_f16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C, float *D,
+                    void *stream) {
+    return ko_gemm_tc_tuned(0, M, N, K, A, B, C, D, 0, stream);
 }
+
+int ko_gemm_bf16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C, float *D,
+                     void *stream) {
+    return ko_gemm_tc_tuned(1, M, N, K, A, B, C, D, 0, stream);
 }
+
+int ko_gemm_tc_poll_status(void) {
+    unsigned int word = 0;
+    KO_CUDA(cudaMemcpyFromSymbol(&word, g_tc_status_word, sizeof word));
+    if (word == 0) return KO_OK;
+    const unsigned int zero = 0;
+    KO_CUDA(cudaMemcpyToSymbol(g_tc_status_word, &zero, sizeof zero));
+    static const char *who[] = {"", "the TMA producer", "the MMA issuer", "an epilogue warp", "the tensor-memory drain"};
+    return ko::fail(KO_ERR_TIMEOUT, "tensor-core GEMM: a bounded wait ran out in %s", word < 5 ? who[word] : "an unknown role");
+}
+
+}  // extern "C"

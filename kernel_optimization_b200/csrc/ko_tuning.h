@@ -20,6 +20,9 @@ int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int
 /* variant: 0 = choose, 1 = 128x128 tiles, 2 = 128x64, 3 = 64x64 */
 int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
                        int variant, void *stream);
+/* fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns of D per tile */
+int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C,
+                     float *D, int bn, void *stream);
 
 #ifdef __cplusplus
 }

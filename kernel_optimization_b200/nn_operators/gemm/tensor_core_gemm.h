@@ -1,0 +1,374 @@
+// Tensor-core GEMM for sm_100a: D[M,N] (FP32) = A[M,K] (row-major) * B[K,N] (column-major) (+ C),
+// FP16 or BF16 inputs, FP32 accumulation in tensor memory.
+//
+// Stands in for the reference's GemmKernelTensorCore (nn_operators/gemm/tensor_core_gemm.h:101-399),
+// a Turing mma.sync.m16n8k8 kernel with FP16 accumulation that is unfinished and disabled there.
+// Nothing of that design carries over; this is a Blackwell pipeline:
+//
+//   warp 0      producer: one lane issues TMA tile loads (cp.async.bulk.tensor.2d, 128-byte swizzle,
+//               this CTA only) of a 128 x 64 A tile and a BN x 64 B tile per stage into a ring of
+//               shared-memory stages, signalling `full` mbarriers with the byte count;
+//   warp 1      MMA: owns the tensor-memory allocation; one lane issues tcgen05.mma
+//               (cta_group::1, kind::f16, M=128, N=BN, K=16; four per stage) reading the operands
+//               straight from shared memory through matrix descriptors, accumulating in TMEM, and
+//               tcgen05.commit to the stage's `empty` mbarrier / the accumulator's `ready` mbarrier;
+//   warps 2-5   epilogue: tcgen05.ld the 128 x BN FP32 accumulator (each warp its 32-lane quadrant),
+//               add C when given, store D with 128-bit writes.
+//
+// The CTA is persistent: tiles are dealt round-robin in an order that keeps concurrently running
+// tiles on neighbouring A/B panels (L2 reuse), and the accumulator is double buffered in TMEM
+// (2 x BN columns) so the epilogue of one tile overlaps the MMAs of the next.
+//
+// M, N and K tails: TMA zero-fills out-of-range rows/columns, zero K-columns add nothing, and the
+// epilogue predicates its stores.  K must be a multiple of 8 (16-byte global row pitch for TMA).
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the waiting role records a code in the
+// device status word, raises the CTA's abort flag and all roles drain and leave; tensor memory is
+// released on every path.
+#pragma once
+
+#include <cuda.h>
+
+#include "../../common/common.h"
+
+namespace ko {
+namespace tc {
+
+constexpr int kBM = 128;          // rows of D per tile = TMEM lanes
+constexpr int kBK = 64;           // K elements per stage: 64 * 2 B = one 128-byte swizzle row
+constexpr int kUmmaK = 16;        // K per tcgen05.mma for 16-bit inputs
+constexpr int kThreads = 192;     // 6 warps: producer, MMA, 4 x epilogue
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+// codes written to the status word (first failure wins)
+enum : unsigned { kStatusOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3, kTimeoutDrain = 4 };
+
+template <int BN>
+struct TileConfig {
+    static constexpr int kBN = BN;
+    static constexpr int kBytesA = kBM * kBK * 2;
+    static constexpr int kBytesB = BN * kBK * 2;
+    static constexpr int kStageBytes = kBytesA + kBytesB;
+    static constexpr int kStages = BN >= 256 ? 4 : 6;
+    static constexpr int kTmemCols = 2 * BN;  // double-buffered FP32 accumulator (power of two >= 32)
+    static constexpr int kBarrierBytes = 256;
+    // + 1024 so the stage ring can be aligned to the 1024-byte swizzle period
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+    static_assert(BN == 64 || BN == 128 || BN == 256, "BN must keep 2*BN a power of two <= 512");
+};
+
+// ------------------------------------------------------------------------------------------------
+// thin PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// TMA 2-D tile load into this CTA's shared memory; x = innermost (K) coordinate, y = row
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// whole warp
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; accumulate == 0 overwrites D
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// the mbarrier is arrived on once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive FP32 columns: thread t receives row (lane base + t)
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what the TMA load above produces): 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);  // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: 8 rows * 128 B
+    d |= (uint64_t)1 << 46;                        // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                        // layout: 128-byte swizzle
+    return d;
+}
+
+// kind::f16 instruction descriptor: FP32 accumulator, A and B of `fmt` (0 = F16, 1 = BF16), both
+// K-major, dense, M x N tile
+__host__ __device__ constexpr uint32_t make_idesc(int fmt, int m, int n) {
+    return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+// tile order: groups of kGroupM tile-rows, tile-columns fastest inside a group's rows
+constexpr int kGroupM = 8;
+__device__ __forceinline__ void tile_coords(long long t, int tiles_m, int tiles_n, int &tm, int &tn) {
+    const long long per_group = (long long)kGroupM * tiles_n;
+    const int group = (int)(t / per_group);
+    const int first_m = group * kGroupM;
+    const int rows_in_group = min(kGroupM, tiles_m - first_m);
+    const int in_group = (int)(t % per_group);
+    tm = first_m + in_group % rows_in_group;
+    tn = in_group / rows_in_group;
+}
+
+struct GemmParams {
+    int M, N, K;
+    const float *C;   // may be null
+    float *D;
+    unsigned *status; // device status word
+    int fmt;          // 0 = F16, 1 = BF16
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+    using Cfg = TileConfig<BN>;
+    extern __shared__ uint8_t ko_tc_smem_raw[];
+    // stage ring on a 1024-byte boundary (swizzle period), barriers behind it
+    const uint32_t raw = smem_u32(ko_tc_smem_raw);
+    const uint32_t ring = (raw + 1023u) & ~1023u;
+    uint8_t *ring_ptr = ko_tc_smem_raw + (ring - raw);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring_ptr + Cfg::kStages * Cfg::kStageBytes);
+    const uint32_t bar_base = ring + Cfg::kStages * Cfg::kStageBytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+    auto acc_ready_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + a); };
+    auto acc_free_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + 2 + a); };
+    const uint32_t drain_bar = bar_base + 8u * (2 * Cfg::kStages + 4);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * Cfg::kStages + 5);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + kBM - 1) / kBM, tiles_n = (p.N + BN - 1) / BN;
+    const long long num_tiles = (long long)tiles_m * tiles_n;
+    const int k_blocks = (p.K + kBK - 1) / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_ready_bar(a), 1);
+            mbar_init(acc_free_bar(a), 4);  // one arrival per epilogue warp
+        }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int tm, tn;
+                tile_coords(t, tiles_m, tiles_n, tm, tn);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % Cfg::kStages;
+                    const uint32_t phase = (it / Cfg::kStages) & 1u;
+                    if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag)) {
+                        if (!*abort_flag) atomicCAS(p.status, kStatusOk, kTimeoutProducer);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
+                    const uint32_t dst = ring + s * Cfg::kStageBytes;
+                    tma_load_2d(dst, &map_a, kb * kBK, tm * kBM, full_bar(s));
+                    tma_load_2d(dst + Cfg::kBytesA, &map_b, kb * kBK, tn * BN, full_bar(s));
+                }
+            }
+            if (!ok) {
+                // loads already issued still land in shared memory: wait (bounded) for the most recent
+                // fill of every stage before the block may retire
+                for (uint32_t back = 0; back < (uint32_t)Cfg::kStages && back < it; ++back) {
+                    const uint32_t j = it - 1 - back;
+                    const uint32_t bar = full_bar(j % Cfg::kStages), parity = (j / Cfg::kStages) & 1u;
+                    for (uint32_t spin = 0; spin < kSpinLimit && !mbar_try_wait(bar, parity); ++spin) {}
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(p.fmt, kBM, BN);
+            uint32_t it = 0, local_tile = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
+                const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+                if (!mbar_wait(acc_free_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % Cfg::kStages;
+                    const uint32_t phase = (it / Cfg::kStages) & 1u;
+                    if (!mbar_wait(full_bar(s), phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = ring + s * Cfg::kStageBytes, b_addr = a_addr + Cfg::kBytesA;
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        // advancing K inside the swizzled row: +32 bytes per 16 elements
+                        const uint64_t da = smem_desc_k_major_sw128(a_addr + k * kUmmaK * 2);
+                        const uint64_t db = smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
+                        umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(s));  // the stage is reusable once these MMAs have read it
+                }
+                if (ok) umma_commit(acc_ready_bar(acc));
+            }
+            if (!ok) {
+                if (!*abort_flag) atomicCAS(p.status, kStatusOk, kTimeoutMma);
+                *abort_flag = 1;
+            }
+            // nothing may still be writing tensor memory when it is released
+            umma_commit(drain_bar);
+            bool drained = false;
+            for (uint32_t spin = 0; spin < kSpinLimit && !(drained = mbar_try_wait(drain_bar, 0)); ++spin) {}
+            if (!drained) atomicCAS(p.status, kStatusOk, kTimeoutDrain);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+        const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0) &&
+                            (p.C == nullptr || (reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+        uint32_t local_tile = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
+            int tm, tn;
+            tile_coords(t, tiles_m, tiles_n, tm, tn);
+            const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+            if (!mbar_wait(acc_ready_bar(acc), acc_phase, abort_flag)) {
+                if (lane == 0 && !*abort_flag) atomicCAS(p.status, kStatusOk, kTimeoutEpilogue);
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const int row = tm * kBM + quad * 32 + lane;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                float v[32];
+                tmem_ld_32x32(t_row + c0, v);  // warp-collective: every lane takes part
+                const int col = tn * BN + c0;
+                if (row < p.M && col < p.N) {
+                    const size_t off = (size_t)row * p.N + col;
+                    if (vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (col + j < p.N) {
+                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                if (p.C) {
+                                    const float4 c = *reinterpret_cast<const float4 *>(p.C + off + j);
+                                    o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+                                }
+                                *reinterpret_cast<float4 *>(p.D + off + j) = o;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < p.N) p.D[off + j] = p.C ? v[j] + p.C[off + j] : v[j];
+                    }
+                }
+            }
+            // the accumulator buffer may be overwritten once all four warps have read it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_free_bar(acc));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+}  // namespace tc
+}  // namespace ko

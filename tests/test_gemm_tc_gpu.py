@@ -1,0 +1,113 @@
+"""GPU parity of ko_gemm_f16_f32 / ko_gemm_bf16_f32 (tcgen05, through the C ABI) against the float64
+oracle on the rounded inputs.  Tolerance (BASELINE): relative Frobenius error <= 1e-3; with exact
+products and FP32 accumulation the kernel actually lands near 1e-6, which is asserted too so that
+a dropped K-step or a mis-addressed tile cannot hide under the loose bound."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL_FRO = 1e-3
+TIGHT_FRO = 2e-6
+
+
+def _bits(oracle, kind):
+    return (oracle.to_f16_bits, oracle.from_f16_bits) if kind == "f16" else (oracle.to_bf16_bits, oracle.from_bf16_bits)
+
+
+def _dev16(cuda, bits, kind):
+    return cuda.from_numpy(bits.view(np.int16)).cuda().view(cuda.float16 if kind == "f16" else cuda.bfloat16)
+
+
+def _run(cuda, lib, kind, ab, bb, c=None, bn=0):
+    M, K = ab.shape
+    N = bb.shape[0]
+    ad, bd = _dev16(cuda, ab, kind), _dev16(cuda, bb, kind)
+    cd = None if c is None else cuda.from_numpy(c).cuda()
+    dd = cuda.full((M, N), float("nan"), dtype=cuda.float32, device="cuda")
+    rc = lib.ko_gemm_tc_tuned(0 if kind == "f16" else 1, M, N, K, ad.data_ptr(), bd.data_ptr(),
+                              None if cd is None else cd.data_ptr(), dd.data_ptr(), bn, cuda.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.ko_last_error_string()
+    cuda.cuda.synchronize()
+    assert lib.ko_gemm_tc_poll_status() == 0, lib.ko_last_error_string()
+    return dd.cpu().numpy()
+
+
+def _case(cuda, lib, oracle, kind, M, N, K, with_c=False, bn=0, seed=3):
+    to_bits, from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), seed, 0)), to_bits(oracle.fill_uniform((N, K), seed, 1))
+    c = oracle.fill_uniform((M, N), seed, 2) if with_c else None
+    d = _run(cuda, lib, kind, ab, bb, c, bn)
+    want = oracle.gemm_tn_f64(from_bits(ab), from_bits(bb), c)
+    err = oracle.rel_frobenius(d, want)
+    assert err <= TOL_FRO and err <= TIGHT_FRO, (kind, M, N, K, bn, err)
+    return d
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_single_tile_and_k_steps(cuda, lib, oracle, kind, bn):
+    for K in (64, 128, 8, 72, 1024):
+        _case(cuda, lib, oracle, kind, 128, bn, K, bn=bn)
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (1, 4, 8), (100, 36, 56), (129, 260, 136), (1000, 520, 200),
+                                   (2048, 1024, 512), (131, 4100, 64), (5000, 12, 320)])
+def test_tails_and_multiple_tiles(cuda, lib, oracle, kind, M, N, K):
+    for bn in (0, 128):
+        _case(cuda, lib, oracle, kind, M, N, K, bn=bn)
+    _case(cuda, lib, oracle, kind, M, N, K, with_c=True)
+
+
+def test_n_not_multiple_of_four_takes_scalar_stores(cuda, lib, oracle):
+    _case(cuda, lib, oracle, "bf16", 200, 37, 64)
+    _case(cuda, lib, oracle, "f16", 200, 37, 64, with_c=True)
+
+
+def test_more_tiles_than_sms_and_both_accumulators(cuda, lib, oracle):
+    # 64 x 32 = 2048 tiles of 128 x 128: every CTA walks many tiles, alternating TMEM buffers
+    _case(cuda, lib, oracle, "bf16", 8192, 4096, 64, bn=128)
+    d1 = _case(cuda, lib, oracle, "f16", 4096, 4096, 256, bn=256)
+    d2 = _case(cuda, lib, oracle, "f16", 4096, 4096, 256, bn=128)
+    assert np.array_equal(d1, d1) and oracle.rel_frobenius(d2, d1.astype(np.float64)) <= TIGHT_FRO
+
+
+def test_exact_small_integers(cuda, lib, oracle):
+    """Inputs that are small integers make every product and partial sum exact: the result must
+    equal the integer matrix product bit for bit, whatever the accumulation order."""
+    rng = np.random.default_rng(3)
+    M, N, K = 384, 320, 192
+    a, b = rng.integers(-4, 5, (M, K)).astype(np.float32), rng.integers(-4, 5, (N, K)).astype(np.float32)
+    want = (a.astype(np.int64) @ b.astype(np.int64).T).astype(np.float32)
+    for kind in ("f16", "bf16"):
+        to_bits, _ = _bits(oracle, kind)
+        assert np.array_equal(_run(cuda, lib, kind, to_bits(a), to_bits(b)), want)
+
+
+def test_baseline_shapes(cuda, lib, oracle, ko):
+    """C4: 4096^3 and the BERT FFN shape 16384 x 3072 x 768, U(-1,1) seed 3.  The float64 oracle
+    checks 64 full rows (first/last tile rows included) and 4096 random entries; cuBLAS-free."""
+    rng = np.random.default_rng(3)
+    for kind, code in (("f16", 1), ("bf16", 2)):
+        _, from_bits = _bits(oracle, kind)
+        for M, N, K in ((4096, 4096, 4096), (16384, 3072, 768)):
+            ab, bb = ko.fill_uniform((M, K), 3, 0, dtype=code), ko.fill_uniform((N, K), 3, 1, dtype=code)
+            d = _run(cuda, lib, kind, ab, bb)
+            rows = np.unique(np.r_[0:16, M - 16:M, rng.integers(0, M, 32)])
+            want = oracle.gemm_tn_f64(from_bits(ab[rows]), from_bits(bb))
+            assert oracle.rel_frobenius(d[rows], want) <= TIGHT_FRO
+            ri, ci = rng.integers(0, M, 4096), rng.integers(0, N, 4096)
+            spot = np.einsum("ik,ik->i", from_bits(ab[ri]).astype(np.float64), from_bits(bb[ci]).astype(np.float64))
+            assert np.abs(d[ri, ci] - spot).max() <= 1e-3 * np.abs(spot).max()
+            assert np.isfinite(d).all()
+
+
+def test_argument_checks(cuda, lib):
+    s = cuda.cuda.current_stream().cuda_stream
+    a = cuda.zeros((128, 64), dtype=cuda.bfloat16, device="cuda")
+    d = cuda.zeros((128, 128), dtype=cuda.float32, device="cuda")
+    assert lib.ko_gemm_bf16_f32(128, 128, 60, a.data_ptr(), a.data_ptr(), None, d.data_ptr(), s) == 3   # K % 8
+    assert lib.ko_gemm_bf16_f32(128, 128, 64, a.data_ptr() + 2, a.data_ptr(), None, d.data_ptr(), s) == 2  # alignment
+    assert lib.ko_gemm_bf16_f32(128, 128, 64, None, a.data_ptr(), None, d.data_ptr(), s) == 1
+    assert lib.ko_gemm_bf16_f32(0, 128, 64, None, None, None, None, s) == 0
