@@ -1,0 +1,412 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 operator set: one JSON line per run.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (default N=1)
+    python bench.py --impl reference --steps K --warmup W    # the CPU check path on the host cores
+    torchrun ... bench.py --gpus N ...                        # one rank per GPU, rows sharded, no collective
+
+Headline workload (`config.workload`): the two BERT-Base row operators the reference's README quotes,
+per GPU -- softmax FP32 [196608, 128] (logits N(0, 2^2), seed 0) followed by LayerNorm FP32
+[16384, 768] (x ~ N(0,1), gamma ~ U(0.5,1.5), beta ~ N(0,0.1^2), eps 1e-12, seed 1).  One step = one
+pass of both over one batch; with N GPUs the rows are sharded (N x the rows, weak scaling) and no data
+crosses between GPUs.  `value` = algorithmic bytes of all ranks per step / device time (max over
+ranks), inputs resident in HBM; every launch reads a buffer set that is not in L2 (the sets are
+rotated and together exceed the 126 MB L2 several times).  `e2e` is the same metric through the
+Tensor API with host buffers (pinned H2D before, D2H after, every step).
+
+The GEMMs of the operator set (SGEMM 1024^3; FP16/BF16 tcgen05 GEMM 4096^3 and 16384x3072x768) are
+timed in the same run next to cuBLAS and reported under "gemm"; the reference's own kernels recompiled
+for sm_100a are timed, when their test-only library is present, under "reference_kernels_on_b200".
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+SOFTMAX_ROWS, SOFTMAX_COLS = 196608, 128
+LN_ROWS, LN_COLS, LN_EPS = 16384, 768, 1e-12
+SOFTMAX_BYTES = 2 * SOFTMAX_ROWS * SOFTMAX_COLS * 4
+LN_BYTES = 2 * LN_ROWS * LN_COLS * 4 + 2 * LN_COLS * 4
+STEP_BYTES = SOFTMAX_BYTES + LN_BYTES
+METRIC, UNIT = "softmax+layernorm HBM throughput (BERT-Base row ops, FP32)", "GB/s"
+WORKLOAD = ("bert_base_row_ops: softmax f32 [196608,128] N(0,4) seed 0 + layernorm f32 [16384,768] affine eps 1e-12 "
+            "seed 1, per GPU; rows sharded across GPUs, no collective")
+# DRAM bytes per launch of the softmax kernel on this workload from the ncu capture summarised in
+# profiles/softmax_warp_kernel_196608x128.txt (dram__bytes_read.sum + dram__bytes_write.sum)
+SOFTMAX_NCU_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, 1590.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = int(get(self._h))
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.002)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU check path (the oracle's FP32 ports, all host threads): the reference arm and the cpu_baseline leg
+# --------------------------------------------------------------------------------------------------
+def cpu_port_step(oracle, xs, xl, g, b):
+    """One pass of the FP32 ports over the sample; returns seconds."""
+    t0 = time.perf_counter()
+    oracle.softmax_f32(xs)
+    oracle.layernorm_f32(xl, LN_EPS, g, b)
+    return time.perf_counter() - t0
+
+
+def cpu_sample(oracle, fraction: int):
+    rs, rl = SOFTMAX_ROWS // fraction, LN_ROWS // fraction
+    xs = oracle.fill_normal((rs, SOFTMAX_COLS), 0, 0, 0.0, 2.0)
+    xl = oracle.fill_normal((rl, LN_COLS), 1, 0, 0.0, 1.0)
+    g, b = oracle.fill_uniform((LN_COLS,), 1, 1, 0.5, 1.5), oracle.fill_normal((LN_COLS,), 1, 2, 0.0, 0.1)
+    sample_bytes = 2 * rs * SOFTMAX_COLS * 4 + 2 * rl * LN_COLS * 4 + 2 * LN_COLS * 4
+    return (xs, xl, g, b), sample_bytes, f"first 1/{fraction} of the rows of both operators ({rs} + {rl} rows), FP32 ports, every step"
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return  # the CPU arm runs on rank 0 only
+    from oracle import ko_oracle as oracle
+
+    cores = oracle.max_threads()
+    sample, sample_bytes, what = cpu_sample(oracle, 8)
+    for _ in range(max(args.warmup, 1)):
+        cpu_port_step(oracle, *sample)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_port_step(oracle, *sample)
+    elapsed = time.perf_counter() - t0
+    gbs = sample_bytes * args.steps / elapsed / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3 * (STEP_BYTES / sample_bytes),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic (seeded Philox4x32-10 fills of the BASELINE shapes)",
+        "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": what},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference project has no CPU implementation; this is the oracle's FP32 restatement of its kernels "
+                "(softmax.h:32-58, layernorm.h:13-50/:184-198 with the merge defect removed) on all host threads; "
+                "ms_per_step is scaled from the sample to the full per-GPU workload",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    import kernel_optimization_b200 as ko
+    from kernel_optimization_b200 import native
+
+    lib = native.lib()  # raises when the CUDA library has not been built: there is no fallback
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE is 1)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- inputs: this rank's row shard of the global tensors, seeded by global element index
+    hbm_peak, tc_peak, peak_kind = measured_peaks()
+    sm_off = rank * SOFTMAX_ROWS * SOFTMAX_COLS
+    ln_off = rank * LN_ROWS * LN_COLS
+    xs_host = ko.fill_normal((SOFTMAX_ROWS, SOFTMAX_COLS), 0, 0, 0.0, 2.0, elem_offset=sm_off)
+    xl_host = ko.fill_normal((LN_ROWS, LN_COLS), 1, 0, 0.0, 1.0, elem_offset=ln_off)
+    g_host, b_host = ko.fill_uniform((LN_COLS,), 1, 1, 0.5, 1.5), ko.fill_normal((LN_COLS,), 1, 2, 0.0, 0.1)
+    # default 4 x 201 MB and 8 x 101 MB of distinct addresses: nothing survives in the 126 MB L2
+    n_sm_sets, n_ln_sets = (args.row_sets, args.row_sets) if args.row_sets > 0 else (4, 8)
+    sm_in = [torch.from_numpy(xs_host).to(dev) for _ in range(n_sm_sets)]
+    sm_out = [torch.empty_like(sm_in[0]) for _ in range(n_sm_sets)]
+    ln_in = [torch.from_numpy(xl_host).to(dev) for _ in range(n_ln_sets)]
+    ln_out = [torch.empty_like(ln_in[0]) for _ in range(n_ln_sets)]
+    gamma, beta = torch.from_numpy(g_host).to(dev), torch.from_numpy(b_host).to(dev)
+
+    def softmax_launch(i):
+        j = i % n_sm_sets
+        native.check(lib.ko_softmax_f32(sm_in[j].data_ptr(), sm_out[j].data_ptr(), SOFTMAX_ROWS, SOFTMAX_COLS, stream()),
+                     "ko_softmax_f32")
+
+    def layernorm_launch(i):
+        j = i % n_ln_sets
+        native.check(lib.ko_layernorm_f32(ln_in[j].data_ptr(), ln_out[j].data_ptr(), LN_ROWS, LN_COLS, LN_EPS,
+                                          gamma.data_ptr(), beta.data_ptr(), 0, stream()), "ko_layernorm_f32")
+
+    def step(i):
+        softmax_launch(i)
+        layernorm_launch(i)
+
+    def timed(fn, iters, warm):
+        """ms per iteration on the device: barrier + synchronize on both sides, events on the launch stream."""
+        for i in range(warm):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)) / iters
+
+    # ---- headline: K steps of (softmax, layernorm)
+    with ClockSampler(local_rank) as clocks:
+        ms_per_step = timed(step, args.steps, args.warmup)
+        # per-kernel durations for the roofline, same buffers, same stream
+        ms_softmax = timed(softmax_launch, args.steps, args.warmup)
+        ms_layernorm = timed(layernorm_launch, args.steps, args.warmup)
+    value = STEP_BYTES * world / (ms_per_step * 1e-3) / 1e9
+    softmax_gbs = SOFTMAX_BYTES / (ms_softmax * 1e-3) / 1e9
+    layernorm_gbs = LN_BYTES / (ms_layernorm * 1e-3) / 1e9
+
+    # ---- parity spot check of what was just timed (rank 0; the oracle is only the checker here)
+    parity = None
+    if rank == 0:
+        from oracle import ko_oracle as oracle
+
+        pick = np.r_[0:256, SOFTMAX_ROWS - 256:SOFTMAX_ROWS]
+        y = sm_out[0][torch.from_numpy(pick).to(dev)].cpu().numpy()
+        parity = {"softmax_max_abs": oracle.max_abs_err(y, oracle.softmax_f64(xs_host[pick]))}
+        pick = np.r_[0:256, LN_ROWS - 256:LN_ROWS]
+        y = ln_out[0][torch.from_numpy(pick).to(dev)].cpu().numpy()
+        parity["layernorm_max_rel"] = oracle.max_rel_err(y, oracle.layernorm_f64(xl_host[pick], LN_EPS, g_host, b_host))
+
+    # ---- e2e: host buffers through the Tensor API, H2D + kernels + D2H inside the timed region
+    t_sm_in, t_sm_out = ko.Tensor(SOFTMAX_BYTES // 2, local_rank), ko.Tensor(SOFTMAX_BYTES // 2, local_rank)
+    t_ln_in, t_ln_out = ko.Tensor(LN_ROWS * LN_COLS * 4, local_rank), ko.Tensor(LN_ROWS * LN_COLS * 4, local_rank)
+    t_sm_in.host_ref(np.float32)[:] = xs_host.reshape(-1)
+    t_ln_in.host_ref(np.float32)[:] = xl_host.reshape(-1)
+
+    def e2e_step(_i):
+        s = stream()
+        t_sm_in.host_to_device_async(s)
+        t_ln_in.host_to_device_async(s)
+        native.check(lib.ko_softmax_f32(t_sm_in.device_ptr, t_sm_out.device_ptr, SOFTMAX_ROWS, SOFTMAX_COLS, s), "softmax")
+        native.check(lib.ko_layernorm_f32(t_ln_in.device_ptr, t_ln_out.device_ptr, LN_ROWS, LN_COLS, LN_EPS,
+                                          gamma.data_ptr(), beta.data_ptr(), 0, s), "layernorm")
+        t_sm_out.device_to_host_async(s)
+        t_ln_out.device_to_host_async(s)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    ms_e2e = timed(e2e_step, e2e_steps, 3)
+    h2d = SOFTMAX_BYTES // 2 + LN_ROWS * LN_COLS * 4
+    e2e = {"value": STEP_BYTES * world / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": h2d, "ms_per_step": ms_e2e, "steps": e2e_steps}
+    if rank == 0:
+        from oracle import ko_oracle as oracle
+
+        got = t_sm_out.host_ref(np.float32).reshape(SOFTMAX_ROWS, SOFTMAX_COLS)[:256]
+        parity["e2e_softmax_max_abs"] = oracle.max_abs_err(got, oracle.softmax_f64(xs_host[:256]))
+    del t_sm_in, t_sm_out, t_ln_in, t_ln_out, sm_in, sm_out, ln_in, ln_out
+
+    # ---- GEMMs next to cuBLAS (each rank its own M-block; B replicated by one NCCL broadcast, untimed)
+    gemm = {}
+    if not args.skip_gemm:
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+
+        def replicate(t):
+            if world > 1:
+                dist.broadcast(t, src=0)
+            return t
+
+        def bench_gemm(name, fn_ours, fn_cublas, flops, iters=20):
+            ms_o = timed(fn_ours, iters, 3)
+            ms_c = timed(fn_cublas, iters, 3)
+            gemm[name] = {"tflops": flops * world / (ms_o * 1e-3) / 1e12, "us": ms_o * 1e3,
+                          "cublas_tflops": flops * world / (ms_c * 1e-3) / 1e12, "cublas_us": ms_c * 1e3,
+                          "vs_cublas": ms_c / ms_o}
+
+        M = N = K = 1024
+        nset = 8
+        a_h, b_h = ko.fill_uniform((M, K), 2, 0, elem_offset=rank * M * K), ko.fill_uniform((K, N), 2, 1)
+        As = [torch.from_numpy(a_h).to(dev) for _ in range(nset)]
+        Bs = [replicate(torch.from_numpy(b_h).to(dev)) for _ in range(nset)]
+        Ds = [torch.empty((M, N), device=dev) for _ in range(nset)]
+        bench_gemm("sgemm_f32_1024",
+                   lambda i: native.check(lib.ko_sgemm_f32(M, N, K, As[i % nset].data_ptr(), Bs[i % nset].data_ptr(), None,
+                                                           Ds[i % nset].data_ptr(), stream()), "ko_sgemm_f32"),
+                   lambda i: torch.matmul(As[i % nset], Bs[i % nset], out=Ds[i % nset]), 2.0 * M * N * K, iters=50)
+        gemm["sgemm_f32_1024"]["cublas_math"] = "cublasSgemm via torch.matmul, TF32 disabled (FFMA)"
+        del As, Bs, Ds
+        for kind, tdt, code, fn in (("bf16", torch.bfloat16, 2, lib.ko_gemm_bf16_f32), ("f16", torch.float16, 1, lib.ko_gemm_f16_f32)):
+            for tag, (M, N, K) in (("4096", (4096, 4096, 4096)), ("ffn_16384x3072x768", (16384, 3072, 768))):
+                nset = 3
+                a_h = ko.fill_uniform((M, K), 3, 0, dtype=code, elem_offset=rank * M * K)
+                b_h = ko.fill_uniform((N, K), 3, 1, dtype=code)
+                As = [torch.from_numpy(a_h.view(np.int16)).to(dev).view(tdt) for _ in range(nset)]
+                Bs = [replicate(torch.from_numpy(b_h.view(np.int16)).to(dev).view(tdt)) for _ in range(nset)]
+                Ds = [torch.empty((M, N), device=dev) for _ in range(nset)]
+                bench_gemm(f"gemm_{kind}_f32_{tag}",
+                           lambda i: native.check(fn(M, N, K, As[i % nset].data_ptr(), Bs[i % nset].data_ptr(), None,
+                                                     Ds[i % nset].data_ptr(), stream()), "ko_gemm_tc"),
+                           lambda i: torch.mm(As[i % nset], Bs[i % nset].t(), out_dtype=torch.float32), 2.0 * M * N * K)
+                gemm[f"gemm_{kind}_f32_{tag}"]["of_measured_bf16_peak"] = gemm[f"gemm_{kind}_f32_{tag}"]["tflops"] / world / tc_peak
+                del As, Bs, Ds
+        torch.cuda.synchronize()
+        native.check(lib.ko_poll_device_status(), "ko_poll_device_status")
+
+    # ---- the reference's own kernels, recompiled for sm_100a (test-only library; informational)
+    ref_rows = None
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libko_ref_kernels.so")
+    if rank == 0 and world == 1 and os.path.exists(ref_path) and not args.skip_gemm:
+        ref = C.CDLL(ref_path)
+        vp, ll, ci, f32 = C.c_void_p, C.c_longlong, C.c_int, C.c_float
+        ref.ko_ref_softmax_f32.argtypes = [vp, vp, ll, ci, vp]
+        ref.ko_ref_layernorm_f32.argtypes = [vp, vp, ll, ci, f32, vp, vp, ci, vp]
+        xs = [torch.from_numpy(xs_host).to(dev) for _ in range(4)]
+        ys = [torch.empty_like(xs[0]) for _ in range(4)]
+        ms = timed(lambda i: ref.ko_ref_softmax_f32(xs[i % 4].data_ptr(), ys[i % 4].data_ptr(), SOFTMAX_ROWS, SOFTMAX_COLS, stream()), 30, 3)
+        ref_rows = {"softmax_gbs": SOFTMAX_BYTES / (ms * 1e-3) / 1e9}
+        del xs, ys
+        xl = [torch.from_numpy(xl_host).to(dev) for _ in range(8)]
+        yl = [torch.empty_like(xl[0]) for _ in range(8)]
+        ms = timed(lambda i: ref.ko_ref_layernorm_f32(xl[i % 8].data_ptr(), yl[i % 8].data_ptr(), LN_ROWS, LN_COLS, 1e-4, None, None, 0, stream()), 30, 3)
+        ref_rows["layernorm_gbs"] = LN_BYTES / (ms * 1e-3) / 1e9
+        ref_rows["note"] = "SoftMaxWarpImpl / LayerNormWarpImpl at the reference driver's launch geometry; the LayerNorm result is not LayerNorm (see DESIGN.md)"
+        del xl, yl
+
+    # ---- CPU baseline beside it (rank 0, single-GPU runs only)
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        from oracle import ko_oracle as oracle
+
+        sample, sample_bytes, what = cpu_sample(oracle, 1)
+        cpu_port_step(oracle, *sample)
+        reps = 5
+        best = min(cpu_port_step(oracle, *sample) for _ in range(reps))
+        cpu_baseline = {"value": sample_bytes / best / 1e9, "unit": UNIT, "cores": oracle.max_threads(), "kind": "port",
+                        "sample": f"the full per-GPU workload (all rows of both operators), FP32 ports, best of {reps} passes"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic (seeded Philox4x32-10 fills of the BASELINE shapes and distributions; no dataset involved)",
+            "config": {"workload": WORKLOAD, "rows_per_gpu": {"softmax": SOFTMAX_ROWS, "layernorm": LN_ROWS},
+                       "l2": f"inputs and outputs rotate over {n_sm_sets} (softmax) / {n_ln_sets} (layernorm) buffer sets "
+                             f"({n_sm_sets * SOFTMAX_BYTES / 1e6:.0f} / {n_ln_sets * LN_BYTES / 1e6:.0f} MB of distinct addresses "
+                             "against a 126 MB L2), so every launch reads from HBM",
+                       "parallelism": f"rows x{world}, no collective"},
+            "roofline": {"bound": "hbm", "kernel": "softmax_warp_kernel (softmax f32 [196608,128])", "achieved": softmax_gbs,
+                         "peak": hbm_peak, "unit": "GB/s", "frac": softmax_gbs / hbm_peak, "traffic": SOFTMAX_NCU_TRAFFIC_BYTES,
+                         "peak_source": peak_kind, "algorithmic_bytes_per_launch": SOFTMAX_BYTES, "us_per_launch": ms_softmax * 1e3},
+            "ops": {"softmax": {"gbs": softmax_gbs, "us": ms_softmax * 1e3, "of_peak": softmax_gbs / hbm_peak, "of_nominal_8TBs": softmax_gbs / 8000.0},
+                    "layernorm": {"gbs": layernorm_gbs, "us": ms_layernorm * 1e3, "of_peak": layernorm_gbs / hbm_peak, "of_nominal_8TBs": layernorm_gbs / 8000.0}},
+            "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks.summary(),
+            "parity": parity, "gemm": gemm, "reference_kernels_on_b200": ref_rows,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--skip-gemm", action="store_true", help="row operators only")
+    ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    ap.add_argument("--row-sets", type=int, default=0,
+                    help="buffer sets to rotate over (0 = default 4/8); 1 keeps a profiler capture small")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

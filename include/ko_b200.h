@@ -40,6 +40,11 @@ const char *ko_status_string(int status);
 const char *ko_last_error_string(void);
 /* major*10000 + minor*100 + patch */
 int ko_version(void);
+/* Kernels built on mbarrier / tcgen05 pipelines bound every device-side wait; one that runs out
+ * records a code in a device status word instead of hanging.  This call waits for the device's
+ * outstanding work, returns KO_ERR_TIMEOUT (and clears the words) if any kernel gave up since the
+ * last poll, KO_OK otherwise.  No counterpart in the reference, whose kernels never wait. */
+int ko_poll_device_status(void);
 
 /* ------------------------------------------------------------------------------------------
  * Tensor: paired host (pinned) + device byte buffer.

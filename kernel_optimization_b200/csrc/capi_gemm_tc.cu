@@ -11,10 +11,6 @@
 
 namespace {
 
-// Bounded device-side waits report here (first failure wins); read and cleared by
-// ko_gemm_tc_poll_status().
-__device__ unsigned int g_tc_status_word;
-
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -116,9 +112,7 @@ int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A
     ko::tc::GemmParams p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.C = C; p.D = D; p.fmt = fmt;
-    void *status_ptr = nullptr;
-    KO_CUDA(cudaGetSymbolAddress(&status_ptr, g_tc_status_word));
-    p.status = static_cast<unsigned *>(status_ptr);
+    if (int st = ko::device_status_word(0, &p.status)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (bn) {
         case 64: return launch<64>(map_a, map_b, p, info.sm_count, s);
@@ -135,16 +129,6 @@ int ko_gemm_f16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const ui
 int ko_gemm_bf16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C, float *D,
                      void *stream) {
     return ko_gemm_tc_tuned(1, M, N, K, A, B, C, D, 0, stream);
-}
-
-int ko_gemm_tc_poll_status(void) {
-    unsigned int word = 0;
-    KO_CUDA(cudaMemcpyFromSymbol(&word, g_tc_status_word, sizeof word));
-    if (word == 0) return KO_OK;
-    const unsigned int zero = 0;
-    KO_CUDA(cudaMemcpyToSymbol(g_tc_status_word, &zero, sizeof zero));
-    static const char *who[] = {"", "the TMA producer", "the MMA issuer", "an epilogue warp", "the tensor-memory drain"};
-    return ko::fail(KO_ERR_TIMEOUT, "tensor-core GEMM: a bounded wait ran out in %s", word < 5 ? who[word] : "an unknown role");
 }
 
 }  // extern "C"

@@ -1,6 +1,5 @@
 // C-ABI launcher of the row softmax: picks the tier and the launch geometry from the runtime shape.
-#include "ko_internal.h"
-#include "ko_tuning.h"
+#include "row_launch.h"
 
 #include "../nn_operators/softmax/softmax.h"
 
@@ -8,89 +7,124 @@ namespace {
 
 using ko::DeviceInfo;
 
-template <int kVecs, int kRows>
-int launch_warp(const float *in, float *out, long long rows, int cols, int block, long long grid_cap,
-                cudaStream_t s) {
-    const int warps_per_block = block / 32;
-    const long long groups = (rows + kRows - 1) / kRows;
-    long long grid = (groups + warps_per_block - 1) / warps_per_block;
-    if (grid_cap > 0 && grid > grid_cap) grid = grid_cap;
-    if (grid > 0x7fffffffLL) grid = 0x7fffffffLL;
-    ko::softmax_warp_kernel<kVecs, kRows><<<(unsigned)grid, block, 0, s>>>(in, out, rows, cols);
+template <int kVecs, int kSlots, int G>
+int launch_warp(const float *in, float *out, long long rows, int cols, const ko_row_knobs_t &k, cudaStream_t s) {
+    constexpr int kRowsPerStep = kSlots * (32 / G);
+    const int block = (k.block > 0 && k.block <= 256) ? k.block : 256;
+    const long long groups = (rows + kRowsPerStep - 1) / kRowsPerStep;
+    const unsigned grid = ko::clamp_grid((groups + block / 32 - 1) / (block / 32), k.grid_cap);
+    ko::softmax_warp_kernel<kVecs, kSlots, G><<<grid, block, 0, s>>>(in, out, rows, cols);
     KO_CHECK_LAUNCH("softmax_warp_kernel");
+    return KO_OK;
+}
+
+template <int kVecs, int kSlots, int G>
+int launch_staged(const float *in, float *out, long long rows, int cols, const ko_row_knobs_t &k,
+                  const DeviceInfo &info, cudaStream_t s, bool *used) {
+    constexpr int W = ko::kStagedConsumerWarps;
+    const ko::StagedPlan plan = ko::plan_staged(rows, (unsigned)cols * 4u, kSlots * (32 / G), k, info);
+    *used = plan.ok;
+    if (!plan.ok) return KO_OK;
+    unsigned *status = nullptr;
+    if (int st = ko::device_status_word(1, &status)) return st;
+    auto kernel = ko::softmax_staged_kernel<kVecs, kSlots, G, W>;
+    if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), plan.smem_bytes)) return st;
+    kernel<<<plan.grid, ko::kStagedThreads, plan.smem_bytes, s>>>(in, out, rows, cols, plan.geo, status);
+    KO_CHECK_LAUNCH("softmax_staged_kernel");
     return KO_OK;
 }
 
 template <int kVecs, int kThreads>
 int launch_block(const float *in, float *out, long long rows, int cols, long long grid_cap, cudaStream_t s) {
-    long long grid = rows;
-    if (grid_cap > 0 && grid > grid_cap) grid = grid_cap;
-    if (grid > 0x7fffffffLL) grid = 0x7fffffffLL;
-    ko::softmax_block_kernel<kVecs, kThreads><<<(unsigned)grid, kThreads, 0, s>>>(in, out, rows, cols);
+    ko::softmax_block_kernel<kVecs, kThreads><<<ko::clamp_grid(rows, grid_cap), kThreads, 0, s>>>(in, out, rows, cols);
     KO_CHECK_LAUNCH("softmax_block_kernel");
     return KO_OK;
 }
 
-int validate(const float *in, float *out, long long rows, int cols) {
-    KO_REQUIRE(rows >= 0 && cols >= 0, KO_ERR_INVALID_ARG, "softmax: negative shape [%lld, %d]", rows, cols);
-    if (rows == 0 || cols == 0) return KO_OK;
-    KO_REQUIRE(in != nullptr && out != nullptr, KO_ERR_INVALID_ARG, "softmax: NULL pointer");
-    return KO_OK;
+// lanes per row and vectors per lane depend on the column count only; `slots` (rows a warp handles
+// together = slots * 32/G) is the tunable
+template <bool kStaged>
+int dispatch_rows(int nvec, int slots, const float *in, float *out, long long rows, int cols, const ko_row_knobs_t &k,
+                  const DeviceInfo &info, cudaStream_t s, bool *used) {
+#define KO_GO(V, R, G)                                                                       \
+    do {                                                                                     \
+        if constexpr (kStaged) return launch_staged<V, R, G>(in, out, rows, cols, k, info, s, used); \
+        else { *used = true; return launch_warp<V, R, G>(in, out, rows, cols, k, s); }       \
+    } while (0)
+#define KO_SLOTS(V, G, DEF)                          \
+    do {                                             \
+        const int want = slots > 0 ? slots : (DEF);  \
+        if (want <= 1) KO_GO(V, 1, G);               \
+        if (want == 2) KO_GO(V, 2, G);               \
+        KO_GO(V, 4, G);                              \
+    } while (0)
+    if (nvec <= 8) KO_SLOTS(1, 8, 4);
+    if (nvec <= 16) KO_SLOTS(2, 8, 2);
+    if (nvec <= 32) KO_SLOTS(4, 8, 2);
+    if (nvec <= 64) KO_SLOTS(4, 16, 2);
+    if (nvec <= 128) KO_SLOTS(4, 32, 2);
+    if (nvec <= 192) { if (slots == 2) KO_GO(6, 2, 32); KO_GO(6, 1, 32); }
+    if (nvec <= 256) { if (slots == 2) KO_GO(8, 2, 32); KO_GO(8, 1, 32); }
+    if (nvec <= 384) KO_GO(12, 1, 32);
+    KO_GO(16, 1, 32);
+#undef KO_SLOTS
+#undef KO_GO
 }
 
 }  // namespace
 
 extern "C" {
 
-int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols, int rows_per_warp, int block,
-                         int64_t grid_cap, void *stream) {
-    if (int st = validate(in, out, rows, cols)) return st;
+int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols, const ko_row_knobs_t *knobs,
+                         void *stream) {
+    KO_REQUIRE(rows >= 0 && cols >= 0, KO_ERR_INVALID_ARG, "softmax: negative shape [%lld, %d]", (long long)rows, cols);
     if (rows == 0 || cols == 0) return KO_OK;
+    KO_REQUIRE(in != nullptr && out != nullptr, KO_ERR_INVALID_ARG, "softmax: NULL pointer");
+    const ko_row_knobs_t k = knobs ? *knobs : ko_row_knobs_t{};
+    KO_REQUIRE(k.tier >= 0 && k.tier <= 4, KO_ERR_INVALID_ARG, "softmax: unknown tier %d", k.tier);
+    KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
+               "softmax: block %d must be a multiple of 32, <= 1024", k.block);
     DeviceInfo info;
     if (int st = ko::current_device_info(&info)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool vec_ok = (cols % 4 == 0) && ko::aligned16(in) && ko::aligned16(out);
     const int nvec = cols / 4;
-    if (block <= 0) block = 256;
-    KO_REQUIRE(block % 32 == 0 && block <= 256, KO_ERR_INVALID_ARG, "softmax: block %d must be a multiple of 32, <= 256", block);
 
-    if (vec_ok && nvec <= 32 * 16) {
-        const int vecs = (nvec + 31) / 32;
-#define KO_WARP(V, R) return launch_warp<V, R>(in, out, rows, cols, block, grid_cap, s)
-        if (vecs == 1) {
-            switch (rows_per_warp) { case 1: KO_WARP(1, 1); case 2: KO_WARP(1, 2); case 8: KO_WARP(1, 8); default: KO_WARP(1, 4); }
-        } else if (vecs == 2) {
-            switch (rows_per_warp) { case 1: KO_WARP(2, 1); case 4: KO_WARP(2, 4); default: KO_WARP(2, 2); }
-        } else if (vecs <= 4) {
-            switch (rows_per_warp) { case 1: KO_WARP(4, 1); case 4: KO_WARP(4, 4); default: KO_WARP(4, 2); }
-        } else if (vecs <= 6) {
-            switch (rows_per_warp) { case 2: KO_WARP(6, 2); default: KO_WARP(6, 1); }
-        } else if (vecs <= 8) {
-            switch (rows_per_warp) { case 2: KO_WARP(8, 2); default: KO_WARP(8, 1); }
-        } else if (vecs <= 12) {
-            KO_WARP(12, 1);
-        } else {
-            KO_WARP(16, 1);
-        }
-#undef KO_WARP
+    int tier = k.tier;
+    if (tier == 0) {
+        if (!vec_ok) tier = 3;
+        else if (nvec <= 32 * 16) tier = 1;  // measured faster than the staged tier at every BASELINE shape
+        else if (nvec <= 1024 * 8) tier = 2;
+        else tier = 3;
     }
-    if (vec_ok && nvec <= 1024 * 8) {
-        // one row per block, <= 8 vectors per thread
-        if (nvec <= 256 * 4) return launch_block<4, 256>(in, out, rows, cols, grid_cap, s);
-        if (nvec <= 512 * 4) return launch_block<4, 512>(in, out, rows, cols, grid_cap, s);
-        if (nvec <= 1024 * 4) return launch_block<4, 1024>(in, out, rows, cols, grid_cap, s);
-        return launch_block<8, 1024>(in, out, rows, cols, grid_cap, s);
+    if (tier == 4) {
+        KO_REQUIRE(vec_ok && nvec <= 32 * 16, KO_ERR_SHAPE, "softmax: the staged tier needs cols %% 4 == 0, cols <= 2048 and 16-byte aligned pointers");
+        bool used = false;
+        if (int st = dispatch_rows<true>(nvec, k.rows_per_warp, in, out, rows, cols, k, info, s, &used)) return st;
+        if (used) return KO_OK;
+        KO_REQUIRE(k.tier == 0, KO_ERR_SHAPE, "softmax: the requested staged geometry does not fit in shared memory");
+        tier = 1;
     }
-    long long grid = rows;
-    const long long cap = grid_cap > 0 ? grid_cap : (long long)info.sm_count * 8;
-    if (grid > cap) grid = cap;
-    ko::softmax_stream_kernel<<<(unsigned)grid, 256, 0, s>>>(in, out, rows, cols);
+    if (tier == 1) {
+        KO_REQUIRE(vec_ok && nvec <= 32 * 16, KO_ERR_SHAPE, "softmax: the warp tier needs cols %% 4 == 0, cols <= 2048 and 16-byte aligned pointers");
+        bool used = false;
+        return dispatch_rows<false>(nvec, k.rows_per_warp, in, out, rows, cols, k, info, s, &used);
+    }
+    if (tier == 2) {
+        KO_REQUIRE(vec_ok && nvec <= 1024 * 8, KO_ERR_SHAPE, "softmax: the block tier needs cols %% 4 == 0, cols <= 32768 and 16-byte aligned pointers");
+        if (nvec <= 256 * 4) return launch_block<4, 256>(in, out, rows, cols, k.grid_cap, s);
+        if (nvec <= 512 * 4) return launch_block<4, 512>(in, out, rows, cols, k.grid_cap, s);
+        if (nvec <= 1024 * 4) return launch_block<4, 1024>(in, out, rows, cols, k.grid_cap, s);
+        return launch_block<8, 1024>(in, out, rows, cols, k.grid_cap, s);
+    }
+    const long long cap = k.grid_cap > 0 ? k.grid_cap : (long long)info.sm_count * 8;
+    ko::softmax_stream_kernel<<<ko::clamp_grid(rows, cap), 256, 0, s>>>(in, out, rows, cols);
     KO_CHECK_LAUNCH("softmax_stream_kernel");
     return KO_OK;
 }
 
 int ko_softmax_f32(const float *in, float *out, int64_t rows, int32_t cols, void *stream) {
-    return ko_softmax_f32_tuned(in, out, rows, cols, /*rows_per_warp=*/0, /*block=*/0, /*grid_cap=*/0, stream);
+    return ko_softmax_f32_tuned(in, out, rows, cols, nullptr, stream);
 }
 
 }  // extern "C"

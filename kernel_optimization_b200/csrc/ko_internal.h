@@ -25,6 +25,10 @@ struct DeviceInfo {
 // properties of the current device (cached per device ordinal); status != KO_OK on failure
 int current_device_info(DeviceInfo *out);
 
+// device status words (device_status.cu): 0 = tensor-core GEMM, 1 = staged row operators
+constexpr int kStatusWordCount = 4;
+int device_status_word(int which, unsigned int **out);
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace ko

@@ -49,6 +49,27 @@ int current_device_info(DeviceInfo *out) {
 }
 }  // namespace ko
 
+#include <map>
+#include <utility>
+
+#include "row_launch.h"
+
+namespace ko {
+int ensure_dynamic_smem(const void *kernel, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, size_t> configured;
+    int dev = 0;
+    KO_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &have = configured[{kernel, dev}];
+    if (bytes > have) {
+        KO_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        have = bytes;
+    }
+    return KO_OK;
+}
+}  // namespace ko
+
 extern "C" {
 
 const char *ko_status_string(int status) {

@@ -1,6 +1,6 @@
-// Launch-geometry overrides of the operator entry points (same semantics as the public calls;
-// 0 selects the library's default for that knob).  Used by the sweep tooling and the tests that
-// pin every instantiated variant; applications call the plain entry points of ko_b200.h.
+// Launch-geometry overrides of the operator entry points (same semantics as the public calls of
+// ko_b200.h; a zero knob selects the library's default).  Used by the sweep tooling and by the tests
+// that pin every instantiated variant; applications call the plain entry points.
 #pragma once
 
 #include <stdint.h>
@@ -9,15 +9,26 @@
 extern "C" {
 #endif
 
-int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols, int rows_per_warp, int block,
-                         int64_t grid_cap, void *stream);
-/* block: warp tier -> threads per block (<= 256); block tier -> threads per row (128..1024) */
+/* knobs of the row operators; pass NULL for all defaults */
+typedef struct ko_row_knobs {
+    int tier;            /* 0 = choose, 1 = warp, 2 = block, 3 = stream (scalar), 4 = staged (TMA ring) */
+    int rows_per_warp;   /* warp / staged tier: independent row slots a warp processes together (a slot is
+                            one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows) */
+    int block;           /* warp tier: threads per block (<= 256); block tier: threads per row (128..1024) */
+    int64_t grid_cap;    /* warp / block / stream tier: upper bound on the grid (0 = one pass per warp) */
+    int stage_rows;      /* staged tier: rows per bulk copy (0 = about 16-32 KB) */
+    int stages;          /* staged tier: ring depth (0 = fill about 100 KB) */
+    int ctas_per_sm;     /* staged tier: persistent blocks per SM (0 = 1) */
+} ko_row_knobs_t;
+
+int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols, const ko_row_knobs_t *knobs,
+                         void *stream);
 int ko_layernorm_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols, float eps, const float *gamma,
-                           const float *beta, int ddof, int rows_per_warp, int block, int64_t grid_cap, void *stream);
+                           const float *beta, int ddof, const ko_row_knobs_t *knobs, void *stream);
 int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps,
-                            const uint16_t *gamma, const uint16_t *beta, int ddof, int rows_per_warp, int block,
-                            int64_t grid_cap, void *stream);
-/* variant: 0 = choose, 1 = 128x128 tiles, 2 = 128x64, 3 = 64x64 */
+                            const uint16_t *gamma, const uint16_t *beta, int ddof, const ko_row_knobs_t *knobs,
+                            void *stream);
+/* variant: 0 = choose, otherwise a tile configuration index (see capi_sgemm.cu) */
 int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
                        int variant, void *stream);
 /* fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns of D per tile */

@@ -29,6 +29,7 @@ PROTOTYPES = {
     "ko_status_string": (C.c_char_p, [_int]),
     "ko_last_error_string": (C.c_char_p, []),
     "ko_version": (_int, []),
+    "ko_poll_device_status": (_int, []),
     "ko_tensor_create": (_int, [_sz, _int, C.POINTER(_vp)]),
     "ko_tensor_destroy": (_int, [_vp]),
     "ko_tensor_host_ptr": (_vp, [_vp]),
@@ -54,14 +55,22 @@ PROTOTYPES = {
     "ko_gemm_bf16_f32": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
 }
 
-# launch-geometry overrides (csrc/ko_tuning.h); optional, bound when exported
+class RowKnobs(C.Structure):
+    """ko_row_knobs_t of csrc/ko_tuning.h: launch-geometry overrides of the row operators (0 = default)."""
+
+    _fields_ = [("tier", _int), ("rows_per_warp", _int), ("block", _int), ("grid_cap", _i64), ("stage_rows", _int),
+                ("stages", _int), ("ctas_per_sm", _int)]
+
+
+_knobs_p = C.POINTER(RowKnobs)
+
+# launch-geometry overrides (csrc/ko_tuning.h); bound when exported
 TUNING_PROTOTYPES = {
-    "ko_softmax_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _int, _int, _i64, _vp]),
-    "ko_layernorm_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _int, _int, _i64, _vp]),
-    "ko_layernorm_bf16_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _int, _int, _i64, _vp]),
+    "ko_softmax_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _knobs_p, _vp]),
+    "ko_layernorm_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),
+    "ko_layernorm_bf16_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),
     "ko_sgemm_f32_tuned": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),
     "ko_gemm_tc_tuned": (_int, [_int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),
-    "ko_gemm_tc_poll_status": (_int, []),
 }
 
 _lib = None

@@ -38,7 +38,6 @@ constexpr int kBM = 128;          // rows of D per tile = TMEM lanes
 constexpr int kBK = 64;           // K elements per stage: 64 * 2 B = one 128-byte swizzle row
 constexpr int kUmmaK = 16;        // K per tcgen05.mma for 16-bit inputs
 constexpr int kThreads = 192;     // 6 warps: producer, MMA, 4 x epilogue
-constexpr uint32_t kSpinLimit = 1u << 24;
 
 // codes written to the status word (first failure wins)
 enum : unsigned { kStatusOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3, kTimeoutDrain = 4 };
@@ -60,41 +59,6 @@ struct TileConfig {
 // ------------------------------------------------------------------------------------------------
 // thin PTX wrappers
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit ran out or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 1023u) == 1023u && *abort_flag) return false;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void fence_barrier_init() {
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

@@ -9,6 +9,9 @@
 //
 // Tiers by row length (the reference's warp / block-cached / block-no-cache split,
 // nn_operators/layernorm/layernorm.h:145-201, :204-252, :254-300):
+//   staged tier  persistent blocks, a producer warp streams chunks of rows into a shared-memory ring
+//                with 1-D bulk copies (TMA), consumer warps work out of shared memory
+//                (common/row_pipeline.h);
 //   warp tier    one warp owns kRows consecutive rows per step, rows in registers;
 //   block tier   one thread block per row, row in registers, one shared-memory exchange;
 //   stream tier  one thread block per row, two passes over global memory, scalar accesses, any
@@ -21,6 +24,7 @@
 
 #include "../../common/common.h"
 #include "../../common/functors.h"
+#include "../../common/row_pipeline.h"
 
 namespace ko {
 
@@ -55,20 +59,37 @@ struct RowIo<__nv_bfloat16> {
     __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
 };
 
-// exact (count, mean, M2) of kCount values held in registers; `valid` masks trailing vectors
-template <int kCount>
-__device__ __forceinline__ Welford welford_of_registers(const float (&v)[kCount], int valid_count) {
+// exact (count, mean, M2) of the valid_vecs * kPerVec values a thread holds as raw 16-byte vectors:
+// mean first, then the squared deviations from it (both passes run over registers)
+template <typename T, int kVecs>
+__device__ __forceinline__ Welford welford_of_vectors(const typename RowIo<T>::Raw (&raw)[kVecs], int valid_vecs) {
+    using Io = RowIo<T>;
+    constexpr int kPer = Io::kPerVec;
     float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < kCount; ++i) sum += i < valid_count ? v[i] : 0.f;
+    for (int j = 0; j < kVecs; ++j) {
+        float f[kPer];
+        Io::unpack(raw[j], f);
+        float part = 0.f;
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) part += f[e];
+        sum += j < valid_vecs ? part : 0.f;
+    }
     Welford w;
-    w.n = (float)valid_count;
-    w.mean = valid_count > 0 ? sum / w.n : 0.f;
+    w.n = (float)(valid_vecs * kPer);
+    w.mean = valid_vecs > 0 ? sum / w.n : 0.f;
     float m2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < kCount; ++i) {
-        const float d = v[i] - w.mean;
-        m2 = i < valid_count ? fmaf(d, d, m2) : m2;
+    for (int j = 0; j < kVecs; ++j) {
+        float f[kPer];
+        Io::unpack(raw[j], f);
+        float part = 0.f;
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) {
+            const float d = f[e] - w.mean;
+            part = fmaf(d, d, part);
+        }
+        m2 += j < valid_vecs ? part : 0.f;
     }
     w.m2 = m2;
     return w;
@@ -80,80 +101,124 @@ __device__ __forceinline__ float rstd_from(const Welford &w, int cols, int ddof,
     return rsqrtf(var + eps);
 }
 
+// normalise one raw vector: ((x - mean) * rstd) * gamma + beta
+template <typename T>
+__device__ __forceinline__ typename RowIo<T>::Raw normalise_vector(const typename RowIo<T>::Raw &raw, float mean, float rstd,
+                                                                  const typename RowIo<T>::Raw *gamma_v,
+                                                                  const typename RowIo<T>::Raw *beta_v, int v) {
+    using Io = RowIo<T>;
+    constexpr int kPer = Io::kPerVec;
+    float f[kPer], g[kPer], b[kPer], y[kPer];
+    Io::unpack(raw, f);
+#pragma unroll
+    for (int e = 0; e < kPer; ++e) { g[e] = 1.f; b[e] = 0.f; }
+    if (gamma_v) Io::unpack(__ldg(gamma_v + v), g);
+    if (beta_v) Io::unpack(__ldg(beta_v + v), b);
+#pragma unroll
+    for (int e = 0; e < kPer; ++e) y[e] = fmaf((f[e] - mean) * rstd, g[e], b[e]);
+    return Io::pack(y);
+}
+
+// kRows rows spread over the warp (kVecs raw vectors per lane each): statistics, then the
+// normalised rows are written to out_v at rows row0 .. row0+kRows-1 (rows >= row_limit are skipped)
+template <typename T, int kVecs, int kRows>
+__device__ __forceinline__ void layernorm_rows_from_registers(const typename RowIo<T>::Raw (&raw)[kRows][kVecs], int my_vecs,
+                                                              int nvec, int lane, long long row0, long long row_limit,
+                                                              typename RowIo<T>::Raw *out_v, int cols, float eps,
+                                                              const typename RowIo<T>::Raw *gamma_v,
+                                                              const typename RowIo<T>::Raw *beta_v, int ddof) {
+    Welford stats[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) stats[r] = welford_of_vectors<T, kVecs>(raw[r], my_vecs);
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) stats[r] = warp_allreduce_welford(stats[r]);
+    float mean[kRows], rstd[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        mean[r] = stats[r].mean;
+        rstd[r] = rstd_from(stats[r], cols, ddof, eps);
+    }
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) {
+        const int v = lane + 32 * j;
+        if (v >= nvec) continue;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            if (row0 + r >= row_limit) continue;
+            st_stream(out_v + (row0 + r) * nvec + v, normalise_vector<T>(raw[r][j], mean[r], rstd[r], gamma_v, beta_v, v));
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // warp tier: kVecs 16-byte vectors per lane per row, kRows rows per warp step
 // ---------------------------------------------------------------------------------------------
 template <typename T, int kVecs, int kRows>
 __device__ __forceinline__ void layernorm_warp_tier(const T *in, T *out, long long rows, int cols, float eps,
                                                     const T *gamma, const T *beta, int ddof) {
-    using Io = RowIo<T>;
-    using Raw = typename Io::Raw;
-    constexpr int kPer = Io::kPerVec;
+    using Raw = typename RowIo<T>::Raw;
     const int lane = threadIdx.x & 31;
-    const int nvec = cols / kPer;
+    const int nvec = cols / RowIo<T>::kPerVec;
     const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
     const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const Raw *in_v = reinterpret_cast<const Raw *>(in);
-    Raw *out_v = reinterpret_cast<Raw *>(out);
-    const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma);
-    const Raw *beta_v = reinterpret_cast<const Raw *>(beta);
-
     // vectors this lane owns in a row: lane, lane+32, ...
     int my_vecs = 0;
 #pragma unroll
     for (int j = 0; j < kVecs; ++j) my_vecs += (lane + 32 * j < nvec) ? 1 : 0;
 
     for (long long row0 = warp_global * kRows; row0 < rows; row0 += warps_per_grid * kRows) {
-        float x[kRows][kVecs * kPer];
+        Raw raw[kRows][kVecs];
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            const bool row_ok = row0 + r < rows;
-            Raw raw[kVecs];
 #pragma unroll
             for (int j = 0; j < kVecs; ++j) {
                 const int v = lane + 32 * j;
-                if (row_ok && v < nvec) raw[j] = ld_stream(in_v + (row0 + r) * nvec + v);
-                else raw[j] = Raw{};
-            }
-#pragma unroll
-            for (int j = 0; j < kVecs; ++j) {
-                float f[kPer];
-                Io::unpack(raw[j], f);
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) x[r][j * kPer + e] = f[e];
+                if (row0 + r < rows && v < nvec) raw[r][j] = ld_stream(in_v + (row0 + r) * nvec + v);
+                else raw[r][j] = Raw{};
             }
         }
-        Welford stats[kRows];
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) stats[r] = welford_of_registers<kVecs * kPer>(x[r], my_vecs * kPer);
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) stats[r] = warp_allreduce_welford(stats[r]);
-
-        float mean[kRows], rstd[kRows];
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            mean[r] = stats[r].mean;
-            rstd[r] = rstd_from(stats[r], cols, ddof, eps);
-        }
-#pragma unroll
-        for (int j = 0; j < kVecs; ++j) {
-            const int v = lane + 32 * j;
-            if (v >= nvec) continue;
-            float g[kPer], b[kPer];
-#pragma unroll
-            for (int e = 0; e < kPer; ++e) { g[e] = 1.f; b[e] = 0.f; }
-            if (gamma) Io::unpack(__ldg(gamma_v + v), g);
-            if (beta) Io::unpack(__ldg(beta_v + v), b);
-#pragma unroll
-            for (int r = 0; r < kRows; ++r) {
-                if (row0 + r >= rows) continue;
-                float y[kPer];
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) y[e] = fmaf((x[r][j * kPer + e] - mean[r]) * rstd[r], g[e], b[e]);
-                st_stream(out_v + (row0 + r) * nvec + v, Io::pack(y));
-            }
-        }
+        layernorm_rows_from_registers<T, kVecs, kRows>(raw, my_vecs, nvec, lane, row0, rows, reinterpret_cast<Raw *>(out),
+                                                       cols, eps, reinterpret_cast<const Raw *>(gamma),
+                                                       reinterpret_cast<const Raw *>(beta), ddof);
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// staged tier: consumer side of the row pipeline (common/row_pipeline.h)
+// ---------------------------------------------------------------------------------------------
+template <typename T, int kVecs, int kRows, int kConsumerWarps>
+__device__ __forceinline__ void layernorm_staged_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                      const T *gamma, const T *beta, int ddof, const RowPipeGeometry geo,
+                                                      uint8_t *smem, unsigned *status) {
+    using Raw = typename RowIo<T>::Raw;
+    const int nvec = cols / RowIo<T>::kPerVec;
+    row_pipeline<kConsumerWarps>(in, rows, geo, smem, status,
+        [&](const uint8_t *stage, long long first_row, int n, int it, int cw, int lane) {
+            int my_vecs = 0;
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) my_vecs += (lane + 32 * j < nvec) ? 1 : 0;
+            const int full_groups = (geo.rows_per_stage + kRows - 1) / kRows;
+            const int groups = (n + kRows - 1) / kRows;
+            for (int g = first_group_of_warp(it, full_groups, cw, kConsumerWarps); g < groups; g += kConsumerWarps) {
+                const int r0 = g * kRows;
+                Raw raw[kRows][kVecs];
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) {
+                    const Raw *row = reinterpret_cast<const Raw *>(stage + (size_t)(r0 + r) * geo.row_bytes);
+#pragma unroll
+                    for (int j = 0; j < kVecs; ++j) {
+                        const int v = lane + 32 * j;
+                        if (r0 + r < n && v < nvec) raw[r][j] = row[v];
+                        else raw[r][j] = Raw{};
+                    }
+                }
+                layernorm_rows_from_registers<T, kVecs, kRows>(raw, my_vecs, nvec, lane, first_row + r0, first_row + n,
+                                                               reinterpret_cast<Raw *>(out), cols, eps,
+                                                               reinterpret_cast<const Raw *>(gamma),
+                                                               reinterpret_cast<const Raw *>(beta), ddof);
+            }
+        });
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -193,7 +258,7 @@ __device__ __forceinline__ void layernorm_block_tier(const T *in, T *out, long l
     for (int j = 0; j < kVecs; ++j) my_vecs += ((int)threadIdx.x + (int)blockDim.x * j < nvec) ? 1 : 0;
 
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-        float x[kVecs * kPer];
+        // all loads first, then one unpack to FP32: the three passes below run on registers
         Raw raw[kVecs];
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
@@ -201,14 +266,29 @@ __device__ __forceinline__ void layernorm_block_tier(const T *in, T *out, long l
             if (v < nvec) raw[j] = ld_stream(in_v + row * nvec + v);
             else raw[j] = Raw{};
         }
+        float x[kVecs][kPer];
+        float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
-            float f[kPer];
-            Io::unpack(raw[j], f);
+            Io::unpack(raw[j], x[j]);
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) x[j * kPer + e] = f[e];
+            for (int e = 0; e < kPer; ++e) sum += x[j][e];  // padded vectors are zero
         }
-        Welford w = welford_of_registers<kVecs * kPer>(x, my_vecs * kPer);
+        Welford w;
+        w.n = (float)(my_vecs * kPer);
+        w.mean = my_vecs > 0 ? sum / w.n : 0.f;
+        float m2 = 0.f;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            float part = 0.f;
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                const float d = x[j][e] - w.mean;
+                part = fmaf(d, d, part);
+            }
+            m2 += j < my_vecs ? part : 0.f;
+        }
+        w.m2 = m2;
         w = block_allreduce_welford(w, s_exchange);
         const float mean = w.mean;
         const float rstd = rstd_from(w, cols, ddof, eps);
@@ -219,10 +299,10 @@ __device__ __forceinline__ void layernorm_block_tier(const T *in, T *out, long l
             float g[kPer], b[kPer], y[kPer];
 #pragma unroll
             for (int e = 0; e < kPer; ++e) { g[e] = 1.f; b[e] = 0.f; }
-            if (gamma) Io::unpack(__ldg(gamma_v + v), g);
-            if (beta) Io::unpack(__ldg(beta_v + v), b);
+            if (gamma_v) Io::unpack(__ldg(gamma_v + v), g);
+            if (beta_v) Io::unpack(__ldg(beta_v + v), b);
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) y[e] = fmaf((x[j * kPer + e] - mean) * rstd, g[e], b[e]);
+            for (int e = 0; e < kPer; ++e) y[e] = fmaf((x[j][e] - mean) * rstd, g[e], b[e]);
             st_stream(out_v + row * nvec + v, Io::pack(y));
         }
     }
@@ -264,6 +344,14 @@ template <typename T, int kVecs, int kRows>
 __global__ void __launch_bounds__(256) layernorm_warp_kernel(const T *in, T *out, long long rows, int cols, float eps,
                                                              const T *gamma, const T *beta, int ddof) {
     layernorm_warp_tier<T, kVecs, kRows>(in, out, rows, cols, eps, gamma, beta, ddof);
+}
+template <typename T, int kVecs, int kRows, int kConsumerWarps>
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32)
+layernorm_staged_kernel(const T *in, T *out, long long rows, int cols, float eps, const T *gamma, const T *beta, int ddof,
+                        const RowPipeGeometry geo, unsigned *status) {
+    extern __shared__ __align__(128) uint8_t ko_row_stage_smem[];
+    layernorm_staged_tier<T, kVecs, kRows, kConsumerWarps>(in, out, rows, cols, eps, gamma, beta, ddof, geo,
+                                                           ko_row_stage_smem, status);
 }
 template <typename T, int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) layernorm_block_kernel(const T *in, T *out, long long rows, int cols,
@@ -321,8 +409,8 @@ struct LayerNormWarpImpl {
     static constexpr int kPer = ko::RowIo<Element>::kPerVec;
     static_assert(num_column % kPer == 0, "the warp tier moves 128-bit vectors");
     static constexpr int kVecs = (num_column / kPer + 31) / 32;
-    static_assert(kVecs * kPer <= 64, "row too long for the warp tier; use LayerNormBlockImpl");
-    static constexpr int kRows = kVecs * kPer <= 16 ? 2 : 1;
+    static_assert(kVecs <= 16, "row too long for the warp tier; use LayerNormBlockImpl");
+    static constexpr int kRows = kVecs <= 4 ? 2 : 1;
     __device__ __forceinline__ static void run(Element *in_data, Element *out_data, Element epsilon,
                                                Element *gamma = nullptr, Element *beta = nullptr) {
         ko::layernorm_warp_tier<Element, kVecs, kRows>(in_data, out_data, num_row, num_column,

@@ -1,41 +1,140 @@
 // Row softmax over the last dimension for sm_100a.
 //
-// Three tiers, chosen by row length (the reference's warp / block-cached / block-no-cache split,
-// nn_operators/softmax/softmax.h:11-60, :62-113, :116-166, re-thought for B200):
+// Four tiers, chosen by row length and alignment (the reference's warp / block-cached /
+// block-no-cache split, nn_operators/softmax/softmax.h:11-60, :62-113, :116-166, re-thought for B200):
 //
-//   warp tier   one warp owns kRows consecutive rows per step; each row sits in registers as
-//               kVecs 128-bit vectors per lane; every load of the step is issued before the
-//               first use, so a warp keeps kRows*kVecs*512 B in flight.  Max and sum are
-//               butterfly all-reduces.  Reads and writes each byte once.
-//   block tier  one thread block per row, the row in registers (kVecs vectors per thread),
-//               warp all-reduce + one shared-memory exchange per statistic.
-//   stream tier one thread block per row, three passes over global memory with scalar
-//               accesses; any column count and any alignment (correctness path).
+//   staged tier persistent blocks; a producer warp streams chunks of whole rows into a shared-memory
+//               ring with 1-D bulk copies (TMA) and consumer warps run the row math out of shared
+//               memory (common/row_pipeline.h).  Bytes in flight are set by the ring, not by occupancy.
+//   warp tier   one warp owns a few consecutive rows per step; a row sits in the registers of a group
+//               of 8, 16 or 32 lanes as kVecs 128-bit vectors per lane (short rows share a warp);
+//               every load of the step is issued before the first use.
+//   block tier  one thread block per row, the row in registers (kVecs vectors per thread), warp
+//               all-reduce + one shared-memory exchange per statistic.
+//   stream tier one thread block per row, three passes over global memory with scalar accesses; any
+//               column count and any alignment (correctness path).
 //
-// All tiers compute exp(x - rowmax) / sum in FP32 (the reference's Subtract functor adds,
-// common/functors.h:168, so it evaluates exp(x + rowmax); the two agree mathematically but the
-// reference overflows once 2*rowmax > 88.7).
+// All tiers compute exp(x - rowmax) / sum in FP32 as 2^((x - rowmax) * log2 e) on the special-function
+// unit; a row's results do not depend on the tier's launch geometry.  (The reference's Subtract
+// functor adds, common/functors.h:168, so it evaluates exp(x + rowmax); the two agree mathematically
+// but the reference overflows once 2*rowmax > 88.7.)
 //
 // The reference's class templates SoftMaxWarpImpl / SoftMaxBlockImpl / SoftMaxBlockNoCacheImpl and
 // the softmax<Kernel> __global__ wrapper keep their names, template parameters and static members,
 // so `softmax<SoftMaxWarpImpl<float, 4, R, C>><<<grid, block, smem, stream>>>(in, out)` still
-// compiles; every tier is a grid-stride loop and therefore correct for any launch geometry.
+// compiles; those tiers are grid-stride loops and therefore correct for any launch geometry.
 #pragma once
 
 #include "../../common/common.h"
 #include "../../common/functors.h"
+#include "../../common/row_pipeline.h"
 
 namespace ko {
 
 constexpr float kNegInf = -__builtin_huge_valf();
+constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ float max4(const float4 &v) { return fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)); }
+__device__ __forceinline__ float4 neg_inf4() { return make_float4(kNegInf, kNegInf, kNegInf, kNegInf); }
+
+// e^(x - m) for the four lanes of v, as 2^(x*log2e - m*log2e); returns their sum
+__device__ __forceinline__ float exp_shifted4(float4 &v, float neg_m_log2e) {
+    v.x = exp2_approx(fmaf(v.x, kLog2e, neg_m_log2e));
+    v.y = exp2_approx(fmaf(v.y, kLog2e, neg_m_log2e));
+    v.z = exp2_approx(fmaf(v.z, kLog2e, neg_m_log2e));
+    v.w = exp2_approx(fmaf(v.w, kLog2e, neg_m_log2e));
+    return (v.x + v.y) + (v.z + v.w);
+}
+__device__ __forceinline__ void scale4(float4 &v, float s) { v.x *= s; v.y *= s; v.z *= s; v.w *= s; }
+
+// A row is spread over a group of G lanes (G = 8, 16 or 32), kVecs 128-bit vectors per lane, so a warp
+// works on 32/G rows at once ("a slot") and short rows do not pay for 32-lane reductions.  G depends
+// only on the column count, so a row's arithmetic is the same in every tier and launch geometry.
+template <int G>
+__device__ __forceinline__ float group_allreduce_max(float v) {
+    if constexpr (G == 32) return warp_redux_max(v);
+#pragma unroll
+    for (int m = G / 2; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, m));
+    return v;
+}
+template <int G>
+__device__ __forceinline__ float group_allreduce_sum(float v) {
+#pragma unroll
+    for (int m = G / 2; m > 0; m >>= 1) v += __shfl_xor_sync(kFullMask, v, m);
+    return v;
+}
+
+// kSlots independent slots, each holding one row per lane group (padding = -inf): in place to
+// probabilities.  The independent chains are what hides the shuffle latency.
+template <int kVecs, int kSlots, int G>
+__device__ __forceinline__ void softmax_rows_in_registers(float4 (&x)[kSlots][kVecs]) {
+    float mx[kSlots], sum[kSlots];
+#pragma unroll
+    for (int r = 0; r < kSlots; ++r) {
+        float m = max4(x[r][0]);
+#pragma unroll
+        for (int j = 1; j < kVecs; ++j) m = fmaxf(m, max4(x[r][j]));
+        mx[r] = m;
+    }
+#pragma unroll
+    for (int r = 0; r < kSlots; ++r) mx[r] = group_allreduce_max<G>(mx[r]);
+#pragma unroll
+    for (int r = 0; r < kSlots; ++r) {
+        const float neg = -mx[r] * kLog2e;
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) s += exp_shifted4(x[r][j], neg);
+        sum[r] = s;
+    }
+#pragma unroll
+    for (int r = 0; r < kSlots; ++r) sum[r] = group_allreduce_sum<G>(sum[r]);
+#pragma unroll
+    for (int r = 0; r < kSlots; ++r) {
+        const float inv = rcp_approx(sum[r]);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) scale4(x[r][j], inv);
+    }
+}
+
+// Loads/stores of a warp's kSlots * (32/G) consecutive rows starting at `base` (a row-major array of
+// float4 with nvec vectors per row); rows >= nrows are padded / skipped.
+template <int kVecs, int kSlots, int G, typename Load>
+__device__ __forceinline__ void softmax_load_rows(float4 (&x)[kSlots][kVecs], int lane, int nvec, long long nrows,
+                                                  Load &&load) {
+    constexpr int kRowsPerSlot = 32 / G;
+    const int sub = lane / G, gl = lane % G;
+#pragma unroll
+    for (int r = 0; r < kSlots; ++r) {
+        const long long row = r * kRowsPerSlot + sub;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = gl + G * j;
+            x[r][j] = (row < nrows && v < nvec) ? load(row, v) : neg_inf4();
+        }
+    }
+}
+template <int kVecs, int kSlots, int G>
+__device__ __forceinline__ void softmax_store_rows(const float4 (&x)[kSlots][kVecs], int lane, int nvec, long long nrows,
+                                                   float4 *out_rows) {
+    constexpr int kRowsPerSlot = 32 / G;
+    const int sub = lane / G, gl = lane % G;
+#pragma unroll
+    for (int r = 0; r < kSlots; ++r) {
+        const long long row = r * kRowsPerSlot + sub;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = gl + G * j;
+            if (row < nrows && v < nvec) st_stream(out_rows + row * nvec + v, x[r][j]);
+        }
+    }
+}
 
 // ---------------------------------------------------------------------------------------------
 // warp tier
 // ---------------------------------------------------------------------------------------------
-template <int kVecs, int kRows>
+template <int kVecs, int kSlots, int G>
 __device__ __forceinline__ void softmax_warp_tier(const float *in, float *out, long long rows, int cols) {
+    constexpr int kRowsPerStep = kSlots * (32 / G);
     const int lane = threadIdx.x & 31;
     const int nvec = cols >> 2;  // 128-bit vectors per row
     const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
@@ -43,61 +142,40 @@ __device__ __forceinline__ void softmax_warp_tier(const float *in, float *out, l
     const float4 *in4 = reinterpret_cast<const float4 *>(in);
     float4 *out4 = reinterpret_cast<float4 *>(out);
 
-    for (long long row0 = warp_global * kRows; row0 < rows; row0 += warps_per_grid * kRows) {
-        float4 x[kRows][kVecs];
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            const bool row_ok = row0 + r < rows;
-#pragma unroll
-            for (int j = 0; j < kVecs; ++j) {
-                const int v = lane + 32 * j;
-                x[r][j] = (row_ok && v < nvec) ? ld_stream(in4 + (row0 + r) * nvec + v)
-                                               : make_float4(kNegInf, kNegInf, kNegInf, kNegInf);
-            }
-        }
-        float mx[kRows];
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            float m = max4(x[r][0]);
-#pragma unroll
-            for (int j = 1; j < kVecs; ++j) m = fmaxf(m, max4(x[r][j]));
-            mx[r] = m;
-        }
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) mx[r] = warp_allreduce_max(mx[r]);
-
-        float sum[kRows];
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            float s = 0.f;
-#pragma unroll
-            for (int j = 0; j < kVecs; ++j) {
-                x[r][j].x = expf(x[r][j].x - mx[r]);
-                x[r][j].y = expf(x[r][j].y - mx[r]);
-                x[r][j].z = expf(x[r][j].z - mx[r]);
-                x[r][j].w = expf(x[r][j].w - mx[r]);
-                s += (x[r][j].x + x[r][j].y) + (x[r][j].z + x[r][j].w);
-            }
-            sum[r] = s;
-        }
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) sum[r] = warp_allreduce_sum(sum[r]);
-
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            const float inv = 1.0f / sum[r];
-            const bool row_ok = row0 + r < rows;
-#pragma unroll
-            for (int j = 0; j < kVecs; ++j) {
-                const int v = lane + 32 * j;
-                if (row_ok && v < nvec) {
-                    float4 y = x[r][j];
-                    y.x *= inv; y.y *= inv; y.z *= inv; y.w *= inv;
-                    st_stream(out4 + (row0 + r) * nvec + v, y);
-                }
-            }
-        }
+    for (long long row0 = warp_global * kRowsPerStep; row0 < rows; row0 += warps_per_grid * kRowsPerStep) {
+        float4 x[kSlots][kVecs];
+        const float4 *src = in4 + row0 * nvec;
+        softmax_load_rows<kVecs, kSlots, G>(x, lane, nvec, rows - row0,
+                                            [&](long long row, int v) { return ld_stream(src + row * nvec + v); });
+        softmax_rows_in_registers<kVecs, kSlots, G>(x);
+        softmax_store_rows<kVecs, kSlots, G>(x, lane, nvec, rows - row0, out4 + row0 * nvec);
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// staged tier: consumer side of the row pipeline
+// ---------------------------------------------------------------------------------------------
+template <int kVecs, int kSlots, int G, int kConsumerWarps>
+__device__ __forceinline__ void softmax_staged_tier(const float *in, float *out, long long rows, int cols,
+                                                    const RowPipeGeometry geo, uint8_t *smem, unsigned *status) {
+    constexpr int kRowsPerStep = kSlots * (32 / G);
+    const int nvec = cols >> 2;
+    float4 *out4 = reinterpret_cast<float4 *>(out);
+    row_pipeline<kConsumerWarps>(in, rows, geo, smem, status,
+        [&](const uint8_t *stage, long long first_row, int n, int it, int cw, int lane) {
+            const float4 *stage4 = reinterpret_cast<const float4 *>(stage);
+            const int full_groups = (geo.rows_per_stage + kRowsPerStep - 1) / kRowsPerStep;
+            const int groups = (n + kRowsPerStep - 1) / kRowsPerStep;
+            for (int g = first_group_of_warp(it, full_groups, cw, kConsumerWarps); g < groups; g += kConsumerWarps) {
+                const int r0 = g * kRowsPerStep;
+                float4 x[kSlots][kVecs];
+                const float4 *src = stage4 + (size_t)r0 * nvec;
+                softmax_load_rows<kVecs, kSlots, G>(x, lane, nvec, n - r0,
+                                                    [&](long long row, int v) { return src[row * nvec + v]; });
+                softmax_rows_in_registers<kVecs, kSlots, G>(x);
+                softmax_store_rows<kVecs, kSlots, G>(x, lane, nvec, n - r0, out4 + (first_row + r0) * nvec);
+            }
+        });
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -127,26 +205,22 @@ __device__ __forceinline__ void softmax_block_tier(const float *in, float *out, 
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
             const int v = threadIdx.x + blockDim.x * j;
-            x[j] = v < nvec ? ld_stream(in4 + row * nvec + v) : make_float4(kNegInf, kNegInf, kNegInf, kNegInf);
+            x[j] = v < nvec ? ld_stream(in4 + row * nvec + v) : neg_inf4();
             m = fmaxf(m, max4(x[j]));
         }
         m = block_allreduce<true>(m, s_exchange);
+        const float neg = -m * kLog2e;
         float s = 0.f;
 #pragma unroll
-        for (int j = 0; j < kVecs; ++j) {
-            x[j].x = expf(x[j].x - m); x[j].y = expf(x[j].y - m);
-            x[j].z = expf(x[j].z - m); x[j].w = expf(x[j].w - m);
-            s += (x[j].x + x[j].y) + (x[j].z + x[j].w);
-        }
+        for (int j = 0; j < kVecs; ++j) s += exp_shifted4(x[j], neg);
         s = block_allreduce<false>(s, s_exchange);
-        const float inv = 1.0f / s;
+        const float inv = rcp_approx(s);
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
             const int v = threadIdx.x + blockDim.x * j;
             if (v < nvec) {
-                float4 y = x[j];
-                y.x *= inv; y.y *= inv; y.z *= inv; y.w *= inv;
-                st_stream(out4 + row * nvec + v, y);
+                scale4(x[j], inv);
+                st_stream(out4 + row * nvec + v, x[j]);
             }
         }
     }
@@ -163,19 +237,26 @@ __device__ __forceinline__ void softmax_stream_tier(const float *in, float *out,
         float m = kNegInf;
         for (int c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, x[c]);
         m = block_allreduce<true>(m, s_exchange);
+        const float neg = -m * kLog2e;
         float s = 0.f;
-        for (int c = threadIdx.x; c < cols; c += blockDim.x) s += expf(x[c] - m);
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) s += exp2_approx(fmaf(x[c], kLog2e, neg));
         s = block_allreduce<false>(s, s_exchange);
-        const float inv = 1.0f / s;
-        for (int c = threadIdx.x; c < cols; c += blockDim.x) y[c] = expf(x[c] - m) * inv;
+        const float inv = rcp_approx(s);
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) y[c] = exp2_approx(fmaf(x[c], kLog2e, neg)) * inv;
         __syncthreads();
     }
 }
 
 // runtime-shape kernels used by the C ABI
-template <int kVecs, int kRows>
+template <int kVecs, int kSlots, int G>
 __global__ void __launch_bounds__(256) softmax_warp_kernel(const float *in, float *out, long long rows, int cols) {
-    softmax_warp_tier<kVecs, kRows>(in, out, rows, cols);
+    softmax_warp_tier<kVecs, kSlots, G>(in, out, rows, cols);
+}
+template <int kVecs, int kSlots, int G, int kConsumerWarps>
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32)
+softmax_staged_kernel(const float *in, float *out, long long rows, int cols, const RowPipeGeometry geo, unsigned *status) {
+    extern __shared__ __align__(128) uint8_t ko_row_stage_smem[];
+    softmax_staged_tier<kVecs, kSlots, G, kConsumerWarps>(in, out, rows, cols, geo, ko_row_stage_smem, status);
 }
 template <int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) softmax_block_kernel(const float *in, float *out, long long rows, int cols) {
@@ -198,11 +279,13 @@ struct SoftMaxWarpImpl {
     static constexpr int vec_len = vec_len_, num_row = num_row_, num_column = num_column_;
     static constexpr int smem_in_bytes = 0;
     static_assert(num_column % 4 == 0, "the warp tier moves 128-bit vectors");
-    static constexpr int kVecs = (num_column / 4 + 31) / 32;
+    static constexpr int kNvec = num_column / 4;
+    static constexpr int kGroup = kNvec <= 32 ? 8 : (kNvec <= 64 ? 16 : 32);   // lanes per row
+    static constexpr int kVecs = (kNvec + kGroup - 1) / kGroup;
     static_assert(kVecs <= 16, "row too long for the warp tier; use SoftMaxBlockImpl");
-    static constexpr int kRows = kVecs >= 8 ? 1 : (kVecs >= 4 ? 2 : 4);
+    static constexpr int kSlots = kVecs >= 8 ? 1 : 2;
     __device__ __forceinline__ static void run(T *in_data, T *out_data) {
-        ko::softmax_warp_tier<kVecs, kRows>(in_data, out_data, num_row, num_column);
+        ko::softmax_warp_tier<kVecs, kSlots, kGroup>(in_data, out_data, num_row, num_column);
     }
 };
 

@@ -8,7 +8,11 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 TOL_FRO = 1e-3
-TIGHT_FRO = 2e-6
+
+
+def tight(K):
+    """FP32 accumulation over K terms: about sqrt(K) * 2^-24, with head-room."""
+    return 2e-6 * max(1.0, (K / 256.0) ** 0.5)
 
 
 def _bits(oracle, kind):
@@ -29,7 +33,7 @@ def _run(cuda, lib, kind, ab, bb, c=None, bn=0):
                               None if cd is None else cd.data_ptr(), dd.data_ptr(), bn, cuda.cuda.current_stream().cuda_stream)
     assert rc == 0, lib.ko_last_error_string()
     cuda.cuda.synchronize()
-    assert lib.ko_gemm_tc_poll_status() == 0, lib.ko_last_error_string()
+    assert lib.ko_poll_device_status() == 0, lib.ko_last_error_string()
     return dd.cpu().numpy()
 
 
@@ -40,7 +44,7 @@ def _case(cuda, lib, oracle, kind, M, N, K, with_c=False, bn=0, seed=3):
     d = _run(cuda, lib, kind, ab, bb, c, bn)
     want = oracle.gemm_tn_f64(from_bits(ab), from_bits(bb), c)
     err = oracle.rel_frobenius(d, want)
-    assert err <= TOL_FRO and err <= TIGHT_FRO, (kind, M, N, K, bn, err)
+    assert err <= TOL_FRO and err <= tight(K), (kind, M, N, K, bn, err)
     return d
 
 
@@ -70,7 +74,7 @@ def test_more_tiles_than_sms_and_both_accumulators(cuda, lib, oracle):
     _case(cuda, lib, oracle, "bf16", 8192, 4096, 64, bn=128)
     d1 = _case(cuda, lib, oracle, "f16", 4096, 4096, 256, bn=256)
     d2 = _case(cuda, lib, oracle, "f16", 4096, 4096, 256, bn=128)
-    assert np.array_equal(d1, d1) and oracle.rel_frobenius(d2, d1.astype(np.float64)) <= TIGHT_FRO
+    assert oracle.rel_frobenius(d2, d1.astype(np.float64)) <= tight(256)
 
 
 def test_exact_small_integers(cuda, lib, oracle):
@@ -96,7 +100,7 @@ def test_baseline_shapes(cuda, lib, oracle, ko):
             d = _run(cuda, lib, kind, ab, bb)
             rows = np.unique(np.r_[0:16, M - 16:M, rng.integers(0, M, 32)])
             want = oracle.gemm_tn_f64(from_bits(ab[rows]), from_bits(bb))
-            assert oracle.rel_frobenius(d[rows], want) <= TIGHT_FRO
+            assert oracle.rel_frobenius(d[rows], want) <= tight(K)
             ri, ci = rng.integers(0, M, 4096), rng.integers(0, N, 4096)
             spot = np.einsum("ik,ik->i", from_bits(ab[ri]).astype(np.float64), from_bits(bb[ci]).astype(np.float64))
             assert np.abs(d[ri, ci] - spot).max() <= 1e-3 * np.abs(spot).max()

@@ -17,17 +17,20 @@ def _inputs(oracle, rows, cols, seed=1):
             oracle.fill_normal((cols,), seed, 2, 0.0, 0.1))
 
 
-def _run_f32(cuda, lib, x, eps, g=None, b=None, ddof=0, rpw=0, block=0, cap=0, inplace=False):
+def _run_f32(cuda, lib, x, eps, g=None, b=None, ddof=0, inplace=False, **knobs):
+    from kernel_optimization_b200.native import RowKnobs
+
     xd = cuda.from_numpy(x).cuda()
     gd = None if g is None else cuda.from_numpy(g).cuda()
     bd = None if b is None else cuda.from_numpy(b).cuda()
     yd = xd if inplace else cuda.empty_like(xd)
     rows, cols = x.shape
     rc = lib.ko_layernorm_f32_tuned(xd.data_ptr(), yd.data_ptr(), rows, cols, eps, None if gd is None else gd.data_ptr(),
-                                    None if bd is None else bd.data_ptr(), ddof, rpw, block, cap,
+                                    None if bd is None else bd.data_ptr(), ddof, RowKnobs(**knobs) if knobs else None,
                                     cuda.cuda.current_stream().cuda_stream)
     cuda.cuda.synchronize()
     assert rc == 0, lib.ko_last_error_string()
+    assert lib.ko_poll_device_status() == 0, lib.ko_last_error_string()
     return yd.cpu().numpy()
 
 
@@ -35,17 +38,20 @@ def _dev_bf16(cuda, bits):
     return cuda.from_numpy(bits.view(np.int16)).cuda().view(cuda.bfloat16)
 
 
-def _run_bf16(cuda, lib, xb, eps, gb=None, bb=None, ddof=0, block=0):
+def _run_bf16(cuda, lib, xb, eps, gb=None, bb=None, ddof=0, **knobs):
+    from kernel_optimization_b200.native import RowKnobs
+
     xd = _dev_bf16(cuda, xb)
     gd = None if gb is None else _dev_bf16(cuda, gb)
     bd = None if bb is None else _dev_bf16(cuda, bb)
     yd = cuda.empty_like(xd)
     rows, cols = xb.shape
     rc = lib.ko_layernorm_bf16_tuned(xd.data_ptr(), yd.data_ptr(), rows, cols, eps, None if gd is None else gd.data_ptr(),
-                                     None if bd is None else bd.data_ptr(), ddof, 0, block, 0,
+                                     None if bd is None else bd.data_ptr(), ddof, RowKnobs(**knobs) if knobs else None,
                                      cuda.cuda.current_stream().cuda_stream)
     cuda.cuda.synchronize()
     assert rc == 0, lib.ko_last_error_string()
+    assert lib.ko_poll_device_status() == 0, lib.ko_last_error_string()
     return yd.view(cuda.int16).cpu().numpy().view(np.uint16)
 
 
@@ -70,26 +76,43 @@ def test_f32_is_not_the_reference_kernels_arithmetic(cuda, lib, oracle, golden):
     assert np.abs(y - golden["layernorm_8x768_warp"]).max() > 10.0
 
 
-@pytest.mark.parametrize("rpw,block,cap", [(1, 64, 0), (2, 128, 0), (1, 256, 5), (2, 256, 1)])
-def test_f32_launch_geometry_does_not_change_rows(cuda, lib, oracle, rpw, block, cap):
-    for cols in (128, 256, 512, 768, 1024):
-        x, g, b = _inputs(oracle, 77, cols)
-        assert np.array_equal(_run_f32(cuda, lib, x, 1e-12, g, b, 0, rpw, block, cap), _run_f32(cuda, lib, x, 1e-12, g, b))
+GEOMETRIES = [dict(tier=1, rows_per_warp=1, block=64), dict(tier=1, rows_per_warp=2, block=128), dict(tier=1, block=256, grid_cap=5),
+              dict(tier=1, rows_per_warp=2, grid_cap=1), dict(tier=4), dict(tier=4, rows_per_warp=1, stages=2),
+              dict(tier=4, rows_per_warp=2, stages=3, ctas_per_sm=2), dict(tier=4, stage_rows=8, stages=2)]
+
+
+@pytest.mark.parametrize("knobs", GEOMETRIES, ids=lambda k: "-".join(f"{a}{b}" for a, b in k.items()))
+def test_f32_warp_and_staged_tiers_give_the_same_rows(cuda, lib, oracle, knobs):
+    for rows, cols in ((77, 128), (77, 256), (130, 512), (77, 768), (77, 1024), (40, 2048), (90, 772)):
+        x, g, b = _inputs(oracle, rows, cols)
+        y = _run_f32(cuda, lib, x, 1e-12, g, b, 0, **knobs)
+        assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=1))
+        assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
 
 
 @pytest.mark.parametrize("block", [128, 256, 512, 1024])
 def test_f32_block_tier_thread_counts(cuda, lib, oracle, block):
-    for cols in (2048, 4096, 8192):
+    for cols in (768, 2048, 4096, 8192):
         x, g, b = _inputs(oracle, 19, cols)
-        assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b, 0, 0, block), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+        assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=2, block=block), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+
+
+def test_f32_stream_tier_and_staged_ring_wrap(cuda, lib, oracle):
+    x, g, b = _inputs(oracle, 23, 768)
+    assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=3), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+    x, g, b = _inputs(oracle, 148 * 8 * 12 + 5, 256)
+    y = _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=4, stage_rows=8, stages=2, rows_per_warp=1)
+    assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=1))
 
 
 def test_f32_edge_rows(cuda, lib, oracle):
     const = np.full((4, 768), 3.25, dtype=np.float32)
     assert np.array_equal(_run_f32(cuda, lib, const, 1e-12), np.zeros_like(const))      # var = 0
     x, g, b = _inputs(oracle, 300, 768)
-    x += 1000.0                                                                          # large common offset
+    x += 10.0   # common offset of 10 sigma; FP32 statistics lose about |mean|/sigma * 2^-24 per unit of offset
     assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+    far = x + 990.0   # offset 1000 sigma: the mean itself is only representable to 6e-5
+    assert oracle.max_rel_err(_run_f32(cuda, lib, far, 1e-12, g, b), oracle.layernorm_f64(far, 1e-12, g, b)) <= 5e-4
     y = _run_f32(cuda, lib, x, 1e-12, g, b)
     assert np.array_equal(_run_f32(cuda, lib, x, 1e-12, g, b, inplace=True), y)
     assert np.array_equal(_run_f32(cuda, lib, x, 1e-12, g, b), y)
@@ -123,12 +146,15 @@ def test_bf16_against_rounded_oracle(cuda, lib, oracle, rows, cols):
     assert oracle.max_rel_err(got, want) <= 2.0 ** -8 * 1.01                    # half an ulp of BF16 rounding
 
 
-@pytest.mark.parametrize("block", [128, 256, 512, 1024])
-def test_bf16_block_tier_thread_counts(cuda, lib, oracle, block):
-    x, g, b = _inputs(oracle, 21, 8192)
-    xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
-    base = _run_bf16(cuda, lib, xb, 1e-12, gb, bb)
-    assert np.mean(_run_bf16(cuda, lib, xb, 1e-12, gb, bb, block=block) != base) <= 2e-3
+@pytest.mark.parametrize("knobs", [dict(tier=1), dict(tier=2, block=128), dict(tier=2, block=256), dict(tier=2, block=512),
+                                   dict(tier=2, block=1024), dict(tier=3), dict(tier=4), dict(tier=4, stages=2, ctas_per_sm=2)],
+                         ids=lambda k: "-".join(f"{a}{b}" for a, b in k.items()))
+def test_bf16_tiers_agree(cuda, lib, oracle, knobs):
+    for rows, cols in ((21, 4096), (50, 1024), (33, 776)):
+        x, g, b = _inputs(oracle, rows, cols)
+        xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
+        base = _run_bf16(cuda, lib, xb, 1e-12, gb, bb, tier=1)
+        assert np.mean(_run_bf16(cuda, lib, xb, 1e-12, gb, bb, **knobs) != base) <= 2e-3
 
 
 def test_bf16_scaled_shard_properties(cuda, lib, oracle, ko):

@@ -10,17 +10,22 @@ pytestmark = pytest.mark.gpu
 TOL_ABS, TOL_ROWSUM = 1e-6, 1e-5
 
 
-def _run(cuda, lib, x, rpw=0, block=0, cap=0, inplace=False):
+def _run(cuda, lib, x, inplace=False, **knobs):
+    from kernel_optimization_b200.native import RowKnobs
+
     xd = cuda.from_numpy(x).cuda()
     yd = xd if inplace else cuda.empty_like(xd)
     s = cuda.cuda.current_stream().cuda_stream
     rows, cols = x.shape
-    if rpw or block or cap:
-        rc = lib.ko_softmax_f32_tuned(xd.data_ptr(), yd.data_ptr(), rows, cols, rpw, block, cap, s)
+    if knobs:
+        rc = lib.ko_softmax_f32_tuned(xd.data_ptr(), yd.data_ptr(), rows, cols, RowKnobs(**knobs), s)
     else:
         rc = lib.ko_softmax_f32(xd.data_ptr(), yd.data_ptr(), rows, cols, s)
     cuda.cuda.synchronize()
+    if rc == 3 and knobs.get("tier") == 4 and knobs.get("stage_rows"):
+        return None  # an explicit ring geometry that does not fit in shared memory is refused, not shrunk
     assert rc == 0, lib.ko_last_error_string()
+    assert lib.ko_poll_device_status() == 0, lib.ko_last_error_string()
     return yd.cpu().numpy()
 
 
@@ -44,13 +49,38 @@ def test_against_reference_kernel_outputs(cuda, lib, oracle, golden):
     assert np.abs(_run(cuda, lib, x) - golden["softmax_16x512_causal"]).max() <= TOL_ABS
 
 
-@pytest.mark.parametrize("rpw,block,cap", [(1, 128, 0), (2, 256, 0), (4, 64, 0), (8, 256, 0), (4, 256, 3), (0, 0, 1)])
-def test_every_launch_geometry_gives_the_same_rows(cuda, lib, oracle, rpw, block, cap):
-    for cols in (128, 256, 512, 768, 1024, 1536, 2048):
-        x = oracle.fill_normal((131, cols), 0, 0, 0.0, 2.0)
-        y = _run(cuda, lib, x, rpw, block, cap)
-        assert np.array_equal(y, _run(cuda, lib, x)), (cols, "row results must not depend on the launch geometry")
+GEOMETRIES = [dict(tier=1, rows_per_warp=1, block=128), dict(tier=1, rows_per_warp=2, block=256),
+              dict(tier=1, rows_per_warp=4, block=64), dict(tier=1, rows_per_warp=8), dict(tier=1, rows_per_warp=4, grid_cap=3),
+              dict(tier=1, grid_cap=1), dict(tier=4), dict(tier=4, rows_per_warp=1, stages=2), dict(tier=4, rows_per_warp=2, stages=3, ctas_per_sm=2),
+              dict(tier=4, rows_per_warp=4, stage_rows=32, stages=5), dict(tier=4, stage_rows=8, stages=2)]
+
+
+@pytest.mark.parametrize("knobs", GEOMETRIES, ids=lambda k: "-".join(f"{a}{b}" for a, b in k.items()))
+def test_warp_and_staged_tiers_give_the_same_rows_for_every_geometry(cuda, lib, oracle, knobs):
+    for rows, cols in ((131, 128), (131, 256), (257, 512), (131, 768), (70, 1024), (131, 1536), (67, 2048), (300, 132)):
+        x = oracle.fill_normal((rows, cols), 0, 0, 0.0, 2.0)
+        y = _run(cuda, lib, x, **knobs)
+        if y is None:
+            assert rows * cols * 4 > 100000, "only large explicit rings may be refused"
+            continue
+        assert np.array_equal(y, _run(cuda, lib, x, tier=1)), (cols, "row results must not depend on tier or geometry")
         assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS
+
+
+@pytest.mark.parametrize("tier", [2, 3])
+def test_block_and_stream_tiers(cuda, lib, oracle, tier):
+    for rows, cols in ((9, 128), (5, 4096), (3, 32768), (4, 1000)):
+        x = oracle.fill_normal((rows, cols), 0, 0, 0.0, 2.0)
+        y = _run(cuda, lib, x, tier=tier)
+        assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS and oracle.max_rowsum_err(y) <= TOL_ROWSUM
+
+
+def test_staged_tier_many_stages_per_block(cuda, lib, oracle):
+    """Enough rows that every persistent block wraps its ring several times (phase bits flip)."""
+    x = oracle.fill_normal((148 * 8 * 40 + 13, 128), 0, 0, 0.0, 2.0)
+    y = _run(cuda, lib, x, tier=4, stage_rows=8, stages=2, rows_per_warp=1)
+    assert np.array_equal(y, _run(cuda, lib, x, tier=1))
+    assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS
 
 
 def test_causal_blocks_and_extreme_logits(cuda, lib, oracle):
