@@ -2,7 +2,13 @@
 #include "ko_internal.h"
 #include "ko_tuning.h"
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "../nn_operators/gemm/simt_gemm.h"
+#include "../nn_operators/gemm/simt_gemm_x2.h"
+#include "row_launch.h"
 
 namespace {
 
@@ -24,23 +30,84 @@ int launch(int M, int N, int K, const float *A, const float *B, const float *C, 
     return KO_OK;
 }
 
-template <typename Cfg>
-double wave_efficiency(long long M, long long N, int sm_count, int blocks_per_sm) {
-    const long long tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + Cfg::BN - 1) / Cfg::BN);
-    const long long slots = (long long)sm_count * blocks_per_sm;
-    const long long waves = (tiles + slots - 1) / slots;
-    const double fill = (double)tiles / (double)(waves * slots);
-    const double useful = (double)(M * N) / (double)(tiles * Cfg::BM * Cfg::BN);
-    return fill * useful;
+// Split-K scratch: partial tiles plus one arrival counter per tile.  One buffer per (device, stream),
+// grown on demand and kept for the life of the process, so that launches on different streams never
+// share partials.  Counters are zero whenever no launch is in flight (the last block resets them).
+struct Scratch {
+    float *partials = nullptr;
+    size_t partial_floats = 0;
+    unsigned *counters = nullptr;
+    size_t counter_count = 0;
+};
+
+int get_scratch(cudaStream_t s, size_t partial_floats, size_t counter_count, Scratch *out) {
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, Scratch> cache;
+    int dev = 0;
+    KO_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    Scratch &sc = cache[{dev, s}];
+    if (sc.partial_floats < partial_floats) {
+        // earlier launches on this stream may still read the old buffer
+        KO_CUDA(cudaStreamSynchronize(s));
+        if (sc.partials) KO_CUDA(cudaFree(sc.partials));
+        sc.partials = nullptr;
+        sc.partial_floats = 0;
+        KO_CUDA(cudaMalloc(&sc.partials, partial_floats * sizeof(float)));
+        sc.partial_floats = partial_floats;
+    }
+    if (sc.counter_count < counter_count) {
+        KO_CUDA(cudaStreamSynchronize(s));
+        if (sc.counters) KO_CUDA(cudaFree(sc.counters));
+        sc.counters = nullptr;
+        sc.counter_count = 0;
+        KO_CUDA(cudaMalloc(&sc.counters, counter_count * sizeof(unsigned)));
+        KO_CUDA(cudaMemset(sc.counters, 0, counter_count * sizeof(unsigned)));
+        sc.counter_count = counter_count;
+    }
+    *out = sc;
+    return KO_OK;
+}
+
+int launch_x2(int M, int N, int K, const float *A, const float *B, const float *C, float *D, int split_k, int sm_count,
+              cudaStream_t s) {
+    namespace x2 = ko::sgemm2;
+    const long long tiles = (long long)((M + x2::BM - 1) / x2::BM) * ((N + x2::BN - 1) / x2::BN);
+    const int ktiles = (K + x2::BK - 1) / x2::BK;
+    if (split_k <= 0) {
+        // fill the SMs (two blocks fit per SM) when the tile count alone cannot; keep >= 8 K-tiles per slice
+        split_k = 1;
+        while (tiles * split_k * 2 <= (long long)sm_count * 2 && ktiles / (split_k * 2) >= 8 && split_k < 16) split_k *= 2;
+    }
+    if (split_k > ktiles) split_k = ktiles > 0 ? ktiles : 1;
+    KO_REQUIRE(tiles * split_k <= 0x7fffffffLL, KO_ERR_SHAPE, "sgemm: %lld blocks exceed the grid limit", tiles * split_k);
+    x2::Params p{M, N, K, A, B, C, D, split_k, nullptr, nullptr};
+    if (split_k > 1) {
+        Scratch sc;
+        if (int st = get_scratch(s, (size_t)tiles * split_k * x2::kTileFloats, (size_t)tiles, &sc)) return st;
+        p.workspace = sc.partials;
+        p.counters = sc.counters;
+    }
+    const bool vec_b = N % 4 == 0 && ko::aligned16(B);
+    const void *kernel = vec_b ? reinterpret_cast<const void *>(x2::sgemm_x2_kernel<true>)
+                               : reinterpret_cast<const void *>(x2::sgemm_x2_kernel<false>);
+    if (int st = ko::ensure_dynamic_smem(kernel, x2::kSmemBytes)) return st;
+    const unsigned grid = (unsigned)(tiles * split_k);
+    if (vec_b) x2::sgemm_x2_kernel<true><<<grid, x2::kThreads, x2::kSmemBytes, s>>>(p);
+    else x2::sgemm_x2_kernel<false><<<grid, x2::kThreads, x2::kSmemBytes, s>>>(p);
+    KO_CHECK_LAUNCH("sgemm_x2_kernel");
+    return KO_OK;
 }
 
 }  // namespace
 
 extern "C" {
 
-// variant: 0 = choose, 1 = 128x128 tiles, 2 = 128x64, 3 = 64x64
+// variant: 0 = choose; 1 = 128x128 tiles with 8x8 per thread; 2 = 128x64; 3 = 64x64 (scalar FFMA,
+// register-staged); 4 = 128x128 with 16x8 per thread, packed FFMA, cp.async ring, split_k slices
+// (split_k 0 = choose, ignored by variants 1-3)
 int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
-                       int variant, void *stream) {
+                       int variant, int split_k, void *stream) {
     KO_REQUIRE(M >= 0 && N >= 0 && K >= 0, KO_ERR_INVALID_ARG, "sgemm: negative shape {%lld,%lld,%lld}",
                (long long)M, (long long)N, (long long)K);
     if (M == 0 || N == 0) return KO_OK;
@@ -52,15 +119,11 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool aligned = K % 4 == 0 && N % 4 == 0 && ko::aligned16(A) && ko::aligned16(B);
 
-    if (variant == 0) {
-        // weigh wave quantisation against the better FFMA:LDS ratio of the larger tiles
-        const double big = 1.00 * wave_efficiency<CfgBig>(M, N, info.sm_count, 1);
-        const double wide = 0.92 * wave_efficiency<CfgWide>(M, N, info.sm_count, 2);
-        const double small = 0.85 * wave_efficiency<CfgSmall>(M, N, info.sm_count, 4);
-        variant = (big >= wide && big >= small) ? 1 : (wide >= small ? 2 : 3);
-    }
+    KO_REQUIRE(split_k >= 0 && split_k <= 64, KO_ERR_INVALID_ARG, "sgemm: split_k %d out of range", split_k);
+    if (variant == 0) variant = (M >= 64 && N >= 64 && K >= 16) ? 4 : 3;
     const int m = (int)M, n = (int)N, k = (int)K;
     switch (variant) {
+        case 4: return launch_x2(m, n, k, A, B, C, D, K == 0 ? 1 : split_k, info.sm_count, s);
         case 1: return launch<CfgBig>(m, n, k, A, B, C, D, aligned, s);
         case 2: return launch<CfgWide>(m, n, k, A, B, C, D, aligned, s);
         case 3: return launch<CfgSmall>(m, n, k, A, B, C, D, aligned, s);
@@ -70,7 +133,7 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
 
 int ko_sgemm_f32(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
                  void *stream) {
-    return ko_sgemm_f32_tuned(M, N, K, A, B, C, D, 0, stream);
+    return ko_sgemm_f32_tuned(M, N, K, A, B, C, D, 0, 0, stream);
 }
 
 }  // extern "C"

@@ -28,9 +28,10 @@ int ko_layernorm_f32_tuned(const float *in, float *out, int64_t rows, int32_t co
 int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps,
                             const uint16_t *gamma, const uint16_t *beta, int ddof, const ko_row_knobs_t *knobs,
                             void *stream);
-/* variant: 0 = choose, otherwise a tile configuration index (see capi_sgemm.cu) */
+/* variant: 0 = choose, 1..3 = scalar-FFMA tilings (128x128, 128x64, 64x64), 4 = packed-FFMA 128x128 kernel;
+ * split_k: K slices of variant 4 (0 = choose, 1 = none) */
 int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
-                       int variant, void *stream);
+                       int variant, int split_k, void *stream);
 /* fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns of D per tile */
 int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C,
                      float *D, int bn, void *stream);
