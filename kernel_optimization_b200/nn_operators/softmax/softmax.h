@@ -52,10 +52,13 @@ __device__ __forceinline__ void scale4(float4 &v, float s) { v.x *= s; v.y *= s;
 // only on the column count, so a row's arithmetic is the same in every tier and launch geometry.
 template <int G>
 __device__ __forceinline__ float group_allreduce_max(float v) {
-    if constexpr (G == 32) return warp_redux_max(v);
+    if constexpr (G == 32) {
+        return warp_redux_max(v);
+    } else {
 #pragma unroll
-    for (int m = G / 2; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, m));
-    return v;
+        for (int m = G / 2; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, m));
+        return v;
+    }
 }
 template <int G>
 __device__ __forceinline__ float group_allreduce_sum(float v) {
