@@ -136,6 +136,23 @@ int ko_layernorm_bf16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t c
 int ko_sgemm_f32(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C,
                  float *D, void *stream);
 
+/* Same operation and kernel as ko_sgemm_f32 for hosts that must not allocate device memory (a process
+ * whose own pool owns the whole GPU, a loop that cannot afford an allocation's implicit
+ * synchronisation, code running where the allocation calls are forbidden).  It has no counterpart
+ * in the reference.  The split-K partial tiles and arrival counters live in a fixed array inside the
+ * library image -- 2 Mi floats (8 MiB) and 4096 counters per GPU, held until the process exits --
+ * and no cudaMalloc / cudaFree or allocating library routine is called.
+ *   split_k  0 = choose (never more slices than the fixed scratch holds), 1 = no split (needs no
+ *            scratch, any size), n > 1 = exactly n K-slices; a request that needs more than the
+ *            scratch holds (tiles * split_k * 16384 floats, tiles = ceil(M/128) * ceil(N/128), at most
+ *            4096 tiles) returns KO_ERR_SHAPE and launches nothing.
+ * The first call on each device looks up the array's device address and configures the kernel; make
+ * that call during set-up, before any stream capture.  Every call on a device uses the same array,
+ * which keeps the previous call's contents (counters are cleared on `stream` before each launch):
+ * calls whose kernels may overlap on the GPU race and must be ordered by the caller. */
+int ko_sgemm_f32_no_alloc(int64_t M, int64_t N, int64_t K, const float *A, const float *B,
+                          const float *C, float *D, int split_k, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Tensor-core GEMM: D[M,N] (FP32, row-major) = A[M,K] (row-major) * B[K,N] (column-major, i.e.
  * element (k,n) at B[n*K + k]) (+ C[M,N] FP32 when C != NULL); FP16 or BF16 inputs as raw
