@@ -167,7 +167,7 @@ def run_gpu_arm(args):
     import torch.distributed as dist
 
     import kernel_optimization_b200 as ko
-    from kernel_optimization_b200 import native
+    from kernel_optimization_b200 import native, sharding
 
     lib = native.lib()  # raises when the CUDA library has not been built: there is no fallback
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -190,16 +190,12 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
 
     def max_over_ranks(ms: float) -> float:
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return sharding.max_over_ranks(ms, dev)
 
     # ---- inputs: this rank's row shard of the global tensors, seeded by global element index
     hbm_peak, tc_peak, peak_kind = measured_peaks()
-    sm_off = rank * SOFTMAX_ROWS * SOFTMAX_COLS
-    ln_off = rank * LN_ROWS * LN_COLS
+    sm_off = sharding.weak_scaled_rows(SOFTMAX_ROWS, SOFTMAX_COLS, rank, world).elem_offset
+    ln_off = sharding.weak_scaled_rows(LN_ROWS, LN_COLS, rank, world).elem_offset
     xs_host = ko.fill_normal((SOFTMAX_ROWS, SOFTMAX_COLS), 0, 0, 0.0, 2.0, elem_offset=sm_off)
     xl_host = ko.fill_normal((LN_ROWS, LN_COLS), 1, 0, 0.0, 1.0, elem_offset=ln_off)
     g_host, b_host = ko.fill_uniform((LN_COLS,), 1, 1, 0.5, 1.5), ko.fill_normal((LN_COLS,), 1, 2, 0.0, 0.1)
@@ -294,10 +290,7 @@ def run_gpu_arm(args):
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
 
-        def replicate(t):
-            if world > 1:
-                dist.broadcast(t, src=0)
-            return t
+        replicate = sharding.replicate_from_rank0
 
         def bench_gemm(name, fn_ours, fn_cublas, flops, iters=20):
             ms_o = timed(fn_ours, iters, 3)

@@ -2,6 +2,7 @@
 // launch one persistent CTA per SM.
 #include "ko_internal.h"
 #include "ko_tuning.h"
+#include "row_launch.h"
 
 #include <mutex>
 
@@ -46,25 +47,29 @@ int make_map(EncodeTiledFn encode, CUtensorMap *map, int fmt, const void *base, 
     return KO_OK;
 }
 
-template <int BN>
-int launch(const CUtensorMap &ma, const CUtensorMap &mb, const ko::tc::GemmParams &p, int sm_count, cudaStream_t s) {
+template <int BN, bool kTmaStore>
+int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &md, const ko::tc::GemmParams &p, int sm_count,
+           cudaStream_t s) {
     using Cfg = ko::tc::TileConfig<BN>;
-    static std::mutex mu;
-    static bool configured[64] = {};
-    int dev = 0;
-    KO_CUDA(cudaGetDevice(&dev));
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!configured[dev]) {
-            KO_CUDA(cudaFuncSetAttribute(ko::tc::gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes));
-            configured[dev] = true;
-        }
-    }
+    auto kernel = ko::tc::gemm_tcgen05_kernel<BN, kTmaStore>;
+    if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), Cfg::kSmemBytes)) return st;
     const long long tiles = (long long)((p.M + ko::tc::kBM - 1) / ko::tc::kBM) * ((p.N + BN - 1) / BN);
     const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
-    ko::tc::gemm_tcgen05_kernel<BN><<<grid, ko::tc::kThreads, Cfg::kSmemBytes, s>>>(ma, mb, p);
+    kernel<<<grid, ko::tc::kThreads, Cfg::kSmemBytes, s>>>(ma, mb, md, p);
     KO_CHECK_LAUNCH("gemm_tcgen05_kernel");
+    return KO_OK;
+}
+
+// FP32 [M, N] row-major output, boxes of 32 rows x 32 columns (128 bytes, 128-byte swizzle)
+int make_store_map(EncodeTiledFn encode, CUtensorMap *map, float *D, int64_t M, int64_t N) {
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, D, dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KO_REQUIRE(r == CUDA_SUCCESS, KO_ERR_CUDA, "cuTensorMapEncodeTiled (D) failed with CUresult %d", (int)r);
     return KO_OK;
 }
 
@@ -78,9 +83,10 @@ double wave_efficiency(long long M, long long N, int bn, int sm_count) {
 
 extern "C" {
 
-// fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns per tile
+// fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns per tile;
+// store_mode: 0 = choose, 1 = TMA-store epilogue (error if not possible), 2 = direct stores
 int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C,
-                     float *D, int bn, void *stream) {
+                     float *D, int bn, int store_mode, void *stream) {
     KO_REQUIRE(fmt == 0 || fmt == 1, KO_ERR_INVALID_ARG, "gemm: fmt must be 0 (f16) or 1 (bf16)");
     KO_REQUIRE(M >= 0 && N >= 0 && K >= 0, KO_ERR_INVALID_ARG, "gemm: negative shape {%lld,%lld,%lld}", (long long)M,
                (long long)N, (long long)K);
@@ -105,9 +111,17 @@ int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A
     }
     KO_REQUIRE(bn == 64 || bn == 128 || bn == 256, KO_ERR_INVALID_ARG, "gemm: tile width %d not in {64,128,256}", bn);
 
-    alignas(64) CUtensorMap map_a, map_b;
+    alignas(64) CUtensorMap map_a, map_b, map_d;
     if (int st = make_map(encode, &map_a, fmt, A, M, K, ko::tc::kBM)) return st;
     if (int st = make_map(encode, &map_b, fmt, B, N, K, bn)) return st;
+    // TMA-store epilogue when D has a 16-byte pitch and nothing is added to it
+    const bool tma_store = store_mode != 2 && C == nullptr && N % 4 == 0 && ko::aligned16(D);
+    KO_REQUIRE(store_mode != 1 || tma_store, KO_ERR_SHAPE, "gemm: the TMA-store epilogue needs C == NULL, N %% 4 == 0 and a 16-byte aligned D");
+    if (tma_store) {
+        if (int st = make_store_map(encode, &map_d, D, M, N)) return st;
+    } else {
+        map_d = map_a;  // unused by the direct-store epilogue
+    }
 
     ko::tc::GemmParams p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
@@ -115,20 +129,20 @@ int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A
     if (int st = ko::device_status_word(0, &p.status)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (bn) {
-        case 64: return launch<64>(map_a, map_b, p, info.sm_count, s);
-        case 128: return launch<128>(map_a, map_b, p, info.sm_count, s);
-        default: return launch<256>(map_a, map_b, p, info.sm_count, s);
+        case 64: return tma_store ? launch<64, true>(map_a, map_b, map_d, p, info.sm_count, s) : launch<64, false>(map_a, map_b, map_d, p, info.sm_count, s);
+        case 128: return tma_store ? launch<128, true>(map_a, map_b, map_d, p, info.sm_count, s) : launch<128, false>(map_a, map_b, map_d, p, info.sm_count, s);
+        default: return tma_store ? launch<256, true>(map_a, map_b, map_d, p, info.sm_count, s) : launch<256, false>(map_a, map_b, map_d, p, info.sm_count, s);
     }
 }
 
 int ko_gemm_f16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C, float *D,
                     void *stream) {
-    return ko_gemm_tc_tuned(0, M, N, K, A, B, C, D, 0, stream);
+    return ko_gemm_tc_tuned(0, M, N, K, A, B, C, D, 0, 0, stream);
 }
 
 int ko_gemm_bf16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C, float *D,
                      void *stream) {
-    return ko_gemm_tc_tuned(1, M, N, K, A, B, C, D, 0, stream);
+    return ko_gemm_tc_tuned(1, M, N, K, A, B, C, D, 0, 0, stream);
 }
 
 }  // extern "C"

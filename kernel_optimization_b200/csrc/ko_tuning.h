@@ -32,9 +32,10 @@ int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int
  * split_k: K slices of variant 4 (0 = choose, 1 = none) */
 int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
                        int variant, int split_k, void *stream);
-/* fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns of D per tile */
+/* fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns of D per tile;
+ * store_mode: 0 = choose, 1 = TMA-store epilogue (KO_ERR_SHAPE when not possible), 2 = direct stores */
 int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C,
-                     float *D, int bn, void *stream);
+                     float *D, int bn, int store_mode, void *stream);
 
 #ifdef __cplusplus
 }

@@ -71,7 +71,7 @@ TUNING_PROTOTYPES = {
     "ko_layernorm_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),
     "ko_layernorm_bf16_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),
     "ko_sgemm_f32_tuned": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _int, _vp]),
-    "ko_gemm_tc_tuned": (_int, [_int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),
+    "ko_gemm_tc_tuned": (_int, [_int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _int, _vp]),
 }
 
 _lib = None

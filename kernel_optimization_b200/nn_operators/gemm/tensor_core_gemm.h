@@ -51,8 +51,11 @@ struct TileConfig {
     static constexpr int kStages = BN >= 256 ? 4 : 6;
     static constexpr int kTmemCols = 2 * BN;  // double-buffered FP32 accumulator (power of two >= 32)
     static constexpr int kBarrierBytes = 256;
+    // epilogue staging for TMA stores: per epilogue warp two 32-row x 32-column FP32 boxes (4 KB each)
+    static constexpr int kStoreBoxBytes = 32 * 32 * 4;
+    static constexpr int kStoreBytes = 4 * 2 * kStoreBoxBytes;
     // + 1024 so the stage ring can be aligned to the 1024-byte swizzle period
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBarrierBytes + 1024;
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN must keep 2*BN a power of two <= 512");
 };
 
@@ -69,6 +72,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+// TMA 2-D tile store from this CTA's shared memory (bulk async-group completion)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until at most N of this thread's bulk groups are still READING their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -153,18 +166,21 @@ struct GemmParams {
     int fmt;          // 0 = F16, 1 = BF16
 };
 
-template <int BN>
+// kTmaStore: D is written by TMA stores staged through shared memory (needs N % 4 == 0, 16-byte aligned D,
+// no C operand); otherwise every thread stores its row segment directly (and adds C when given)
+template <int BN, bool kTmaStore>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
     using Cfg = TileConfig<BN>;
     extern __shared__ uint8_t ko_tc_smem_raw[];
     // stage ring on a 1024-byte boundary (swizzle period), barriers behind it
     const uint32_t raw = smem_u32(ko_tc_smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;
     uint8_t *ring_ptr = ko_tc_smem_raw + (ring - raw);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(ring_ptr + Cfg::kStages * Cfg::kStageBytes);
-    const uint32_t bar_base = ring + Cfg::kStages * Cfg::kStageBytes;
+    const uint32_t store_base = ring + Cfg::kStages * Cfg::kStageBytes;  // 1024-byte aligned
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring_ptr + Cfg::kStages * Cfg::kStageBytes + Cfg::kStoreBytes);
+    const uint32_t bar_base = store_base + Cfg::kStoreBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
     auto acc_ready_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + a); };
@@ -193,6 +209,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         fence_proxy_async();
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
+        if (kTmaStore) prefetch_tensormap(&map_d);
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
     tc_fence_before();
@@ -293,6 +310,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_after();
             const int row = tm * kBM + quad * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+            if constexpr (kTmaStore) {
+                // registers -> swizzled shared box (row = lane, 8 chunks of 16 B, chunk j stored at j ^ (row & 7):
+                // conflict-free, and exactly the 128-byte swizzle the store's tensor map undoes) -> TMA store
+                const int ep_warp = warp - 2;
+                const int row_base = tm * kBM + quad * 32;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    float v[32];
+                    tmem_ld_32x32(t_row + c0, v);
+                    const uint32_t box = store_base + (uint32_t)(ep_warp * 2 + ((c0 >> 5) & 1)) * Cfg::kStoreBoxBytes;
+                    if (lane == 0) bulk_wait_group_read<1>();  // the store issued from this box two chunks ago has read it
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t dst = box + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                                     "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                                     : "memory");
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    const int col = tn * BN + c0;
+                    if (lane == 0) {
+                        // rows / columns beyond M / N are clipped by the map; a box that lies entirely outside is
+                        // skipped, but still closes a (then empty) group so that the two-deep box rotation holds
+                        if (row_base < p.M && col < p.N) tma_store_2d(&map_d, col, row_base, box);
+                        bulk_commit_group();
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 float v[32];
@@ -319,11 +366,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             }
+            }
             // the accumulator buffer may be overwritten once all four warps have read it
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_free_bar(acc));
         }
+        // shared memory must outlive the reads of the stores still in flight
+        if (kTmaStore && lane == 0) bulk_wait_group_read<0>();
+        __syncwarp();
     }
 
     tc_fence_before();

@@ -23,25 +23,25 @@ def _dev16(cuda, bits, kind):
     return cuda.from_numpy(bits.view(np.int16)).cuda().view(cuda.float16 if kind == "f16" else cuda.bfloat16)
 
 
-def _run(cuda, lib, kind, ab, bb, c=None, bn=0):
+def _run(cuda, lib, kind, ab, bb, c=None, bn=0, store_mode=0):
     M, K = ab.shape
     N = bb.shape[0]
     ad, bd = _dev16(cuda, ab, kind), _dev16(cuda, bb, kind)
     cd = None if c is None else cuda.from_numpy(c).cuda()
     dd = cuda.full((M, N), float("nan"), dtype=cuda.float32, device="cuda")
     rc = lib.ko_gemm_tc_tuned(0 if kind == "f16" else 1, M, N, K, ad.data_ptr(), bd.data_ptr(),
-                              None if cd is None else cd.data_ptr(), dd.data_ptr(), bn, cuda.cuda.current_stream().cuda_stream)
+                              None if cd is None else cd.data_ptr(), dd.data_ptr(), bn, store_mode, cuda.cuda.current_stream().cuda_stream)
     assert rc == 0, lib.ko_last_error_string()
     cuda.cuda.synchronize()
     assert lib.ko_poll_device_status() == 0, lib.ko_last_error_string()
     return dd.cpu().numpy()
 
 
-def _case(cuda, lib, oracle, kind, M, N, K, with_c=False, bn=0, seed=3):
+def _case(cuda, lib, oracle, kind, M, N, K, with_c=False, bn=0, seed=3, store_mode=0):
     to_bits, from_bits = _bits(oracle, kind)
     ab, bb = to_bits(oracle.fill_uniform((M, K), seed, 0)), to_bits(oracle.fill_uniform((N, K), seed, 1))
     c = oracle.fill_uniform((M, N), seed, 2) if with_c else None
-    d = _run(cuda, lib, kind, ab, bb, c, bn)
+    d = _run(cuda, lib, kind, ab, bb, c, bn, store_mode)
     want = oracle.gemm_tn_f64(from_bits(ab), from_bits(bb), c)
     err = oracle.rel_frobenius(d, want)
     assert err <= TOL_FRO and err <= tight(K), (kind, M, N, K, bn, err)
@@ -62,6 +62,14 @@ def test_tails_and_multiple_tiles(cuda, lib, oracle, kind, M, N, K):
     for bn in (0, 128):
         _case(cuda, lib, oracle, kind, M, N, K, bn=bn)
     _case(cuda, lib, oracle, kind, M, N, K, with_c=True)
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_both_epilogues_give_the_same_bits(cuda, lib, oracle, bn):
+    for M, N, K in ((128, 256, 64), (1000, 520, 200), (129, 260, 136), (4096, 1024, 128)):
+        d_tma = _case(cuda, lib, oracle, "bf16", M, N, K, bn=bn, store_mode=1)
+        d_direct = _case(cuda, lib, oracle, "bf16", M, N, K, bn=bn, store_mode=2)
+        assert np.array_equal(d_tma, d_direct)
 
 
 def test_n_not_multiple_of_four_takes_scalar_stores(cuda, lib, oracle):
