@@ -44,7 +44,7 @@ WORKLOAD = ("bert_base_row_ops: softmax f32 [196608,128] N(0,4) seed 0 + layerno
             "seed 1, per GPU; rows sharded across GPUs, no collective")
 # DRAM bytes per launch of the softmax kernel on this workload from the ncu capture summarised in
 # profiles/softmax_warp_kernel_196608x128.txt (dram__bytes_read.sum + dram__bytes_write.sum)
-SOFTMAX_NCU_TRAFFIC_BYTES = None
+SOFTMAX_NCU_TRAFFIC_BYTES = 145_612_800
 
 
 def measured_peaks():
@@ -383,6 +383,74 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+CASES = {
+    "sgemm_2048": "FP32 SGEMM 2048^3 (48 MB of operands)",
+    "sgemm_1024": "FP32 SGEMM 1024^3 (BASELINE config 3)",
+    "gemm_bf16_4096": "BF16 tcgen05 GEMM 4096^3 (BASELINE config 4)",
+    "gemm_bf16_ffn": "BF16 tcgen05 GEMM 16384x3072x768 (BASELINE config 4, FFN shape)",
+    "softmax_c5_shard": "softmax FP32 [196608,512] with the causal -1e4 pattern (1/8 of BASELINE config 5)",
+    "layernorm_bf16_c5_shard": "LayerNorm BF16 [32768,4096] (1/8 of BASELINE config 5)",
+}
+
+
+def run_case(args):
+    """One operator case, a few launches, one JSON line: small enough for an ncu capture."""
+    import torch
+
+    import kernel_optimization_b200 as ko
+    from kernel_optimization_b200 import native
+
+    lib = native.lib()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    s = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    name = args.case
+    if name.startswith("sgemm"):
+        n = int(name.split("_")[1])
+        a = torch.from_numpy(ko.fill_uniform((n, n), 2, 0)).to(dev)
+        b = torch.from_numpy(ko.fill_uniform((n, n), 2, 1)).to(dev)
+        d = torch.empty((n, n), device=dev)
+        launch = lambda: native.check(lib.ko_sgemm_f32(n, n, n, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s()), name)  # noqa: E731
+        work, unit = 2.0 * n ** 3, "TFLOP/s"
+    elif name.startswith("gemm_bf16"):
+        M, N, K = (4096, 4096, 4096) if name.endswith("4096") else (16384, 3072, 768)
+        a = torch.from_numpy(ko.fill_uniform((M, K), 3, 0, dtype=2).view(np.int16)).to(dev)
+        b = torch.from_numpy(ko.fill_uniform((N, K), 3, 1, dtype=2).view(np.int16)).to(dev)
+        d = torch.empty((M, N), device=dev)
+        launch = lambda: native.check(lib.ko_gemm_bf16_f32(M, N, K, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s()), name)  # noqa: E731
+        work, unit = 2.0 * M * N * K, "TFLOP/s"
+    elif name == "softmax_c5_shard":
+        rows, cols = 196608, 512
+        x = ko.fill_normal((rows, cols), 4, 0, 0.0, 2.0)
+        ko.fill_causal_mask_(x, 0, 512, -1e4)
+        xd = torch.from_numpy(x).to(dev)
+        yd = torch.empty_like(xd)
+        launch = lambda: native.check(lib.ko_softmax_f32(xd.data_ptr(), yd.data_ptr(), rows, cols, s()), name)  # noqa: E731
+        work, unit = 2.0 * rows * cols * 4, "GB/s"
+    else:
+        rows, cols = 32768, 4096
+        xd = torch.from_numpy(ko.fill_normal((rows, cols), 4, 0, dtype=2).view(np.int16)).to(dev)
+        g = torch.from_numpy(ko.fill_uniform((cols,), 4, 1, 0.5, 1.5, dtype=2).view(np.int16)).to(dev)
+        b = torch.from_numpy(ko.fill_normal((cols,), 4, 2, 0.0, 0.1, dtype=2).view(np.int16)).to(dev)
+        yd = torch.empty_like(xd)
+        launch = lambda: native.check(lib.ko_layernorm_bf16(xd.data_ptr(), yd.data_ptr(), rows, cols, LN_EPS, g.data_ptr(), b.data_ptr(), 0, s()), name)  # noqa: E731
+        work, unit = 2.0 * rows * cols * 2, "GB/s"
+    for _ in range(max(args.warmup, 1)):
+        launch()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    native.check(lib.ko_poll_device_status(), "ko_poll_device_status")
+    ms = e0.elapsed_time(e1) / args.steps
+    scale = 1e12 if unit == "TFLOP/s" else 1e9
+    print(json.dumps({"case": name, "what": CASES[name], "us_per_launch": ms * 1e3, "value": work / (ms * 1e-3) / scale,
+                      "unit": unit, "steps": args.steps, "note": "same buffers every launch (L2-warm for small cases)"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -393,7 +461,12 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
     ap.add_argument("--row-sets", type=int, default=0,
                     help="buffer sets to rotate over (0 = default 4/8); 1 keeps a profiler capture small")
+    ap.add_argument("--case", choices=sorted(CASES), default=None,
+                    help="run a single operator case a few times instead of the benchmark (for profiler captures)")
     args = ap.parse_args()
+    if args.case:
+        run_case(args)
+        return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)
