@@ -112,11 +112,19 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------------
 # CPU check path (the oracle's FP32 ports, all host threads): the reference arm and the cpu_baseline leg
 # --------------------------------------------------------------------------------------------------
-def cpu_port_step(oracle, xs, xl, g, b):
-    """One pass of the FP32 ports over the sample; returns seconds."""
+def host_cores() -> int:
+    """Cores this process may run on (torchrun pins OMP_NUM_THREADS to 1, so ask the scheduler instead)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_port_step(oracle, xs, xl, g, b, threads):
+    """One pass of the FP32 ports over the sample on `threads` host threads; returns seconds."""
     t0 = time.perf_counter()
-    oracle.softmax_f32(xs)
-    oracle.layernorm_f32(xl, LN_EPS, g, b)
+    oracle.softmax_f32(xs, threads=threads)
+    oracle.layernorm_f32(xl, LN_EPS, g, b, threads=threads)
     return time.perf_counter() - t0
 
 
@@ -135,13 +143,13 @@ def run_reference_arm(args):
         return  # the CPU arm runs on rank 0 only
     from oracle import ko_oracle as oracle
 
-    cores = oracle.max_threads()
+    cores = host_cores()
     sample, sample_bytes, what = cpu_sample(oracle, 8)
     for _ in range(max(args.warmup, 1)):
-        cpu_port_step(oracle, *sample)
+        cpu_port_step(oracle, *sample, cores)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_port_step(oracle, *sample)
+        cpu_port_step(oracle, *sample, cores)
     elapsed = time.perf_counter() - t0
     gbs = sample_bytes * args.steps / elapsed / 1e9
     line = {
@@ -156,7 +164,7 @@ def run_reference_arm(args):
                 "(softmax.h:32-58, layernorm.h:13-50/:184-198 with the merge defect removed) on all host threads; "
                 "ms_per_step is scaled from the sample to the full per-GPU workload",
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -354,10 +362,11 @@ def run_gpu_arm(args):
         from oracle import ko_oracle as oracle
 
         sample, sample_bytes, what = cpu_sample(oracle, 1)
-        cpu_port_step(oracle, *sample)
+        cores = host_cores()
+        cpu_port_step(oracle, *sample, cores)
         reps = 5
-        best = min(cpu_port_step(oracle, *sample) for _ in range(reps))
-        cpu_baseline = {"value": sample_bytes / best / 1e9, "unit": UNIT, "cores": oracle.max_threads(), "kind": "port",
+        best = min(cpu_port_step(oracle, *sample, cores) for _ in range(reps))
+        cpu_baseline = {"value": sample_bytes / best / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
                         "sample": f"the full per-GPU workload (all rows of both operators), FP32 ports, best of {reps} passes"}
 
     if rank == 0:
@@ -378,7 +387,139 @@ def run_gpu_arm(args):
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks.summary(),
             "parity": parity, "gemm": gemm, "reference_kernels_on_b200": ref_rows,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------------------
+# BASELINE config 5: the scaled sweep, strong scaling (the totals are fixed, every rank takes 1/N)
+# --------------------------------------------------------------------------------------------------
+C5_SOFTMAX_ROWS, C5_SOFTMAX_COLS = 8 * 196608, 512
+C5_LN_ROWS, C5_LN_COLS = 262144, 4096
+C5_M, C5_N, C5_K = 65536, 8192, 8192
+
+
+def run_scaled(args):
+    """softmax FP32 [8x196608, 512] causal -1e4, LayerNorm BF16 [262144, 4096], BF16 GEMM 65536 x 8192 x 8192
+    (B replicated by one NCCL broadcast, untimed), seed 4; rows / M-blocks sharded over the ranks."""
+    import torch
+    import torch.distributed as dist
+
+    import kernel_optimization_b200 as ko
+    from kernel_optimization_b200 import native, sharding
+
+    lib = native.lib()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    hbm_peak, tc_peak, peak_kind = measured_peaks()
+
+    def stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, iters, warm):
+        for _ in range(warm):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        barrier()
+        return sharding.max_over_ranks(e0.elapsed_time(e1), dev) / iters
+
+    from oracle import ko_oracle as oracle  # checker for the sampled rows below
+
+    out = {}
+    parity = {}
+    rng = np.random.default_rng(4 + rank)
+    # ---- softmax: shard boundaries on multiples of 512 keep every causal block on one GPU
+    sh = sharding.row_shard(C5_SOFTMAX_ROWS, C5_SOFTMAX_COLS, rank, world, multiple_of=512)
+    x = ko.fill_normal((sh.rows, sh.cols), 4, 0, 0.0, 2.0, elem_offset=sh.elem_offset)
+    ko.fill_causal_mask_(x, sh.begin, 512, -1e4)
+    xd = torch.from_numpy(x).to(dev)
+    yd = torch.empty_like(xd)
+    ms = timed(lambda: native.check(lib.ko_softmax_f32(xd.data_ptr(), yd.data_ptr(), sh.rows, sh.cols, stream()), "softmax"),
+               args.steps, args.warmup)
+    total = 2.0 * C5_SOFTMAX_ROWS * C5_SOFTMAX_COLS * 4
+    out["softmax_f32_causal"] = {"gbs": total / (ms * 1e-3) / 1e9, "ms": ms, "of_peak_per_gpu": total / world / (ms * 1e-3) / 1e9 / hbm_peak,
+                                 "bytes": total, "rows_per_gpu": sh.rows}
+    pick = np.unique(np.r_[0:512, sh.rows - 512:sh.rows, rng.integers(0, sh.rows, 4096)])
+    got = yd[torch.from_numpy(pick).to(dev)].cpu().numpy()
+    parity["softmax_max_abs"] = oracle.max_abs_err(got, oracle.softmax_f64(x[pick]))
+    parity["softmax_rowsum"] = oracle.max_rowsum_err(got)
+    del x, xd, yd
+    # ---- LayerNorm BF16
+    sh = sharding.row_shard(C5_LN_ROWS, C5_LN_COLS, rank, world)
+    xb = ko.fill_normal((sh.rows, sh.cols), 4, 1, 0.0, 1.0, dtype=2, elem_offset=sh.elem_offset)
+    gb, bb = ko.fill_uniform((sh.cols,), 4, 2, 0.5, 1.5, dtype=2), ko.fill_normal((sh.cols,), 4, 3, 0.0, 0.1, dtype=2)
+    to_dev = lambda a: torch.from_numpy(a.view(np.int16)).to(dev)  # noqa: E731
+    xd, gd, bd = to_dev(xb), to_dev(gb), to_dev(bb)
+    yd = torch.empty_like(xd)
+    ms = timed(lambda: native.check(lib.ko_layernorm_bf16(xd.data_ptr(), yd.data_ptr(), sh.rows, sh.cols, LN_EPS, gd.data_ptr(),
+                                                          bd.data_ptr(), 0, stream()), "layernorm"), args.steps, args.warmup)
+    total = 2.0 * C5_LN_ROWS * C5_LN_COLS * 2
+    out["layernorm_bf16"] = {"gbs": total / (ms * 1e-3) / 1e9, "ms": ms, "of_peak_per_gpu": total / world / (ms * 1e-3) / 1e9 / hbm_peak,
+                             "bytes": total, "rows_per_gpu": sh.rows}
+    pick = np.unique(np.r_[0:64, sh.rows - 64:sh.rows, rng.integers(0, sh.rows, 512)])
+    got = oracle.from_bf16_bits(yd[torch.from_numpy(pick).to(dev)].cpu().numpy().view(np.uint16))
+    want = oracle.layernorm_f64(oracle.from_bf16_bits(xb[pick]), LN_EPS, oracle.from_bf16_bits(gb), oracle.from_bf16_bits(bb))
+    parity["layernorm_bf16_max_rel"] = oracle.max_rel_err(got, want)
+    del xb, xd, yd
+    # ---- BF16 GEMM, M-sharded, B broadcast once (timed separately)
+    sh = sharding.row_shard(C5_M, C5_K, rank, world, multiple_of=128)
+    ab = ko.fill_uniform((sh.rows, C5_K), 4, 4, dtype=2, elem_offset=sh.elem_offset)
+    ad = to_dev(ab)
+    bh = ko.fill_uniform((C5_N, C5_K), 4, 5, dtype=2) if rank == 0 else None
+    bd = to_dev(bh) if rank == 0 else torch.empty((C5_N, C5_K), dtype=torch.int16, device=dev)
+    barrier()
+    t0 = time.perf_counter()
+    sharding.replicate_from_rank0(bd)
+    barrier()
+    bcast_ms = (time.perf_counter() - t0) * 1e3
+    dd = torch.empty((sh.rows, C5_N), device=dev)
+    gsteps = max(2, min(args.steps, 5))
+    ms = timed(lambda: native.check(lib.ko_gemm_bf16_f32(sh.rows, C5_N, C5_K, ad.data_ptr(), bd.data_ptr(), None, dd.data_ptr(), stream()),
+                                    "gemm"), gsteps, 1)
+    flops = 2.0 * C5_M * C5_N * C5_K
+    a_t, b_t = ad.view(torch.bfloat16), bd.view(torch.bfloat16)
+    ms_c = timed(lambda: torch.mm(a_t, b_t.t(), out_dtype=torch.float32), gsteps, 1)
+    out["gemm_bf16_f32"] = {"tflops": flops / (ms * 1e-3) / 1e12, "ms": ms, "cublas_tflops": flops / (ms_c * 1e-3) / 1e12, "vs_cublas": ms_c / ms,
+                            "of_measured_bf16_peak_per_gpu": flops / world / (ms * 1e-3) / 1e12 / tc_peak, "flops": flops,
+                            "b_broadcast_ms": bcast_ms, "b_bytes": C5_N * C5_K * 2, "m_per_gpu": sh.rows}
+    native.check(lib.ko_poll_device_status(), "ko_poll_device_status")
+    rows = np.unique(np.r_[0:8, sh.rows - 8:sh.rows, rng.integers(0, sh.rows, 16)])
+    bfull = oracle.from_bf16_bits(bd.cpu().numpy().view(np.uint16))
+    want = oracle.gemm_tn_f64(oracle.from_bf16_bits(ab[rows]), bfull)
+    parity["gemm_rel_fro_sampled_rows"] = oracle.rel_frobenius(dd[torch.from_numpy(rows).to(dev)].cpu().numpy(), want)
+    gathered = [None] * world
+    if world > 1:
+        dist.all_gather_object(gathered, parity)
+    else:
+        gathered = [parity]
+    if rank == 0:
+        worst = {k: max(g[k] for g in gathered) for k in parity}
+        row_bytes = out["softmax_f32_causal"]["bytes"] + out["layernorm_bf16"]["bytes"]
+        row_ms = out["softmax_f32_causal"]["ms"] + out["layernorm_bf16"]["ms"]
+        emit({"metric": "scaled sweep (BASELINE config 5): softmax+layernorm HBM throughput", "value": row_bytes / (row_ms * 1e-3) / 1e9,
+              "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": row_ms, "higher_is_better": True,
+              "scaling": "strong", "vs_baseline": None, "dtype": "f32 softmax / bf16 layernorm (f32 statistics) / bf16 gemm (f32 accumulate)",
+              "data": "synthetic (seeded Philox4x32-10, seed 4)",
+              "config": {"workload": "config5_scaled: softmax f32 [1572864,512] causal -1e4 + layernorm bf16 [262144,4096] + bf16 gemm 65536x8192x8192, "
+                                     "rows / M-blocks sharded, B replicated by one untimed NCCL broadcast",
+                         "l2": "every per-GPU operand is larger than the 126 MB L2", "parallelism": f"rows and M-blocks x{world}, no data-path collective"},
+              "ops": out, "parity_worst_over_ranks": worst, "peak_source": peak_kind})
     if world > 1:
         dist.destroy_process_group()
 
@@ -447,8 +588,8 @@ def run_case(args):
     native.check(lib.ko_poll_device_status(), "ko_poll_device_status")
     ms = e0.elapsed_time(e1) / args.steps
     scale = 1e12 if unit == "TFLOP/s" else 1e9
-    print(json.dumps({"case": name, "what": CASES[name], "us_per_launch": ms * 1e3, "value": work / (ms * 1e-3) / scale,
-                      "unit": unit, "steps": args.steps, "note": "same buffers every launch (L2-warm for small cases)"}), flush=True)
+    emit({"case": name, "what": CASES[name], "us_per_launch": ms * 1e3, "value": work / (ms * 1e-3) / scale,
+          "unit": unit, "steps": args.steps, "note": "same buffers every launch (L2-warm for small cases)"})
 
 
 def main():
@@ -461,15 +602,42 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
     ap.add_argument("--row-sets", type=int, default=0,
                     help="buffer sets to rotate over (0 = default 4/8); 1 keeps a profiler capture small")
+    ap.add_argument("--workload", choices=["bert_base", "scaled"], default="bert_base",
+                    help="bert_base: configs 1+2 per GPU, weak scaling (default); scaled: config 5 totals, strong scaling")
     ap.add_argument("--case", choices=sorted(CASES), default=None,
                     help="run a single operator case a few times instead of the benchmark (for profiler captures)")
     args = ap.parse_args()
+    # stdout carries exactly one JSON line: park the real stdout and point fd 1 at stderr meanwhile, so
+    # banners printed by libraries (NCCL's version line, for one) cannot end up in front of it
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        _dispatch(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    for line in _RESULT_LINES:
+        print(line, flush=True)
+
+
+_RESULT_LINES: list = []
+
+
+def emit(line: dict) -> None:
+    _RESULT_LINES.append(json.dumps(line))
+
+
+def _dispatch(args):
     if args.case:
         run_case(args)
         return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "scaled":
+        run_scaled(args)
     else:
         run_gpu_arm(args)
 

@@ -203,7 +203,8 @@ struct Welford {
 __device__ __forceinline__ Welford welford_merge(const Welford &a, const Welford &b) {
     Welford r;
     r.n = a.n + b.n;
-    const float w = r.n > 0.f ? b.n / r.n : 0.f;
+    float w = 0.5f;  // equal counts (the common case) need no division
+    if (a.n != b.n) w = r.n > 0.f ? b.n / r.n : 0.f;
     const float delta = b.mean - a.mean;
     r.mean = fmaf(delta, w, a.mean);
     r.m2 = a.m2 + b.m2 + delta * delta * a.n * w;
@@ -244,6 +245,32 @@ __device__ __forceinline__ float rcp_approx(float x) {
 __device__ __forceinline__ float warp_redux_max(float v) {
     float r;
     asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// packed FP32 pairs (sm_100a: add/mul/fma on two IEEE FP32 values per instruction)
+// ---------------------------------------------------------------------------------------------
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pair_of(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void pair_split(f32x2 v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 pair_add(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 pair_mul(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 pair_fma(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
     return r;
 }
 

@@ -60,6 +60,25 @@ int launch_block_vecs(int vecs, const Args<T> &a, long long grid_cap, cudaStream
     return launch_block<T, 8, kThreads>(a, grid_cap, s);
 }
 
+template <typename T, int kVecs, int kThreads>
+int launch_resident(const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
+    const long long cap = grid_cap > 0 ? grid_cap : (long long)sm_count * (kThreads <= 256 ? 8 : (kThreads <= 512 ? 4 : 2));
+    const unsigned grid = ko::clamp_grid(a.rows, cap);
+    if (a.gamma || a.beta)
+        ko::layernorm_resident_kernel<T, kVecs, kThreads, true><<<grid, kThreads, 0, s>>>(a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+    else
+        ko::layernorm_resident_kernel<T, kVecs, kThreads, false><<<grid, kThreads, 0, s>>>(a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+    KO_CHECK_LAUNCH("layernorm_resident_kernel");
+    return KO_OK;
+}
+
+template <typename T, int kThreads>
+int launch_resident_vecs(int vecs, const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
+    if (vecs <= 1) return launch_resident<T, 1, kThreads>(a, grid_cap, sm_count, s);
+    if (vecs <= 2) return launch_resident<T, 2, kThreads>(a, grid_cap, sm_count, s);
+    return launch_resident<T, 4, kThreads>(a, grid_cap, sm_count, s);
+}
+
 template <typename T, bool kStaged>
 int dispatch_rows(int vecs, int rpw, const Args<T> &a, const ko_row_knobs_t &k, const DeviceInfo &info, cudaStream_t s,
                   bool *used) {
@@ -85,7 +104,7 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
     if (a.rows == 0 || a.cols == 0) return KO_OK;
     KO_REQUIRE(a.in != nullptr && a.out != nullptr, KO_ERR_INVALID_ARG, "layernorm: NULL pointer");
     const ko_row_knobs_t k = knobs ? *knobs : ko_row_knobs_t{};
-    KO_REQUIRE(k.tier >= 0 && k.tier <= 4, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
+    KO_REQUIRE(k.tier >= 0 && k.tier <= 5, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
     KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
                "layernorm: block %d must be a multiple of 32, <= 1024", k.block);
     DeviceInfo info;
@@ -102,9 +121,30 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
     int tier = k.tier;
     if (tier == 0) {
         if (!vec_ok) tier = 3;
-        else if (warp_ok) tier = 1;  // measured faster than the staged tier at every BASELINE shape
+        // measured on B200: the warp tier wins while a lane holds at most 8 vectors of 16-bit data
+        // (16 of FP32); beyond that the resident tier (row unpacked once, packed FP32 math) is faster
+        else if (warp_ok && (sizeof(T) == 4 || nvec <= 256)) tier = 1;
+        else if (nvec <= 1024 * 4) tier = 5;
         else if (nvec <= 1024 * kMaxVecsPerThread) tier = 2;
         else tier = 3;
+    }
+    if (tier == 5) {
+        // resident tier: at most 4 vectors per thread
+        KO_REQUIRE(vec_ok && nvec <= 1024 * 4, KO_ERR_SHAPE, "layernorm: the resident tier needs 16-byte aligned rows of at most 4096 vectors");
+        int threads = k.block;
+        if (threads == 0) {
+            threads = 256;  // two vectors per thread at 4096 BF16 columns
+            while (threads < 1024 && nvec > threads * 4) threads *= 2;
+        }
+        KO_REQUIRE(nvec <= threads * 4, KO_ERR_SHAPE, "layernorm: %d threads hold at most %d vectors per row", threads, threads * 4);
+        const int per_thread = (nvec + threads - 1) / threads;
+        switch (threads) {
+            case 128: return launch_resident_vecs<T, 128>(per_thread, a, k.grid_cap, info.sm_count, s);
+            case 256: return launch_resident_vecs<T, 256>(per_thread, a, k.grid_cap, info.sm_count, s);
+            case 512: return launch_resident_vecs<T, 512>(per_thread, a, k.grid_cap, info.sm_count, s);
+            case 1024: return launch_resident_vecs<T, 1024>(per_thread, a, k.grid_cap, info.sm_count, s);
+            default: return ko::fail(KO_ERR_INVALID_ARG, "layernorm: resident tier needs 128/256/512/1024 threads, got %d", threads);
+        }
     }
     if (tier == 4) {
         KO_REQUIRE(warp_ok, KO_ERR_SHAPE, "layernorm: the staged tier needs 16-byte aligned rows of at most 512 vectors");

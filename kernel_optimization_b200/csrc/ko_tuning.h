@@ -11,10 +11,11 @@ extern "C" {
 
 /* knobs of the row operators; pass NULL for all defaults */
 typedef struct ko_row_knobs {
-    int tier;            /* 0 = choose, 1 = warp, 2 = block, 3 = stream (scalar), 4 = staged (TMA ring) */
+    int tier;            /* 0 = choose, 1 = warp, 2 = block, 3 = stream (scalar), 4 = staged (TMA ring),
+                            5 = resident (LayerNorm only: persistent blocks, packed FP32 math) */
     int rows_per_warp;   /* warp / staged tier: independent row slots a warp processes together (a slot is
                             one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows) */
-    int block;           /* warp tier: threads per block (<= 256); block tier: threads per row (128..1024) */
+    int block;           /* warp tier: threads per block (<= 256); block / resident tier: threads per row (128..1024) */
     int64_t grid_cap;    /* warp / block / stream tier: upper bound on the grid (0 = one pass per warp) */
     int stage_rows;      /* staged tier: rows per bulk copy (0 = about 16-32 KB) */
     int stages;          /* staged tier: ring depth (0 = fill about 100 KB) */

@@ -14,6 +14,8 @@
 //                (common/row_pipeline.h);
 //   warp tier    one warp owns kRows consecutive rows per step, rows in registers;
 //   block tier   one thread block per row, row in registers, one shared-memory exchange;
+//   resident tier persistent blocks for long rows: gamma/beta held in registers, packed FP32 math,
+//                next row prefetched;
 //   stream tier  one thread block per row, two passes over global memory, scalar accesses, any
 //                column count and alignment.
 // y = ((x - mean) * rstd) * gamma + beta, gamma/beta optional, in the I/O element type.
@@ -40,6 +42,16 @@ struct RowIo<float> {
         f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w;
     }
     __device__ __forceinline__ static Raw pack(const float (&f)[4]) { return make_float4(f[0], f[1], f[2], f[3]); }
+    __device__ __forceinline__ static void unpack_pairs(const Raw &r, f32x2 *p) {
+        p[0] = pair_of(r.x, r.y);
+        p[1] = pair_of(r.z, r.w);
+    }
+    __device__ __forceinline__ static Raw pack_pairs(const f32x2 *p) {
+        Raw r;
+        pair_split(p[0], r.x, r.y);
+        pair_split(p[1], r.z, r.w);
+        return r;
+    }
     __device__ __forceinline__ static float to_float(float v) { return v; }
     __device__ __forceinline__ static float from_float(float v) { return v; }
 };
@@ -54,6 +66,18 @@ struct RowIo<__nv_bfloat16> {
     }
     __device__ __forceinline__ static Raw pack(const float (&f)[8]) {
         return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+    }
+    __device__ __forceinline__ static void unpack_pairs(const Raw &r, f32x2 *p) {
+        p[0] = pair_of(bf16_lo(r.x), bf16_hi(r.x));
+        p[1] = pair_of(bf16_lo(r.y), bf16_hi(r.y));
+        p[2] = pair_of(bf16_lo(r.z), bf16_hi(r.z));
+        p[3] = pair_of(bf16_lo(r.w), bf16_hi(r.w));
+    }
+    __device__ __forceinline__ static Raw pack_pairs(const f32x2 *p) {
+        float lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pair_split(p[i], lo[i], hi[i]);
+        return make_uint4(pack_bf16(lo[0], hi[0]), pack_bf16(lo[1], hi[1]), pack_bf16(lo[2], hi[2]), pack_bf16(lo[3], hi[3]));
     }
     __device__ __forceinline__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
@@ -309,6 +333,129 @@ __device__ __forceinline__ void layernorm_block_tier(const T *in, T *out, long l
 }
 
 // ---------------------------------------------------------------------------------------------
+// resident tier: persistent blocks, one row per block at a time, everything in registers
+// ---------------------------------------------------------------------------------------------
+// For rows too long for a single warp's registers (e.g. 4096 BF16 columns).  A thread always owns the
+// same columns, so gamma and beta are unpacked to FP32 pairs once, outside the row loop; a row is
+// unpacked once and its three passes (sum, squared deviations, normalise) run on packed FP32 pairs
+// (add/mul/fma.f32x2); the next row's loads are issued before the current row is processed.
+template <int kThreads>
+__device__ __forceinline__ Welford block_allreduce_welford_fixed(Welford w, float *s_exchange) {
+    constexpr int kWarps = kThreads / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    w = warp_allreduce_welford(w);
+    __syncthreads();
+    if (lane == 0) {
+        s_exchange[warp] = w.n;
+        s_exchange[32 + warp] = w.mean;
+        s_exchange[64 + warp] = w.m2;
+    }
+    __syncthreads();
+    Welford t;
+    t.n = lane < kWarps ? s_exchange[lane] : 0.f;
+    t.mean = lane < kWarps ? s_exchange[32 + lane] : 0.f;
+    t.m2 = lane < kWarps ? s_exchange[64 + lane] : 0.f;
+#pragma unroll
+    for (int m = kWarps / 2; m > 0; m >>= 1) {
+        Welford o;
+        o.n = __shfl_xor_sync(kFullMask, t.n, m);
+        o.mean = __shfl_xor_sync(kFullMask, t.mean, m);
+        o.m2 = __shfl_xor_sync(kFullMask, t.m2, m);
+        t = welford_merge(t, o);
+    }
+    t.mean = __shfl_sync(kFullMask, t.mean, 0);
+    t.m2 = __shfl_sync(kFullMask, t.m2, 0);
+    return t;
+}
+
+template <typename T, int kVecs, int kThreads, bool kAffine>
+__device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                        const T *gamma, const T *beta, int ddof, float *s_exchange) {
+    using Io = RowIo<T>;
+    using Raw = typename Io::Raw;
+    constexpr int kPer = Io::kPerVec, kPairsPerVec = kPer / 2;
+    const int nvec = cols / kPer;
+    const Raw *in_v = reinterpret_cast<const Raw *>(in);
+    Raw *out_v = reinterpret_cast<Raw *>(out);
+    int my_vecs = 0;
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) my_vecs += ((int)threadIdx.x + kThreads * j < nvec) ? 1 : 0;
+
+    f32x2 g2[kAffine ? kVecs * kPairsPerVec : 1], b2[kAffine ? kVecs * kPairsPerVec : 1];
+    if constexpr (kAffine) {
+        const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma), *beta_v = reinterpret_cast<const Raw *>(beta);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = threadIdx.x + kThreads * j;
+#pragma unroll
+            for (int q = 0; q < kPairsPerVec; ++q) {
+                g2[j * kPairsPerVec + q] = pair_of(1.f, 1.f);
+                b2[j * kPairsPerVec + q] = pair_of(0.f, 0.f);
+            }
+            if (v < nvec) {
+                if (gamma_v) Io::unpack_pairs(__ldg(gamma_v + v), g2 + j * kPairsPerVec);
+                if (beta_v) Io::unpack_pairs(__ldg(beta_v + v), b2 + j * kPairsPerVec);
+            }
+        }
+    }
+
+    Raw next[kVecs];
+    auto fetch = [&](long long row) {
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = threadIdx.x + kThreads * j;
+            if (row < rows && v < nvec) next[j] = ld_stream(in_v + row * nvec + v);
+            else next[j] = Raw{};
+        }
+    };
+    fetch(blockIdx.x);
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        f32x2 x2[kVecs * kPairsPerVec];
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) Io::unpack_pairs(next[j], x2 + j * kPairsPerVec);
+        fetch(row + gridDim.x);  // in flight while this row is processed
+
+        f32x2 acc = pair_of(0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < kVecs * kPairsPerVec; ++i) acc = pair_add(acc, x2[i]);  // padded vectors are zero
+        float lo, hi;
+        pair_split(acc, lo, hi);
+        Welford w;
+        w.n = (float)(my_vecs * kPer);
+        w.mean = my_vecs > 0 ? (lo + hi) / w.n : 0.f;
+        const f32x2 neg_local = pair_of(-w.mean, -w.mean);
+        f32x2 dev2 = pair_of(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            f32x2 part = pair_of(0.f, 0.f);
+#pragma unroll
+            for (int q = 0; q < kPairsPerVec; ++q) {
+                const f32x2 d = pair_add(x2[j * kPairsPerVec + q], neg_local);
+                part = pair_fma(d, d, part);
+            }
+            if (j < my_vecs) dev2 = pair_add(dev2, part);
+        }
+        pair_split(dev2, lo, hi);
+        w.m2 = lo + hi;
+        w = block_allreduce_welford_fixed<kThreads>(w, s_exchange);
+        const float rstd = rstd_from(w, cols, ddof, eps);
+        const f32x2 neg_mean = pair_of(-w.mean, -w.mean), rstd2 = pair_of(rstd, rstd);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = threadIdx.x + kThreads * j;
+            if (v >= nvec) continue;
+            f32x2 y2[kPairsPerVec];
+#pragma unroll
+            for (int q = 0; q < kPairsPerVec; ++q) {
+                const f32x2 t = pair_mul(pair_add(x2[j * kPairsPerVec + q], neg_mean), rstd2);
+                y2[q] = kAffine ? pair_fma(t, g2[j * kPairsPerVec + q], b2[j * kPairsPerVec + q]) : t;
+            }
+            st_stream(out_v + row * nvec + v, Io::pack_pairs(y2));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // stream tier: any cols / alignment; per-thread running Welford, two passes over global memory
 // ---------------------------------------------------------------------------------------------
 template <typename T>
@@ -358,6 +505,12 @@ __global__ void __launch_bounds__(kThreads) layernorm_block_kernel(const T *in, 
                                                                    float eps, const T *gamma, const T *beta, int ddof) {
     __shared__ float s_exchange[96];
     layernorm_block_tier<T, kVecs>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
+}
+template <typename T, int kVecs, int kThreads, bool kAffine>
+__global__ void __launch_bounds__(kThreads) layernorm_resident_kernel(const T *in, T *out, long long rows, int cols,
+                                                                      float eps, const T *gamma, const T *beta, int ddof) {
+    __shared__ float s_exchange[96];
+    layernorm_resident_tier<T, kVecs, kThreads, kAffine>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
 }
 template <typename T>
 __global__ void __launch_bounds__(256) layernorm_stream_kernel(const T *in, T *out, long long rows, int cols, float eps,

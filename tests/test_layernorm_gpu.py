@@ -97,6 +97,17 @@ def test_f32_block_tier_thread_counts(cuda, lib, oracle, block):
         assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=2, block=block), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
 
 
+@pytest.mark.parametrize("block", [0, 128, 256, 512, 1024])
+def test_f32_resident_tier(cuda, lib, oracle, block):
+    for rows, cols in ((19, 768), (300, 2048), (7, 2052), (5, 16384), (40, 4096)):
+        if block and cols // 4 > block * 4:
+            continue
+        x, g, b = _inputs(oracle, rows, cols)
+        for gg, bb in ((g, b), (None, None), (g, None)):
+            y = _run_f32(cuda, lib, x, 1e-12, gg, bb, 0, tier=5, block=block, grid_cap=3 if rows > 100 else 0)
+            assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, gg, bb)) <= TOL_REL
+
+
 def test_f32_stream_tier_and_staged_ring_wrap(cuda, lib, oracle):
     x, g, b = _inputs(oracle, 23, 768)
     assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=3), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
@@ -147,7 +158,8 @@ def test_bf16_against_rounded_oracle(cuda, lib, oracle, rows, cols):
 
 
 @pytest.mark.parametrize("knobs", [dict(tier=1), dict(tier=2, block=128), dict(tier=2, block=256), dict(tier=2, block=512),
-                                   dict(tier=2, block=1024), dict(tier=3), dict(tier=4), dict(tier=4, stages=2, ctas_per_sm=2)],
+                                   dict(tier=2, block=1024), dict(tier=3), dict(tier=4), dict(tier=4, stages=2, ctas_per_sm=2),
+                                   dict(tier=5), dict(tier=5, block=128), dict(tier=5, block=512, grid_cap=3), dict(tier=5, block=1024)],
                          ids=lambda k: "-".join(f"{a}{b}" for a, b in k.items()))
 def test_bf16_tiers_agree(cuda, lib, oracle, knobs):
     for rows, cols in ((21, 4096), (50, 1024), (33, 776)):
