@@ -72,6 +72,7 @@ extern "C" int ko_sgemm_f32_no_alloc(int64_t M, int64_t N, int64_t K, const floa
                (long long)M, (long long)N, (long long)K);
     KO_REQUIRE(split_k >= 0 && split_k <= 64, KO_ERR_INVALID_ARG, "sgemm (no-alloc): split_k %d out of range", split_k);
     if (M == 0 || N == 0) return KO_OK;
+    if (K == 0) return ko_sgemm_f32(M, N, K, A, B, C, D, stream);  // empty sum: no scratch involved
     KO_REQUIRE(M <= 0x7fffffff && N <= 0x7fffffff && K <= 0x7fffffff, KO_ERR_SHAPE, "sgemm (no-alloc): dimension exceeds 2^31-1");
     KO_REQUIRE(D != nullptr && (K == 0 || (A != nullptr && B != nullptr)), KO_ERR_INVALID_ARG, "sgemm (no-alloc): NULL pointer");
     KO_REQUIRE(D != A && D != B, KO_ERR_INVALID_ARG, "sgemm (no-alloc): D must not alias A or B");
@@ -98,7 +99,8 @@ extern "C" int ko_sgemm_f32_no_alloc(int64_t M, int64_t N, int64_t K, const floa
                tiles, split_k, tiles * split_k * (long long)x2::kTileFloats, tiles, kMaxPartialFloats, kMaxTiles, fits);
     KO_REQUIRE(tiles * split_k <= 0x7fffffffLL, KO_ERR_SHAPE, "sgemm (no-alloc): too many blocks");
 
-    x2::Params p{(int)M, (int)N, (int)K, A, B, C, D, split_k, nullptr, nullptr};
+    // tiles * split_k blocks: every tile is cut into split_k K-slices, one scratch slot per slice
+    x2::Params p{(int)M, (int)N, (int)K, A, B, C, D, (int)(tiles * split_k), split_k, nullptr, nullptr};
     if (split_k > 1) {
         p.workspace = reinterpret_cast<float *>(setup->scratch);
         p.counters = reinterpret_cast<unsigned *>(setup->scratch + kCounterOffset);

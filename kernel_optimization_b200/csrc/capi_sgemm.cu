@@ -8,6 +8,7 @@
 
 #include "../nn_operators/gemm/simt_gemm.h"
 #include "../nn_operators/gemm/simt_gemm_x2.h"
+#include "../nn_operators/gemm/simt_gemm_a8.h"
 #include "row_launch.h"
 
 namespace {
@@ -69,22 +70,47 @@ int get_scratch(cudaStream_t s, size_t partial_floats, size_t counter_count, Scr
     return KO_OK;
 }
 
+// split_k: 0 = choose the block count (stream-K), 1 = one block per tile, n > 1 = n K-slices per tile
 int launch_x2(int M, int N, int K, const float *A, const float *B, const float *C, float *D, int split_k, int sm_count,
               cudaStream_t s) {
     namespace x2 = ko::sgemm2;
     const long long tiles = (long long)((M + x2::BM - 1) / x2::BM) * ((N + x2::BN - 1) / x2::BN);
     const int ktiles = (K + x2::BK - 1) / x2::BK;
-    if (split_k <= 0) {
-        // fill the SMs (two blocks fit per SM) when the tile count alone cannot; keep >= 8 K-tiles per slice
-        split_k = 1;
-        while (tiles * split_k * 2 <= (long long)sm_count * 2 && ktiles / (split_k * 2) >= 8 && split_k < 16) split_k *= 2;
-    }
-    if (split_k > ktiles) split_k = ktiles > 0 ? ktiles : 1;
-    KO_REQUIRE(tiles * split_k <= 0x7fffffffLL, KO_ERR_SHAPE, "sgemm: %lld blocks exceed the grid limit", tiles * split_k);
-    x2::Params p{M, N, K, A, B, C, D, split_k, nullptr, nullptr};
+    const long long units = tiles * ktiles;
+    long long ctas = tiles;
+    int max_contrib = 1;
     if (split_k > 1) {
+        if (split_k > ktiles) split_k = ktiles;
+        ctas = tiles * split_k;
+        max_contrib = split_k;  // slices of a uniform split never straddle a tile
+    } else if (split_k == 0 && tiles * 2 <= sm_count) {
+        // few tiles (1024^3 has 64): a uniform split that gives about one block per SM measured faster than
+        // finer ranges, whose partial-tile traffic and short K loops cost more than the idle SMs
+        int split = (int)(sm_count / tiles);
+        while (split > 1 && ktiles / split < 16) --split;
+        if (split > 1) {
+            ctas = tiles * split;
+            max_contrib = split;
+        }
+    } else if (split_k == 0 && tiles < 4LL * sm_count) {
+        // two blocks fit per SM: hand every slot the same number of (tile, K-tile) units, as long as a
+        // block still gets at least 8 K-tiles to amortise its pipeline fill and the partial-tile traffic
+        const long long slots = 2LL * sm_count;
+        if (tiles % slots != 0) {
+            ctas = slots;
+            if (units / ctas < 8) ctas = units / 8 > tiles ? units / 8 : tiles;
+        }
+        if (ctas != tiles) {
+            const long long per_block = units / ctas;  // floor: the shortest range
+            max_contrib = (int)((ktiles + per_block - 1) / per_block) + 1;
+            if (max_contrib > ctas) max_contrib = (int)ctas;
+        }
+    }
+    KO_REQUIRE(ctas <= 0x7fffffffLL, KO_ERR_SHAPE, "sgemm: %lld blocks exceed the grid limit", ctas);
+    x2::Params p{M, N, K, A, B, C, D, (int)ctas, max_contrib, nullptr, nullptr};
+    if (ctas != tiles) {
         Scratch sc;
-        if (int st = get_scratch(s, (size_t)tiles * split_k * x2::kTileFloats, (size_t)tiles, &sc)) return st;
+        if (int st = get_scratch(s, (size_t)tiles * max_contrib * x2::kTileFloats, (size_t)tiles, &sc)) return st;
         p.workspace = sc.partials;
         p.counters = sc.counters;
     }
@@ -92,10 +118,24 @@ int launch_x2(int M, int N, int K, const float *A, const float *B, const float *
     const void *kernel = vec_b ? reinterpret_cast<const void *>(x2::sgemm_x2_kernel<true>)
                                : reinterpret_cast<const void *>(x2::sgemm_x2_kernel<false>);
     if (int st = ko::ensure_dynamic_smem(kernel, x2::kSmemBytes)) return st;
-    const unsigned grid = (unsigned)(tiles * split_k);
-    if (vec_b) x2::sgemm_x2_kernel<true><<<grid, x2::kThreads, x2::kSmemBytes, s>>>(p);
-    else x2::sgemm_x2_kernel<false><<<grid, x2::kThreads, x2::kSmemBytes, s>>>(p);
+    if (vec_b) x2::sgemm_x2_kernel<true><<<(unsigned)ctas, x2::kThreads, x2::kSmemBytes, s>>>(p);
+    else x2::sgemm_x2_kernel<false><<<(unsigned)ctas, x2::kThreads, x2::kSmemBytes, s>>>(p);
     KO_CHECK_LAUNCH("sgemm_x2_kernel");
+    return KO_OK;
+}
+
+int launch_a8(int M, int N, int K, const float *A, const float *B, const float *C, float *D, cudaStream_t s) {
+    namespace a8 = ko::sgemm8;
+    const long long tiles = (long long)((M + a8::BM - 1) / a8::BM) * ((N + a8::BN - 1) / a8::BN);
+    KO_REQUIRE(tiles <= 0x7fffffffLL, KO_ERR_SHAPE, "sgemm: %lld blocks exceed the grid limit", tiles);
+    const a8::Params p{M, N, K, A, B, C, D};
+    const bool vec_b = N % 4 == 0 && ko::aligned16(B);
+    const void *kernel = vec_b ? reinterpret_cast<const void *>(a8::sgemm_a8_kernel<true>)
+                               : reinterpret_cast<const void *>(a8::sgemm_a8_kernel<false>);
+    if (int st = ko::ensure_dynamic_smem(kernel, a8::kSmemBytes)) return st;
+    if (vec_b) a8::sgemm_a8_kernel<true><<<(unsigned)tiles, a8::kThreads, a8::kSmemBytes, s>>>(p);
+    else a8::sgemm_a8_kernel<false><<<(unsigned)tiles, a8::kThreads, a8::kSmemBytes, s>>>(p);
+    KO_CHECK_LAUNCH("sgemm_a8_kernel");
     return KO_OK;
 }
 
@@ -121,9 +161,11 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
 
     KO_REQUIRE(split_k >= 0 && split_k <= 64, KO_ERR_INVALID_ARG, "sgemm: split_k %d out of range", split_k);
     if (variant == 0) variant = (M >= 64 && N >= 64 && K >= 16) ? 4 : 3;
+    if (K == 0 && variant >= 4) variant = 3;  // an empty sum: D = C (or 0), nothing to pipeline
     const int m = (int)M, n = (int)N, k = (int)K;
     switch (variant) {
-        case 4: return launch_x2(m, n, k, A, B, C, D, K == 0 ? 1 : split_k, info.sm_count, s);
+        case 4: return launch_x2(m, n, k, A, B, C, D, split_k, info.sm_count, s);
+        case 5: return launch_a8(m, n, k, A, B, C, D, s);
         case 1: return launch<CfgBig>(m, n, k, A, B, C, D, aligned, s);
         case 2: return launch<CfgWide>(m, n, k, A, B, C, D, aligned, s);
         case 3: return launch<CfgSmall>(m, n, k, A, B, C, D, aligned, s);

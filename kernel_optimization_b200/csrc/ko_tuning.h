@@ -30,7 +30,8 @@ int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int
                             const uint16_t *gamma, const uint16_t *beta, int ddof, const ko_row_knobs_t *knobs,
                             void *stream);
 /* variant: 0 = choose, 1..3 = scalar-FFMA tilings (128x128, 128x64, 64x64), 4 = packed-FFMA 128x128 kernel;
- * split_k: K slices of variant 4 (0 = choose, 1 = none) */
+ * 5 = 128x64 scalar-FFMA cp.async kernel; split_k (variant 4): 0 = choose the block count (stream-K),
+ * 1 = one block per tile, n > 1 = n K-slices per tile */
 int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
                        int variant, int split_k, void *stream);
 /* fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns of D per tile;

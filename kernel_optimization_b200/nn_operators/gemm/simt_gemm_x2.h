@@ -12,10 +12,16 @@
 // legal and nothing is read out of bounds -- the reference prefetches past the end,
 // nn_operators/gemm/simt_gemm.h:287-292); B[K,N] goes in 16-byte pieces.  kStages tiles are in flight.
 //
+// Work distribution ("stream-K"): the (tile, K-tile) pairs form one linear sequence of units that is
+// cut into `ctas` equal contiguous ranges, one per block.  With ctas == tiles every block owns one
+// whole tile; with ctas == tiles * s every tile is cut into s K-slices (classic split-K); any other
+// count (e.g. two blocks per SM) gives ranges that may end one tile and begin the next, so that a
+// problem with few tiles still keeps every SM busy for the same time.
+//
 // Accumulation order: one FMA per k in ascending k per output, as in the reference
-// (simt_gemm.h:202-222).  With split_k == 1 the result is bit-identical to that order; with
-// split_k > 1 each K-slice is accumulated that way and the slices are added in slice order by the
-// block that finishes last (deterministic, no atomics on data, no waiting between blocks).
+// (simt_gemm.h:202-222).  A tile computed by one block is bit-identical to that order; a tile shared
+// by several blocks has each K-range accumulated that way and the ranges added in K order by the block
+// that finishes last (deterministic; no atomics on data, no waiting between blocks).
 #pragma once
 
 #include "../../common/common.h"
@@ -57,10 +63,19 @@ struct Params {
     int M, N, K;
     const float *A, *B, *C;
     float *D;
-    int split_k;        // >= 1
-    float *workspace;   // split_k > 1: [tiles][split_k][BM*BN] partial tiles
-    unsigned *counters; // split_k > 1: one arrival counter per tile, zero between launches
+    int ctas;           // blocks sharing the tiles * ktiles work units (== gridDim.x)
+    int max_contrib;    // upper bound on the blocks that touch one tile (workspace slots per tile)
+    float *workspace;   // [tiles][max_contrib][BM*BN] partial tiles (used when a tile is shared)
+    unsigned *counters; // one arrival counter per tile, zero between launches
 };
+
+// the block whose unit range [b*U/G, (b+1)*U/G) contains unit u
+__device__ __forceinline__ int block_of_unit(long long u, long long U, int G) {
+    int b = (int)(u * G / U);
+    while ((long long)(b + 1) * U / G <= u) ++b;
+    while ((long long)b * U / G > u) --b;
+    return b;
+}
 
 // kVecB: N % 4 == 0 and B 16-byte aligned (16-byte copies of B); otherwise 4-byte copies
 template <bool kVecB>
@@ -71,16 +86,12 @@ __global__ void __launch_bounds__(kThreads) sgemm_x2_kernel(const Params p) {
     const int warp_m = warp >> 1, warp_n = warp & 1;   // 2 x 2 warps of 64 x 64
     const int lane_m = lane >> 3, lane_n = lane & 7;   // 4 x 8 lanes of 16 x 8
     const int tiles_n = (p.N + BN - 1) / BN;
-    const int tile = blockIdx.x / p.split_k, slice = blockIdx.x % p.split_k;
-    const int m_base = (tile / tiles_n) * BM, n_base = (tile % tiles_n) * BN;
-
-    // this block's K range, in whole BK tiles
     const int ktiles_total = (p.K + BK - 1) / BK;
-    const int kt_begin = (int)((long long)ktiles_total * slice / p.split_k);
-    const int kt_end = (int)((long long)ktiles_total * (slice + 1) / p.split_k);
-    const int ktiles = kt_end - kt_begin;
+    const long long units = (long long)((p.M + BM - 1) / BM) * tiles_n * ktiles_total;
+    const long long unit_begin = units * blockIdx.x / p.ctas, unit_end = units * (blockIdx.x + 1) / p.ctas;
 
     const uint32_t smem_base = smem_u32(smem);
+    int m_base = 0, n_base = 0;
     auto issue_tile = [&](int kt, int stage) {
         const int k0 = kt * BK;
         const uint32_t as = smem_base + (uint32_t)stage * kStageFloats * 4u;
@@ -116,6 +127,21 @@ __global__ void __launch_bounds__(kThreads) sgemm_x2_kernel(const Params p) {
         }
     };
 
+    const int a_off = warp_m * 64 + lane_m * 4;  // + q * 16, q = 0..3
+    const int b_off = warp_n * 64 + lane_n * 4;  // + q * 32, q = 0..1
+
+    for (long long u = unit_begin; u < unit_end;) {
+    // ---- one segment: K-tiles [kt_begin, kt_end) of one output tile
+    const int tile = (int)(u / ktiles_total);
+    const int kt_begin = (int)(u % ktiles_total);
+    const int kt_end = (int)min((long long)ktiles_total, kt_begin + (unit_end - u));
+    const int ktiles = kt_end - kt_begin;
+    u += ktiles;
+    const bool whole_tile = ktiles == ktiles_total;
+    m_base = (tile / tiles_n) * BM;
+    n_base = (tile % tiles_n) * BN;
+    __syncthreads();  // the previous segment's shared-memory reads (and s_is_last) are done
+
     // acc[ip][j]: rows (2*ip, 2*ip+1) of the thread's 16, column j of its 8
     u64 acc[8][8];
 #pragma unroll
@@ -129,9 +155,6 @@ __global__ void __launch_bounds__(kThreads) sgemm_x2_kernel(const Params p) {
         if (s < ktiles) issue_tile(kt_begin + s, s);
         cp_async_commit();
     }
-
-    const int a_off = warp_m * 64 + lane_m * 4;  // + q * 16, q = 0..3
-    const int b_off = warp_n * 64 + lane_n * 4;  // + q * 32, q = 0..1
 
     for (int t = 0; t < ktiles; ++t) {
         cp_async_wait<kStages - 2>();
@@ -186,35 +209,44 @@ __global__ void __launch_bounds__(kThreads) sgemm_x2_kernel(const Params p) {
                 }
                 out[(ip * 2 + h) * 2 + jq] = make_float4(v[0], v[1], v[2], v[3]);
             }
-    if (p.split_k > 1) {
-        // publish this slice's partial tile: [tile][slice][chunk][thread] float4, coalesced
-        float4 *mine = reinterpret_cast<float4 *>(p.workspace + ((size_t)tile * p.split_k + slice) * kTileFloats);
+    int contributors = 1, slot = 0;
+    if (!whole_tile) {
+        const long long first_unit = (long long)tile * ktiles_total;
+        const int first_block = block_of_unit(first_unit, units, p.ctas);
+        contributors = block_of_unit(first_unit + ktiles_total - 1, units, p.ctas) - first_block + 1;
+        slot = (int)blockIdx.x - first_block;
+    }
+    bool finish_tile = true;
+    if (!whole_tile) {
+        // publish this K-range's partial tile: [tile][slot][chunk][thread] float4, coalesced
+        float4 *mine = reinterpret_cast<float4 *>(p.workspace + ((size_t)tile * p.max_contrib + slot) * kTileFloats);
 #pragma unroll
         for (int c = 0; c < 32; ++c) mine[c * kThreads + tid] = out[c];
         __threadfence();
         __syncthreads();
         if (tid == 0) {
             const unsigned prev = atomicAdd(p.counters + tile, 1u);
-            s_is_last = (prev == (unsigned)p.split_k - 1u);
+            s_is_last = (prev == (unsigned)contributors - 1u);
         }
         __syncthreads();
-        if (!s_is_last) return;
-        __threadfence();
+        finish_tile = s_is_last != 0;
+        if (finish_tile) __threadfence();
     }
+    if (finish_tile) {
 
-    if (p.split_k > 1) {
-        // add the slices in slice order, whichever block arrived last (its own slice comes from
-        // registers, bit-identical to what it published); all 32 loads of a slice are independent
+    if (!whole_tile) {
+        // add the K-ranges in K order, whichever block arrived last (its own range comes from
+        // registers, bit-identical to what it published); all loads of a range are independent
         // (two halves of 16 chunks keep the register count below the limit)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             float4 sum[16];
 #pragma unroll
             for (int c = 0; c < 16; ++c) sum[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s = 0; s < p.split_k; ++s) {
-                const float4 *part = reinterpret_cast<const float4 *>(p.workspace + ((size_t)tile * p.split_k + s) * kTileFloats) +
+            for (int s = 0; s < contributors; ++s) {
+                const float4 *part = reinterpret_cast<const float4 *>(p.workspace + ((size_t)tile * p.max_contrib + s) * kTileFloats) +
                                      (half * 16) * kThreads + tid;
-                const bool own = s == slice;
+                const bool own = s == slot;
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     const float4 v = own ? out[half * 16 + c] : __ldcg(part + c * kThreads);
@@ -254,7 +286,9 @@ __global__ void __launch_bounds__(kThreads) sgemm_x2_kernel(const Params p) {
                 }
             }
         }
-    if (p.split_k > 1 && tid == 0) p.counters[tile] = 0u;  // ready for the next launch
+    if (!whole_tile && tid == 0) p.counters[tile] = 0u;  // ready for the next launch
+    }  // finish_tile
+    }  // segments
 }
 
 }  // namespace sgemm2

@@ -26,7 +26,7 @@ SHAPES = [(1, 1, 1), (64, 64, 8), (100, 36, 52), (129, 65, 17), (256, 256, 256),
           (128, 128, 1), (640, 384, 72)]
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_unsplit_kernels_are_bit_identical_to_the_reference_order(cuda, lib, oracle, M, N, K, variant):
     a, b, c = oracle.fill_uniform((M, K), 2, 0), oracle.fill_uniform((K, N), 2, 1), oracle.fill_uniform((M, N), 2, 2)
@@ -37,7 +37,8 @@ def test_unsplit_kernels_are_bit_identical_to_the_reference_order(cuda, lib, ora
 
 
 @pytest.mark.parametrize("split_k", [0, 2, 3, 4, 8])
-@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (300, 200, 1000), (129, 65, 170), (1024, 1024, 1024), (64, 64, 4096), (17, 513, 333)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (300, 200, 1000), (129, 65, 170), (1024, 1024, 1024), (64, 64, 4096), (17, 513, 333),
+                                   (2048, 1536, 512), (1920, 1152, 1000)])
 def test_split_k_is_deterministic_and_within_tolerance(cuda, lib, oracle, M, N, K, split_k):
     a, b, c = oracle.fill_uniform((M, K), 2, 0), oracle.fill_uniform((K, N), 2, 1), oracle.fill_uniform((M, N), 2, 2)
     for cc in (None, c):
