@@ -3,7 +3,10 @@
 // grid, GemmKernel::thread_per_block and GemmKernel::smem_total_size_in_bytes.
 #pragma once
 
+#include <type_traits>
+
 #include "simt_gemm.h"
+#include "tensor_core_compat.h"
 
 template <typename GemmKernel>
 __global__ void __launch_bounds__(GemmKernel::thread_per_block)
