@@ -79,6 +79,21 @@ int launch_resident_vecs(int vecs, const Args<T> &a, long long grid_cap, int sm_
     return launch_resident<T, 4, kThreads>(a, grid_cap, sm_count, s);
 }
 
+// one row per cluster of `c` blocks of 1024 threads, up to 8 vectors per thread
+template <typename T>
+int launch_cluster(const Args<T> &a, int c, long long grid_cap, int sm_count, cudaStream_t s) {
+    const int slice = (a.cols / ko::RowIo<T>::kPerVec + c - 1) / c;
+    long long clusters = a.rows;
+    const long long cap = grid_cap > 0 ? grid_cap / c : (long long)(sm_count / c) * 2;
+    if (clusters > cap) clusters = cap > 0 ? cap : 1;
+    const unsigned grid = (unsigned)(clusters * c);
+    if (slice <= 256 * 4)
+        return ko::launch_clustered(ko::layernorm_cluster_kernel<T, 4, 256>, grid, 256, c, s, a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+    if (slice <= 1024 * 4)
+        return ko::launch_clustered(ko::layernorm_cluster_kernel<T, 4, 1024>, grid, 1024, c, s, a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+    return ko::launch_clustered(ko::layernorm_cluster_kernel<T, 8, 1024>, grid, 1024, c, s, a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+}
+
 template <typename T, bool kStaged>
 int dispatch_rows(int vecs, int rpw, const Args<T> &a, const ko_row_knobs_t &k, const DeviceInfo &info, cudaStream_t s,
                   bool *used) {
@@ -104,7 +119,9 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
     if (a.rows == 0 || a.cols == 0) return KO_OK;
     KO_REQUIRE(a.in != nullptr && a.out != nullptr, KO_ERR_INVALID_ARG, "layernorm: NULL pointer");
     const ko_row_knobs_t k = knobs ? *knobs : ko_row_knobs_t{};
-    KO_REQUIRE(k.tier >= 0 && k.tier <= 5, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
+    KO_REQUIRE(k.tier >= 0 && k.tier <= 6, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
+    KO_REQUIRE(k.cluster == 0 || k.cluster == 2 || k.cluster == 4 || k.cluster == 8, KO_ERR_INVALID_ARG,
+               "layernorm: cluster size %d not in {2,4,8}", k.cluster);
     KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
                "layernorm: block %d must be a multiple of 32, <= 1024", k.block);
     DeviceInfo info;
@@ -126,7 +143,14 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         else if (warp_ok && (sizeof(T) == 4 || nvec <= 256)) tier = 1;
         else if (nvec <= 1024 * 4) tier = 5;
         else if (nvec <= 1024 * kMaxVecsPerThread) tier = 2;
+        else if (nvec <= 8 * 1024 * kMaxVecsPerThread) tier = 6;  // beyond one block's registers: a cluster holds the row
         else tier = 3;
+    }
+    if (tier == 6) {
+        KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "layernorm: the cluster tier needs 16-byte aligned rows");
+        const int c = ko::cluster_size_for(nvec, 1024 * kMaxVecsPerThread, k.cluster);
+        KO_REQUIRE(c > 0, KO_ERR_SHAPE, "layernorm: %d columns exceed what a cluster of 8 blocks holds", a.cols);
+        return launch_cluster<T>(a, c, k.grid_cap, info.sm_count, s);
     }
     if (tier == 5) {
         // resident tier: at most 4 vectors per thread

@@ -41,6 +41,19 @@ int launch_block(const float *in, float *out, long long rows, int cols, long lon
     return KO_OK;
 }
 
+// one row per cluster of `c` blocks of 1024 threads, up to 8 vectors per thread
+int launch_cluster(const float *in, float *out, long long rows, int cols, int c, long long grid_cap, int sm_count,
+                   cudaStream_t s) {
+    const int slice = (cols / 4 + c - 1) / c;
+    long long clusters = rows;
+    const long long cap = grid_cap > 0 ? grid_cap / c : (long long)(sm_count / c) * 2;
+    if (clusters > cap) clusters = cap > 0 ? cap : 1;
+    const unsigned grid = (unsigned)(clusters * c);
+    if (slice <= 256 * 4) return ko::launch_clustered(ko::softmax_cluster_kernel<4, 256>, grid, 256, c, s, in, out, rows, cols);
+    if (slice <= 1024 * 4) return ko::launch_clustered(ko::softmax_cluster_kernel<4, 1024>, grid, 1024, c, s, in, out, rows, cols);
+    return ko::launch_clustered(ko::softmax_cluster_kernel<8, 1024>, grid, 1024, c, s, in, out, rows, cols);
+}
+
 // lanes per row and vectors per lane depend on the column count only; `slots` (rows a warp handles
 // together = slots * 32/G) is the tunable
 template <bool kStaged>
@@ -81,7 +94,9 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
     if (rows == 0 || cols == 0) return KO_OK;
     KO_REQUIRE(in != nullptr && out != nullptr, KO_ERR_INVALID_ARG, "softmax: NULL pointer");
     const ko_row_knobs_t k = knobs ? *knobs : ko_row_knobs_t{};
-    KO_REQUIRE(k.tier >= 0 && k.tier <= 4, KO_ERR_INVALID_ARG, "softmax: unknown tier %d", k.tier);
+    KO_REQUIRE((k.tier >= 0 && k.tier <= 4) || k.tier == 6, KO_ERR_INVALID_ARG, "softmax: unknown tier %d", k.tier);
+    KO_REQUIRE(k.cluster == 0 || k.cluster == 2 || k.cluster == 4 || k.cluster == 8, KO_ERR_INVALID_ARG,
+               "softmax: cluster size %d not in {2,4,8}", k.cluster);
     KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
                "softmax: block %d must be a multiple of 32, <= 1024", k.block);
     DeviceInfo info;
@@ -95,7 +110,14 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
         if (!vec_ok) tier = 3;
         else if (nvec <= 32 * 16) tier = 1;  // measured faster than the staged tier at every BASELINE shape
         else if (nvec <= 1024 * 8) tier = 2;
+        else if (nvec <= 8 * 1024 * 8) tier = 6;  // beyond one block's registers: a cluster holds the row
         else tier = 3;
+    }
+    if (tier == 6) {
+        KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "softmax: the cluster tier needs cols %% 4 == 0 and 16-byte aligned pointers");
+        const int c = ko::cluster_size_for(nvec, 1024 * 8, k.cluster);
+        KO_REQUIRE(c > 0, KO_ERR_SHAPE, "softmax: %d columns exceed what a cluster of 8 blocks holds (262144)", cols);
+        return launch_cluster(in, out, rows, cols, c, k.grid_cap, info.sm_count, s);
     }
     if (tier == 4) {
         KO_REQUIRE(vec_ok && nvec <= 32 * 16, KO_ERR_SHAPE, "softmax: the staged tier needs cols %% 4 == 0, cols <= 2048 and 16-byte aligned pointers");

@@ -12,7 +12,8 @@ extern "C" {
 /* knobs of the row operators; pass NULL for all defaults */
 typedef struct ko_row_knobs {
     int tier;            /* 0 = choose, 1 = warp, 2 = block, 3 = stream (scalar), 4 = staged (TMA ring),
-                            5 = resident (LayerNorm only: persistent blocks, packed FP32 math) */
+                            5 = resident (LayerNorm only: persistent blocks, packed FP32 math),
+                            6 = cluster (one row per thread-block cluster, partials through DSMEM) */
     int rows_per_warp;   /* warp / staged tier: independent row slots a warp processes together (a slot is
                             one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows) */
     int block;           /* warp tier: threads per block (<= 256); block / resident tier: threads per row (128..1024) */
@@ -20,6 +21,7 @@ typedef struct ko_row_knobs {
     int stage_rows;      /* staged tier: rows per bulk copy (0 = about 16-32 KB) */
     int stages;          /* staged tier: ring depth (0 = fill about 100 KB) */
     int ctas_per_sm;     /* staged tier: persistent blocks per SM (0 = 1) */
+    int cluster;         /* cluster tier: blocks per cluster, 2 / 4 / 8 (0 = smallest that holds the row) */
 } ko_row_knobs_t;
 
 int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols, const ko_row_knobs_t *knobs,

@@ -52,6 +52,34 @@ inline StagedPlan plan_staged(long long rows, unsigned row_bytes, int rows_per_g
 // raises a kernel's dynamic shared-memory limit once per (kernel, device) and only when it grows
 int ensure_dynamic_smem(const void *kernel, size_t bytes);
 
+// Launch `kernel` with thread-block clusters of `cluster` blocks along x (grid must be a multiple of it).
+template <typename... KernelArgs, typename... Args>
+int launch_clustered(void (*kernel)(KernelArgs...), unsigned grid, unsigned block, unsigned cluster, cudaStream_t s,
+                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    KO_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...));
+    return KO_OK;
+}
+
+// cluster size (power of two, <= 8) so that a block's slice of `nvec` vectors fits `per_block` vectors;
+// 0 when even 8 blocks are not enough
+inline int cluster_size_for(int nvec, int per_block, int wanted) {
+    int c = wanted > 0 ? wanted : 2;
+    while (c < 8 && (nvec + c - 1) / c > per_block) c *= 2;
+    return (nvec + c - 1) / c <= per_block ? c : 0;
+}
+
 inline unsigned clamp_grid(long long wanted, long long cap) {
     if (cap > 0 && wanted > cap) wanted = cap;
     if (wanted > 0x7fffffffLL) wanted = 0x7fffffffLL;

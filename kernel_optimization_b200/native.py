@@ -60,7 +60,7 @@ class RowKnobs(C.Structure):
     """ko_row_knobs_t of csrc/ko_tuning.h: launch-geometry overrides of the row operators (0 = default)."""
 
     _fields_ = [("tier", _int), ("rows_per_warp", _int), ("block", _int), ("grid_cap", _i64), ("stage_rows", _int),
-                ("stages", _int), ("ctas_per_sm", _int)]
+                ("stages", _int), ("ctas_per_sm", _int), ("cluster", _int)]
 
 
 _knobs_p = C.POINTER(RowKnobs)

@@ -16,6 +16,8 @@
 //   block tier   one thread block per row, row in registers, one shared-memory exchange;
 //   resident tier persistent blocks for long rows: gamma/beta held in registers, packed FP32 math,
 //                next row prefetched;
+//   cluster tier one row per thread-block cluster, Welford triples exchanged through distributed
+//                shared memory (rows beyond one block's registers, or few very long rows);
 //   stream tier  one thread block per row, two passes over global memory, scalar accesses, any
 //                column count and alignment.
 // y = ((x - mean) * rstd) * gamma + beta, gamma/beta optional, in the I/O element type.
@@ -23,6 +25,8 @@
 // The reference's LayerNormWarpImpl / LayerNormBlockImpl / LayerNormBlockNoCacheImpl templates and
 // the layer_normalization<Kernel> __global__ wrapper keep their names and parameters.
 #pragma once
+
+#include <cooperative_groups.h>
 
 #include "../../common/common.h"
 #include "../../common/functors.h"
@@ -456,6 +460,64 @@ __device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, lon
 }
 
 // ---------------------------------------------------------------------------------------------
+// cluster tier: one row per thread-block cluster, Welford triples exchanged through DSMEM
+// ---------------------------------------------------------------------------------------------
+// Each block of the cluster holds a contiguous slice of the row in registers and reduces it to one
+// (n, mean, M2) triple; the triples sit in each block's shared memory and every block merges all of
+// them, in rank order, reading its peers' copies through distributed shared memory.  One cluster
+// barrier per row (slots double buffered by row parity); the row is read from HBM once.
+template <typename T, int kVecs>
+__device__ __forceinline__ void layernorm_cluster_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                       const T *gamma, const T *beta, int ddof, float *s_exchange,
+                                                       float (*s_part)[3]) {
+    namespace cg = cooperative_groups;
+    using Raw = typename RowIo<T>::Raw;
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned nblocks = cluster.num_blocks(), rank = cluster.block_rank();
+    const int nvec = cols / RowIo<T>::kPerVec;
+    const int slice = (nvec + (int)nblocks - 1) / (int)nblocks;
+    const int v_begin = (int)rank * slice, v_end = min(nvec, v_begin + slice);
+    const Raw *in_v = reinterpret_cast<const Raw *>(in);
+    Raw *out_v = reinterpret_cast<Raw *>(out);
+    const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma);
+    const Raw *beta_v = reinterpret_cast<const Raw *>(beta);
+    int my_vecs = 0;
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) my_vecs += (v_begin + (int)threadIdx.x + (int)blockDim.x * j < v_end) ? 1 : 0;
+    const long long clusters = gridDim.x / nblocks, first = blockIdx.x / nblocks;
+    int parity = 0;
+    for (long long row = first; row < rows; row += clusters, parity ^= 1) {
+        Raw raw[kVecs];
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
+            if (v < v_end) raw[j] = ld_stream(in_v + row * nvec + v);
+            else raw[j] = Raw{};
+        }
+        Welford w = welford_of_vectors<T, kVecs>(raw, my_vecs);
+        w = block_allreduce_welford(w, s_exchange);
+        if (threadIdx.x == 0) {
+            s_part[parity][0] = w.n;
+            s_part[parity][1] = w.mean;
+            s_part[parity][2] = w.m2;
+        }
+        cluster.sync();
+        Welford all{0.f, 0.f, 0.f};
+        for (unsigned r = 0; r < nblocks; ++r) {
+            const float *peer = cluster.map_shared_rank(&s_part[parity][0], r);
+            all = welford_merge(all, Welford{peer[0], peer[1], peer[2]});
+        }
+        const float mean = all.mean, rstd = rstd_from(all, cols, ddof, eps);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
+            if (v < v_end) st_stream(out_v + row * nvec + v, normalise_vector<T>(raw[j], mean, rstd, gamma_v, beta_v, v));
+        }
+    }
+    cluster.sync();  // no block may exit while a peer can still read its shared memory
+}
+
+// ---------------------------------------------------------------------------------------------
 // stream tier: any cols / alignment; per-thread running Welford, two passes over global memory
 // ---------------------------------------------------------------------------------------------
 template <typename T>
@@ -511,6 +573,13 @@ __global__ void __launch_bounds__(kThreads) layernorm_resident_kernel(const T *i
                                                                       float eps, const T *gamma, const T *beta, int ddof) {
     __shared__ float s_exchange[96];
     layernorm_resident_tier<T, kVecs, kThreads, kAffine>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
+}
+template <typename T, int kVecs, int kThreads>
+__global__ void __launch_bounds__(kThreads) layernorm_cluster_kernel(const T *in, T *out, long long rows, int cols, float eps,
+                                                                     const T *gamma, const T *beta, int ddof) {
+    __shared__ float s_exchange[96];
+    __shared__ float s_part[2][3];
+    layernorm_cluster_tier<T, kVecs>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange, s_part);
 }
 template <typename T>
 __global__ void __launch_bounds__(256) layernorm_stream_kernel(const T *in, T *out, long long rows, int cols, float eps,

@@ -1,6 +1,6 @@
 // Row softmax over the last dimension for sm_100a.
 //
-// Four tiers, chosen by row length and alignment (the reference's warp / block-cached /
+// Five tiers, chosen by row length and alignment (the reference's warp / block-cached /
 // block-no-cache split, nn_operators/softmax/softmax.h:11-60, :62-113, :116-166, re-thought for B200):
 //
 //   staged tier persistent blocks; a producer warp streams chunks of whole rows into a shared-memory
@@ -11,6 +11,8 @@
 //               every load of the step is issued before the first use.
 //   block tier  one thread block per row, the row in registers (kVecs vectors per thread), warp
 //               all-reduce + one shared-memory exchange per statistic.
+//   cluster tier one row per thread-block cluster (2, 4 or 8 blocks), each block a slice of the row in
+//               registers, (max, sum) partials exchanged through distributed shared memory.
 //   stream tier one thread block per row, three passes over global memory with scalar accesses; any
 //               column count and any alignment (correctness path).
 //
@@ -24,6 +26,8 @@
 // so `softmax<SoftMaxWarpImpl<float, 4, R, C>><<<grid, block, smem, stream>>>(in, out)` still
 // compiles; those tiers are grid-stride loops and therefore correct for any launch geometry.
 #pragma once
+
+#include <cooperative_groups.h>
 
 #include "../../common/common.h"
 #include "../../common/functors.h"
@@ -230,6 +234,62 @@ __device__ __forceinline__ void softmax_block_tier(const float *in, float *out, 
 }
 
 // ---------------------------------------------------------------------------------------------
+// cluster tier: one row per thread-block CLUSTER, the row in the registers of all its blocks
+// ---------------------------------------------------------------------------------------------
+// For rows beyond one block's registers (more than 32768 columns) or few very long rows: each of the
+// cluster's blocks holds a contiguous slice of the row, block-level (max, sum) partials are exchanged
+// through distributed shared memory (every block reads its peers' partials with plain loads from
+// their shared memory), so the row is still read from HBM exactly once.  Two cluster barriers per row;
+// the exchange slots are double buffered by row parity so no third barrier is needed.
+template <int kVecs>
+__device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out, long long rows, int cols,
+                                                     float *s_exchange, float (*s_part)[2]) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned nblocks = cluster.num_blocks(), rank = cluster.block_rank();
+    const int nvec = cols >> 2;
+    const int slice = (nvec + (int)nblocks - 1) / (int)nblocks;
+    const int v_begin = (int)rank * slice, v_end = min(nvec, v_begin + slice);
+    const float4 *in4 = reinterpret_cast<const float4 *>(in);
+    float4 *out4 = reinterpret_cast<float4 *>(out);
+    const long long clusters = gridDim.x / nblocks, first = blockIdx.x / nblocks;
+    int parity = 0;
+    for (long long row = first; row < rows; row += clusters, parity ^= 1) {
+        float4 x[kVecs];
+        float m = kNegInf;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
+            x[j] = v < v_end ? ld_stream(in4 + row * nvec + v) : neg_inf4();
+            m = fmaxf(m, max4(x[j]));
+        }
+        m = block_allreduce<true>(m, s_exchange);
+        if (threadIdx.x == 0) s_part[parity][0] = m;
+        cluster.sync();
+        for (unsigned r = 0; r < nblocks; ++r) m = fmaxf(m, cluster.map_shared_rank(&s_part[parity][0], r)[0]);
+        const float neg = -m * kLog2e;
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) s += exp_shifted4(x[j], neg);  // padding: 2^(-inf) = 0
+        s = block_allreduce<false>(s, s_exchange);
+        if (threadIdx.x == 0) s_part[parity][1] = s;
+        cluster.sync();
+        float total = 0.f;
+        for (unsigned r = 0; r < nblocks; ++r) total += cluster.map_shared_rank(&s_part[parity][1], r)[0];  // rank order
+        const float inv = rcp_approx(total);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
+            if (v < v_end) {
+                scale4(x[j], inv);
+                st_stream(out4 + row * nvec + v, x[j]);
+            }
+        }
+    }
+    cluster.sync();  // no block may exit while a peer can still read its shared memory
+}
+
+// ---------------------------------------------------------------------------------------------
 // stream tier: any cols, any alignment; three passes over global memory
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void softmax_stream_tier(const float *in, float *out, long long rows, int cols,
@@ -265,6 +325,12 @@ template <int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) softmax_block_kernel(const float *in, float *out, long long rows, int cols) {
     __shared__ float s_exchange[33];
     softmax_block_tier<kVecs>(in, out, rows, cols, s_exchange);
+}
+template <int kVecs, int kThreads>
+__global__ void __launch_bounds__(kThreads) softmax_cluster_kernel(const float *in, float *out, long long rows, int cols) {
+    __shared__ float s_exchange[33];
+    __shared__ float s_part[2][2];
+    softmax_cluster_tier<kVecs>(in, out, rows, cols, s_exchange, s_part);
 }
 __global__ void __launch_bounds__(256) softmax_stream_kernel(const float *in, float *out, long long rows, int cols) {
     __shared__ float s_exchange[33];

@@ -108,6 +108,20 @@ def test_f32_resident_tier(cuda, lib, oracle, block):
             assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, gg, bb)) <= TOL_REL
 
 
+@pytest.mark.parametrize("cluster", [0, 2, 4, 8])
+def test_cluster_tier_merges_triples_through_dsmem(cuda, lib, oracle, cluster):
+    for rows, cols in ((5, 4096), (3, 40000), (37, 8192), (2, 131072), (300, 2048), (3, 1028)):
+        x, g, b = _inputs(oracle, rows, cols)
+        y = _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=6, cluster=cluster)
+        assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+        assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=6, cluster=cluster, grid_cap=16))
+    x, g, b = _inputs(oracle, 4, 65536)
+    xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
+    got = oracle.from_bf16_bits(_run_bf16(cuda, lib, xb, 1e-12, gb, bb, tier=6, cluster=cluster))
+    want = oracle.layernorm_f64(oracle.from_bf16_bits(xb), 1e-12, oracle.from_bf16_bits(gb), oracle.from_bf16_bits(bb))
+    assert oracle.max_rel_err(got, want) <= 2.0 ** -8 * 1.01
+
+
 def test_f32_stream_tier_and_staged_ring_wrap(cuda, lib, oracle):
     x, g, b = _inputs(oracle, 23, 768)
     assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=3), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL

@@ -75,6 +75,15 @@ def test_block_and_stream_tiers(cuda, lib, oracle, tier):
         assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS and oracle.max_rowsum_err(y) <= TOL_ROWSUM
 
 
+@pytest.mark.parametrize("cluster", [0, 2, 4, 8])
+def test_cluster_tier_exchanges_partials_through_dsmem(cuda, lib, oracle, cluster):
+    for rows, cols in ((5, 4096), (3, 40000), (37, 8192), (2, 131072), (300, 2048), (2, 262144), (3, 1028)):
+        x = oracle.fill_normal((rows, cols), 0, 0, 0.0, 2.0)
+        y = _run(cuda, lib, x, tier=6, cluster=cluster)
+        assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS and oracle.max_rowsum_err(y) <= TOL_ROWSUM
+        assert np.array_equal(y, _run(cuda, lib, x, tier=6, cluster=cluster, grid_cap=16))  # fewer clusters, more rows each
+
+
 def test_staged_tier_many_stages_per_block(cuda, lib, oracle):
     """Enough rows that every persistent block wraps its ring several times (phase bits flip)."""
     x = oracle.fill_normal((148 * 8 * 40 + 13, 128), 0, 0, 0.0, 2.0)
