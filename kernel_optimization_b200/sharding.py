@@ -61,6 +61,10 @@ def replicate_from_rank0(tensor):
     """Replicate the GEMM's B operand: one broadcast from rank 0 at set-up, outside any timed region."""
     import torch.distributed as dist
 
+    import torch
+
     if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-        dist.broadcast(tensor, src=0)
+        # 16-bit operands travel as raw integers, which NCCL does not move: broadcast the bytes
+        payload = tensor.view(torch.uint8) if tensor.dtype in (torch.int16, torch.uint16) else tensor
+        dist.broadcast(payload, src=0)
     return tensor
