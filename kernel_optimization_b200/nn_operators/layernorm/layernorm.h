@@ -343,35 +343,25 @@ __device__ __forceinline__ void layernorm_block_tier(const T *in, T *out, long l
 // same columns, so gamma and beta are unpacked to FP32 pairs once, outside the row loop; a row is
 // unpacked once and its three passes (sum, squared deviations, normalise) run on packed FP32 pairs
 // (add/mul/fma.f32x2); the next row's loads are issued before the current row is processed.
+// sum over the block; `slot` alternates between calls so that one barrier per call suffices
+// (a slot is rewritten only after every thread has passed the barrier of the call in between)
 template <int kThreads>
-__device__ __forceinline__ Welford block_allreduce_welford_fixed(Welford w, float *s_exchange) {
+__device__ __forceinline__ float block_sum_fixed(float v, float *s_exchange, int slot) {
     constexpr int kWarps = kThreads / 32;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    w = warp_allreduce_welford(w);
+    v = warp_allreduce_sum(v);
+    float *mine = s_exchange + slot * 32;
+    if ((threadIdx.x & 31) == 0) mine[threadIdx.x >> 5] = v;
     __syncthreads();
-    if (lane == 0) {
-        s_exchange[warp] = w.n;
-        s_exchange[32 + warp] = w.mean;
-        s_exchange[64 + warp] = w.m2;
-    }
-    __syncthreads();
-    Welford t;
-    t.n = lane < kWarps ? s_exchange[lane] : 0.f;
-    t.mean = lane < kWarps ? s_exchange[32 + lane] : 0.f;
-    t.m2 = lane < kWarps ? s_exchange[64 + lane] : 0.f;
+    float total = mine[0];
 #pragma unroll
-    for (int m = kWarps / 2; m > 0; m >>= 1) {
-        Welford o;
-        o.n = __shfl_xor_sync(kFullMask, t.n, m);
-        o.mean = __shfl_xor_sync(kFullMask, t.mean, m);
-        o.m2 = __shfl_xor_sync(kFullMask, t.m2, m);
-        t = welford_merge(t, o);
-    }
-    t.mean = __shfl_sync(kFullMask, t.mean, 0);
-    t.m2 = __shfl_sync(kFullMask, t.m2, 0);
-    return t;
+    for (int w = 1; w < kWarps; ++w) total += mine[w];  // same order in every thread
+    return total;
 }
 
+// The statistics of this tier are the exact two-pass form of the Welford/Chan result: every thread
+// sums its registers, one block-wide sum gives the row mean, then the squared deviations from that
+// mean are summed the same way.  (Merging per-thread (n, mean, M2) triples gives the same numbers but
+// costs about 100 instructions per thread and row, which dominates when a thread holds 16 values.)
 template <typename T, int kVecs, int kThreads, bool kAffine>
 __device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, long long rows, int cols, float eps,
                                                         const T *gamma, const T *beta, int ddof, float *s_exchange) {
@@ -384,6 +374,8 @@ __device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, lon
     int my_vecs = 0;
 #pragma unroll
     for (int j = 0; j < kVecs; ++j) my_vecs += ((int)threadIdx.x + kThreads * j < nvec) ? 1 : 0;
+    const float inv_cols = 1.0f / (float)cols;
+    const float inv_denom = cols - ddof > 0 ? 1.0f / (float)(cols - ddof) : 0.f;
 
     f32x2 g2[kAffine ? kVecs * kPairsPerVec : 1], b2[kAffine ? kVecs * kPairsPerVec : 1];
     if constexpr (kAffine) {
@@ -424,26 +416,24 @@ __device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, lon
         for (int i = 0; i < kVecs * kPairsPerVec; ++i) acc = pair_add(acc, x2[i]);  // padded vectors are zero
         float lo, hi;
         pair_split(acc, lo, hi);
-        Welford w;
-        w.n = (float)(my_vecs * kPer);
-        w.mean = my_vecs > 0 ? (lo + hi) / w.n : 0.f;
-        const f32x2 neg_local = pair_of(-w.mean, -w.mean);
+        const float mean = block_sum_fixed<kThreads>(lo + hi, s_exchange, 0) * inv_cols;
+        const f32x2 neg_mean = pair_of(-mean, -mean);
         f32x2 dev2 = pair_of(0.f, 0.f);
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
             f32x2 part = pair_of(0.f, 0.f);
 #pragma unroll
             for (int q = 0; q < kPairsPerVec; ++q) {
-                const f32x2 d = pair_add(x2[j * kPairsPerVec + q], neg_local);
+                const f32x2 d = pair_add(x2[j * kPairsPerVec + q], neg_mean);
+                x2[j * kPairsPerVec + q] = d;  // keep the centred value for the last pass
                 part = pair_fma(d, d, part);
             }
-            if (j < my_vecs) dev2 = pair_add(dev2, part);
+            if (j < my_vecs) dev2 = pair_add(dev2, part);  // padded vectors would add mean^2
         }
         pair_split(dev2, lo, hi);
-        w.m2 = lo + hi;
-        w = block_allreduce_welford_fixed<kThreads>(w, s_exchange);
-        const float rstd = rstd_from(w, cols, ddof, eps);
-        const f32x2 neg_mean = pair_of(-w.mean, -w.mean), rstd2 = pair_of(rstd, rstd);
+        const float var = block_sum_fixed<kThreads>(lo + hi, s_exchange, 1) * inv_denom;
+        const float rstd = rsqrtf(var + eps);
+        const f32x2 rstd2 = pair_of(rstd, rstd);
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
             const int v = threadIdx.x + kThreads * j;
@@ -451,7 +441,7 @@ __device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, lon
             f32x2 y2[kPairsPerVec];
 #pragma unroll
             for (int q = 0; q < kPairsPerVec; ++q) {
-                const f32x2 t = pair_mul(pair_add(x2[j * kPairsPerVec + q], neg_mean), rstd2);
+                const f32x2 t = pair_mul(x2[j * kPairsPerVec + q], rstd2);
                 y2[q] = kAffine ? pair_fma(t, g2[j * kPairsPerVec + q], b2[j * kPairsPerVec + q]) : t;
             }
             st_stream(out_v + row * nvec + v, Io::pack_pairs(y2));
