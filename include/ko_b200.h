@@ -45,6 +45,10 @@ int ko_version(void);
  * outstanding work, returns KO_ERR_TIMEOUT (and clears the words) if any kernel gave up since the
  * last poll, KO_OK otherwise.  No counterpart in the reference, whose kernels never wait. */
 int ko_poll_device_status(void);
+/* Exercises that path without any fault: launches a one-warp kernel that waits at most `polls`
+ * (1 .. 2^20) polls on an mbarrier nothing arrives at, lets the wait run out and records a code;
+ * the next ko_poll_device_status() returns KO_ERR_TIMEOUT.  No counterpart in the reference. */
+int ko_selftest_bounded_wait(unsigned polls, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Tensor: paired host (pinned) + device byte buffer.

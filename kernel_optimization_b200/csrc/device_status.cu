@@ -30,3 +30,34 @@ extern "C" int ko_poll_device_status(void) {
     }
     return KO_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Self-test of the failure-detection path: a kernel waits, with a short bound, on an mbarrier that
+// nothing ever arrives at; the wait runs out, the kernel records a code in the "reserved" status word
+// and returns normally.  The host then sees KO_ERR_TIMEOUT from ko_poll_device_status().  Nothing
+// faults, traps or hangs: this is how a stuck pipeline would surface in production.
+// ---------------------------------------------------------------------------------------------
+#include "../common/common.h"
+
+namespace {
+__global__ void bounded_wait_selftest_kernel(unsigned *status, unsigned polls) {
+    __shared__ unsigned long long bar;
+    const unsigned addr = ko::smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        ko::mbar_init(addr, 1);
+        ko::fence_barrier_init();
+        bool arrived = false;
+        for (unsigned spin = 0; spin < polls && !arrived; ++spin) arrived = ko::mbar_try_wait(addr, 0);
+        if (!arrived) atomicCAS(status, 0u, 0x7e57u);
+    }
+}
+}  // namespace
+
+extern "C" int ko_selftest_bounded_wait(unsigned polls, void *stream) {
+    unsigned *status = nullptr;
+    if (int st = ko::device_status_word(2, &status)) return st;
+    KO_REQUIRE(polls > 0 && polls <= (1u << 20), KO_ERR_INVALID_ARG, "selftest: polls must be in [1, 2^20]");
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, polls);
+    KO_CHECK_LAUNCH("bounded_wait_selftest_kernel");
+    return KO_OK;
+}

@@ -30,6 +30,7 @@ PROTOTYPES = {
     "ko_last_error_string": (C.c_char_p, []),
     "ko_version": (_int, []),
     "ko_poll_device_status": (_int, []),
+    "ko_selftest_bounded_wait": (_int, [C.c_uint, _vp]),
     "ko_tensor_create": (_int, [_sz, _int, C.POINTER(_vp)]),
     "ko_tensor_destroy": (_int, [_vp]),
     "ko_tensor_host_ptr": (_vp, [_vp]),

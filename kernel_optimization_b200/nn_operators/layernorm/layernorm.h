@@ -155,6 +155,77 @@ __device__ __forceinline__ void layernorm_rows_from_registers(const typename Row
                                                               typename RowIo<T>::Raw *out_v, int cols, float eps,
                                                               const typename RowIo<T>::Raw *gamma_v,
                                                               const typename RowIo<T>::Raw *beta_v, int ddof) {
+    using Io = RowIo<T>;
+    constexpr int kPer = Io::kPerVec, kPairsPerVec = kPer / 2;
+    if constexpr (kVecs * kPer <= 32) {  // depends on the row length only, so a row's bits do not depend on kRows
+        // Short rows: the whole row fits in registers as FP32, so it is unpacked once and all three passes
+        // run on packed FP32 pairs.  Statistics in their exact two-pass form: the warp-wide sum gives the row
+        // mean, then the squared deviations from THAT mean are summed (the value a Welford/Chan merge of the
+        // lanes' triples converges to, without the merges' ~70 instructions per row).
+        const float inv_cols = 1.0f / (float)cols;
+        const float inv_denom = cols - ddof > 0 ? 1.0f / (float)(cols - ddof) : 0.f;
+        f32x2 x2[kRows][kVecs * kPairsPerVec];
+        float mean[kRows], rstd[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            f32x2 acc = pair_of(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                Io::unpack_pairs(raw[r][j], x2[r] + j * kPairsPerVec);  // padded vectors are zero
+#pragma unroll
+                for (int q = 0; q < kPairsPerVec; ++q) acc = pair_add(acc, x2[r][j * kPairsPerVec + q]);
+            }
+            float lo, hi;
+            pair_split(acc, lo, hi);
+            mean[r] = lo + hi;
+        }
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) mean[r] = warp_allreduce_sum(mean[r]) * inv_cols;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const f32x2 neg_mean = pair_of(-mean[r], -mean[r]);
+            f32x2 dev2 = pair_of(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                f32x2 part = pair_of(0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < kPairsPerVec; ++q) {
+                    const f32x2 d = pair_add(x2[r][j * kPairsPerVec + q], neg_mean);
+                    x2[r][j * kPairsPerVec + q] = d;  // centred value, reused by the last pass
+                    part = pair_fma(d, d, part);
+                }
+                if (j < my_vecs) dev2 = pair_add(dev2, part);  // a padded vector would add mean^2
+            }
+            float lo, hi;
+            pair_split(dev2, lo, hi);
+            rstd[r] = lo + hi;
+        }
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) rstd[r] = rsqrtf(warp_allreduce_sum(rstd[r]) * inv_denom + eps);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = lane + 32 * j;
+            if (v >= nvec) continue;
+            f32x2 g2[kPairsPerVec], b2[kPairsPerVec];
+            if (gamma_v) Io::unpack_pairs(__ldg(gamma_v + v), g2);
+            if (beta_v) Io::unpack_pairs(__ldg(beta_v + v), b2);
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                if (row0 + r >= row_limit) continue;
+                const f32x2 rstd2 = pair_of(rstd[r], rstd[r]);
+                f32x2 y2[kPairsPerVec];
+#pragma unroll
+                for (int q = 0; q < kPairsPerVec; ++q) {
+                    f32x2 t = pair_mul(x2[r][j * kPairsPerVec + q], rstd2);
+                    if (gamma_v) t = beta_v ? pair_fma(t, g2[q], b2[q]) : pair_mul(t, g2[q]);
+                    else if (beta_v) t = pair_add(t, b2[q]);
+                    y2[q] = t;
+                }
+                st_stream(out_v + (row0 + r) * nvec + v, Io::pack_pairs(y2));
+            }
+        }
+        return;
+    }
     Welford stats[kRows];
 #pragma unroll
     for (int r = 0; r < kRows; ++r) stats[r] = welford_of_vectors<T, kVecs>(raw[r], my_vecs);
