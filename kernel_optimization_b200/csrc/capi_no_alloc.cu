@@ -29,6 +29,7 @@
 namespace {
 
 namespace x2 = ko::sgemm2;
+using Wide = x2::Shape<2, 2>;  // 128 x 128 tiles, one group of 4 warps per block
 
 constexpr size_t kMaxPartialFloats = (size_t)2 << 20;  // 2 Mi floats = 8 MiB, e.g. 1024 x 1024 outputs in 2 K-slices
 constexpr size_t kMaxTiles = 4096;                     // arrival counters (one per 128 x 128 output tile)
@@ -55,8 +56,8 @@ int setup_for_current_device(DeviceSetup **out) {
         unsigned char *ptr = nullptr;
         KO_CUDA(cudaGetSymbolAddress((void **)&ptr, g_no_alloc_scratch));
         KO_REQUIRE(ptr != nullptr, KO_ERR_CUDA, "cudaGetSymbolAddress returned a null scratch address");
-        KO_CUDA(cudaFuncSetAttribute(x2::sgemm_x2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, x2::kSmemBytes));
-        KO_CUDA(cudaFuncSetAttribute(x2::sgemm_x2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, x2::kSmemBytes));
+        KO_CUDA(cudaFuncSetAttribute(x2::sgemm_x2_kernel<true, 2, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Wide::smem_bytes(1)));
+        KO_CUDA(cudaFuncSetAttribute(x2::sgemm_x2_kernel<false, 2, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Wide::smem_bytes(1)));
         st.scratch = ptr;
         st.ready = true;
     }
@@ -82,10 +83,10 @@ extern "C" int ko_sgemm_f32_no_alloc(int64_t M, int64_t N, int64_t K, const floa
     if (int st = setup_for_current_device(&setup)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-    const long long tiles = ((M + x2::BM - 1) / x2::BM) * ((N + x2::BN - 1) / x2::BN);
+    const long long tiles = ((M + Wide::BM - 1) / Wide::BM) * ((N + Wide::BN - 1) / Wide::BN);
     const int ktiles = (int)((K + x2::BK - 1) / x2::BK);
     // how many K slices the fixed scratch can hold for this output size
-    long long fits = tiles <= (long long)kMaxTiles ? (long long)(kMaxPartialFloats / ((size_t)tiles * x2::kTileFloats)) : 0;
+    long long fits = tiles <= (long long)kMaxTiles ? (long long)(kMaxPartialFloats / ((size_t)tiles * Wide::kTileFloats)) : 0;
     if (fits < 1) fits = 1;  // one slice needs no scratch at all
     if (split_k == 0) {
         // same rule as ko_sgemm_f32 (fill the SMs, keep >= 8 K-tiles per slice), capped by the scratch
@@ -96,11 +97,11 @@ extern "C" int ko_sgemm_f32_no_alloc(int64_t M, int64_t N, int64_t K, const floa
     KO_REQUIRE(split_k <= fits, KO_ERR_SHAPE,
                "sgemm (no-alloc): %lld output tiles in %d K-slices need %lld scratch floats (and %lld counters); the "
                "fixed scratch holds %zu floats and %zu counters -- use fewer slices (at most %lld here) or ko_sgemm_f32",
-               tiles, split_k, tiles * split_k * (long long)x2::kTileFloats, tiles, kMaxPartialFloats, kMaxTiles, fits);
+               tiles, split_k, tiles * split_k * (long long)Wide::kTileFloats, tiles, kMaxPartialFloats, kMaxTiles, fits);
     KO_REQUIRE(tiles * split_k <= 0x7fffffffLL, KO_ERR_SHAPE, "sgemm (no-alloc): too many blocks");
 
     // tiles * split_k blocks: every tile is cut into split_k K-slices, one scratch slot per slice
-    x2::Params p{(int)M, (int)N, (int)K, A, B, C, D, (int)(tiles * split_k), split_k, nullptr, nullptr};
+    x2::Params p{(int)M, (int)N, (int)K, A, B, C, D, (int)(tiles * split_k), split_k, 0, nullptr, nullptr};
     if (split_k > 1) {
         p.workspace = reinterpret_cast<float *>(setup->scratch);
         p.counters = reinterpret_cast<unsigned *>(setup->scratch + kCounterOffset);
@@ -109,8 +110,8 @@ extern "C" int ko_sgemm_f32_no_alloc(int64_t M, int64_t N, int64_t K, const floa
     }
     const bool vec_b = N % 4 == 0 && ko::aligned16(B);
     const unsigned grid = (unsigned)(tiles * split_k);
-    if (vec_b) x2::sgemm_x2_kernel<true><<<grid, x2::kThreads, x2::kSmemBytes, s>>>(p);
-    else x2::sgemm_x2_kernel<false><<<grid, x2::kThreads, x2::kSmemBytes, s>>>(p);
+    if (vec_b) x2::sgemm_x2_kernel<true, 2, 2, 1><<<grid, Wide::kGroupThreads, Wide::smem_bytes(1), s>>>(p);
+    else x2::sgemm_x2_kernel<false, 2, 2, 1><<<grid, Wide::kGroupThreads, Wide::smem_bytes(1), s>>>(p);
     KO_CHECK_LAUNCH("sgemm_x2_kernel (no-alloc)");
     return KO_OK;
 }

@@ -70,58 +70,89 @@ int get_scratch(cudaStream_t s, size_t partial_floats, size_t counter_count, Scr
     return KO_OK;
 }
 
-// split_k: 0 = choose the block count (stream-K), 1 = one block per tile, n > 1 = n K-slices per tile
-int launch_x2(int M, int N, int K, const float *A, const float *B, const float *C, float *D, int split_k, int sm_count,
-              cudaStream_t s) {
+// One launch of sgemm_x2_kernel<kVecB, kWarpsM, kWarpsN, kGroups>.
+// split_k: 0 = choose the block count, 1 = one block per tile, n > 1 = n K-slices per tile.
+template <int kWarpsM, int kWarpsN, int kGroups>
+int launch_x2_shape(int M, int N, int K, const float *A, const float *B, const float *C, float *D, int split_k,
+                    int sm_count, cudaStream_t s) {
     namespace x2 = ko::sgemm2;
-    const long long tiles = (long long)((M + x2::BM - 1) / x2::BM) * ((N + x2::BN - 1) / x2::BN);
+    using S = x2::Shape<kWarpsM, kWarpsN>;
+    const long long tiles = (long long)((M + S::BM - 1) / S::BM) * ((N + S::BN - 1) / S::BN);
     const int ktiles = (K + x2::BK - 1) / x2::BK;
     const long long units = tiles * ktiles;
+    const long long slots = (kGroups == 1 ? 2LL : 1LL) * sm_count;  // blocks resident at a time
     long long ctas = tiles;
     int max_contrib = 1;
+    bool ranges = false;  // blocks own contiguous unit ranges that may straddle tiles
     if (split_k > 1) {
         if (split_k > ktiles) split_k = ktiles;
         ctas = tiles * split_k;
         max_contrib = split_k;  // slices of a uniform split never straddle a tile
     } else if (split_k == 0 && tiles * 2 <= sm_count) {
-        // few tiles (1024^3 has 64): a uniform split that gives about one block per SM measured faster than
-        // finer ranges, whose partial-tile traffic and short K loops cost more than the idle SMs
+        // few tiles: a uniform split that gives about one block per SM measured faster than finer ranges,
+        // whose partial-tile traffic and short K loops cost more than the idle SMs
         int split = (int)(sm_count / tiles);
         while (split > 1 && ktiles / split < 16) --split;
         if (split > 1) {
             ctas = tiles * split;
             max_contrib = split;
         }
-    } else if (split_k == 0 && tiles < 4LL * sm_count) {
-        // two blocks fit per SM: hand every slot the same number of (tile, K-tile) units, as long as a
-        // block still gets at least 8 K-tiles to amortise its pipeline fill and the partial-tile traffic
-        const long long slots = 2LL * sm_count;
-        if (tiles % slots != 0) {
-            ctas = slots;
-            if (units / ctas < 8) ctas = units / 8 > tiles ? units / 8 : tiles;
-        }
-        if (ctas != tiles) {
-            const long long per_block = units / ctas;  // floor: the shortest range
-            max_contrib = (int)((ktiles + per_block - 1) / per_block) + 1;
-            if (max_contrib > ctas) max_contrib = (int)ctas;
-        }
+    } else if (split_k == 0 && kGroups == 1 && tiles < 2 * slots && tiles % slots != 0) {
+        // up to two waves of whole tiles, the last one partly empty: hand every slot the same number of
+        // (tile, K-tile) units instead, as long as a block still gets at least 8 K-tiles to amortise its
+        // pipeline fill and the partial-tile traffic.  (With more waves the tail costs less than the
+        // partial tiles: 4096^3, 3.46 waves, measured 2510 us as whole tiles and 2584 us as ranges.)
+        ctas = slots;
+        if (units / ctas < 8) ctas = units / 8 > tiles ? units / 8 : tiles;
+        ranges = ctas != tiles;
     }
     KO_REQUIRE(ctas <= 0x7fffffffLL, KO_ERR_SHAPE, "sgemm: %lld blocks exceed the grid limit", ctas);
-    x2::Params p{M, N, K, A, B, C, D, (int)ctas, max_contrib, nullptr, nullptr};
+    x2::Params p{M, N, K, A, B, C, D, (int)ctas, max_contrib, ranges ? 1 : 0, nullptr, nullptr};
     if (ctas != tiles) {
+        if (ranges) {
+            const long long per_block = units / ctas;  // floor: the shortest range
+            const long long most = (ktiles + per_block - 1) / per_block + 1;
+            p.max_contrib = (int)(most > ctas ? ctas : most);
+        }
         Scratch sc;
-        if (int st = get_scratch(s, (size_t)tiles * max_contrib * x2::kTileFloats, (size_t)tiles, &sc)) return st;
+        const size_t partials = ranges ? (size_t)ctas * 2 : (size_t)tiles * max_contrib;
+        if (int st = get_scratch(s, partials * S::kTileFloats, (size_t)tiles, &sc)) return st;
         p.workspace = sc.partials;
         p.counters = sc.counters;
     }
     const bool vec_b = N % 4 == 0 && ko::aligned16(B);
-    const void *kernel = vec_b ? reinterpret_cast<const void *>(x2::sgemm_x2_kernel<true>)
-                               : reinterpret_cast<const void *>(x2::sgemm_x2_kernel<false>);
-    if (int st = ko::ensure_dynamic_smem(kernel, x2::kSmemBytes)) return st;
-    if (vec_b) x2::sgemm_x2_kernel<true><<<(unsigned)ctas, x2::kThreads, x2::kSmemBytes, s>>>(p);
-    else x2::sgemm_x2_kernel<false><<<(unsigned)ctas, x2::kThreads, x2::kSmemBytes, s>>>(p);
+    constexpr int smem_bytes = S::smem_bytes(kGroups);
+    auto go = [&](auto kernel) -> int {
+        if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), smem_bytes)) return st;
+        kernel<<<(unsigned)ctas, S::kGroupThreads * kGroups, smem_bytes, s>>>(p);
+        return KO_OK;
+    };
+    const int st = vec_b ? go(x2::sgemm_x2_kernel<true, kWarpsM, kWarpsN, kGroups>) : go(x2::sgemm_x2_kernel<false, kWarpsM, kWarpsN, kGroups>);
+    if (st) return st;
     KO_CHECK_LAUNCH("sgemm_x2_kernel");
     return KO_OK;
+}
+
+// shape: 0 = choose; 1 = 128 x 128 tiles, 128-thread blocks (two per SM); 2 = 128 x 128 tiles, two groups of
+// 4 warps halve the block's K range; 3 = 64 x 128 tiles, four groups of 2 warps quarter it.
+int launch_x2(int M, int N, int K, const float *A, const float *B, const float *C, float *D, int split_k, int shape,
+              int sm_count, cudaStream_t s) {
+    if (shape == 0) {
+        // The grouped shapes add K parts like K-slices, so they are chosen only when the caller left the
+        // split to us.  At most one 128 x 128 tile per SM: groups give every scheduler a second warp, and
+        // the half-height tile doubles the tile count, which saves or shortens the split across blocks
+        // (1024^3: 63.8 us as 128-thread blocks, 55.5 us grouped; 512^3: 37.2 -> 22.8 us; 1536^3: 160 -> 152 us;
+        // from 2048^3 on two 128-thread blocks per SM are faster).
+        const long long wide_tiles = (long long)((M + 127) / 128) * ((N + 127) / 128);
+        const int ktiles = (K + ko::sgemm2::BK - 1) / ko::sgemm2::BK;
+        shape = 1;
+        if (split_k == 0 && wide_tiles <= sm_count && ktiles >= 8) shape = (M > 64 && ktiles >= 16) ? 3 : 2;
+    }
+    switch (shape) {
+        case 1: return launch_x2_shape<2, 2, 1>(M, N, K, A, B, C, D, split_k, sm_count, s);
+        case 2: return launch_x2_shape<2, 2, 2>(M, N, K, A, B, C, D, split_k, sm_count, s);
+        default: return launch_x2_shape<1, 2, 4>(M, N, K, A, B, C, D, split_k, sm_count, s);
+    }
 }
 
 int launch_a8(int M, int N, int K, const float *A, const float *B, const float *C, float *D, cudaStream_t s) {
@@ -164,7 +195,10 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
     if (K == 0 && variant >= 4) variant = 3;  // an empty sum: D = C (or 0), nothing to pipeline
     const int m = (int)M, n = (int)N, k = (int)K;
     switch (variant) {
-        case 4: return launch_x2(m, n, k, A, B, C, D, split_k, info.sm_count, s);
+        case 4: return launch_x2(m, n, k, A, B, C, D, split_k, 0, info.sm_count, s);
+        case 6: return launch_x2(m, n, k, A, B, C, D, split_k, 1, info.sm_count, s);  // 128 x 128, 128-thread blocks
+        case 7: return launch_x2(m, n, k, A, B, C, D, split_k, 2, info.sm_count, s);  // 128 x 128, two warp groups
+        case 8: return launch_x2(m, n, k, A, B, C, D, split_k, 3, info.sm_count, s);  // 64 x 128, four warp groups
         case 5: return launch_a8(m, n, k, A, B, C, D, s);
         case 1: return launch<CfgBig>(m, n, k, A, B, C, D, aligned, s);
         case 2: return launch<CfgWide>(m, n, k, A, B, C, D, aligned, s);

@@ -32,7 +32,9 @@ int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int
                             const uint16_t *gamma, const uint16_t *beta, int ddof, const ko_row_knobs_t *knobs,
                             void *stream);
 /* variant: 0 = choose, 1..3 = scalar-FFMA tilings (128x128, 128x64, 64x64), 4 = packed-FFMA 128x128 kernel;
- * 5 = 128x64 scalar-FFMA cp.async kernel; split_k (variant 4): 0 = choose the block count (stream-K),
+ * 5 = 128x64 scalar-FFMA cp.async kernel; 6 / 7 / 8 = variant 4 pinned to 128x128 tiles with 128-thread
+ * blocks / 128x128 tiles with two warp groups that halve the block's K range / 64x128 tiles with four
+ * warp groups that quarter it; split_k (variants 4, 6, 7, 8): 0 = choose the block count (stream-K),
  * 1 = one block per tile, n > 1 = n K-slices per tile */
 int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
                        int variant, int split_k, void *stream);

@@ -26,7 +26,7 @@ SHAPES = [(1, 1, 1), (64, 64, 8), (100, 36, 52), (129, 65, 17), (256, 256, 256),
           (128, 128, 1), (640, 384, 72)]
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5, 6])
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_unsplit_kernels_are_bit_identical_to_the_reference_order(cuda, lib, oracle, M, N, K, variant):
     a, b, c = oracle.fill_uniform((M, K), 2, 0), oracle.fill_uniform((K, N), 2, 1), oracle.fill_uniform((M, N), 2, 2)
@@ -46,6 +46,37 @@ def test_split_k_is_deterministic_and_within_tolerance(cuda, lib, oracle, M, N, 
         assert oracle.rel_frobenius(d, oracle.sgemm_f64(a, b, cc)) <= TOL_FRO
         assert np.array_equal(d, _run(cuda, lib, a, b, cc, 4, split_k=split_k)), "slices are added in a fixed order"
         # only the association of the K sum differs from the sequential order (whose own error grows with K)
+        assert oracle.rel_frobenius(d, oracle.sgemm_f32(a, b, cc).astype(np.float64)) <= 3 * TOL_FRO
+
+
+@pytest.mark.parametrize("variant", [7, 8])   # two groups of 4 warps on 128x128 tiles, four groups of 2 warps on 64x128 tiles
+@pytest.mark.parametrize("split_k", [0, 1, 2, 3])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (128, 128, 16), (100, 36, 52), (129, 65, 17), (256, 256, 256), (300, 200, 1000),
+                                   (17, 513, 33), (1024, 1024, 1024), (64, 64, 4096), (1920, 1152, 136)])
+def test_warp_groups_split_k_inside_the_block(cuda, lib, oracle, M, N, K, variant, split_k):
+    """The groups' K parts are added in K order through shared memory: deterministic, within the tolerance,
+    and (a single K-tile has nothing to split) bit-identical to the reference order when K <= 16."""
+    a, b, c = oracle.fill_uniform((M, K), 2, 0), oracle.fill_uniform((K, N), 2, 1), oracle.fill_uniform((M, N), 2, 2)
+    for cc in (None, c):
+        d = _run(cuda, lib, a, b, cc, variant, split_k=split_k)
+        assert oracle.rel_frobenius(d, oracle.sgemm_f64(a, b, cc)) <= TOL_FRO
+        assert np.array_equal(d, _run(cuda, lib, a, b, cc, variant, split_k=split_k))
+        seq = oracle.sgemm_f32(a, b, cc)
+        assert oracle.rel_frobenius(d, seq.astype(np.float64)) <= 3 * TOL_FRO
+        if K <= 16:
+            assert np.array_equal(d, seq)
+
+
+@pytest.mark.parametrize("M,N,K", [(2560, 2560, 256), (2304, 2432, 130), (1664, 1664, 512)])
+def test_unit_ranges_that_straddle_tiles(cuda, lib, oracle, M, N, K):
+    """More tiles than resident blocks but a partly empty last wave: blocks own equal ranges of (tile, K-tile)
+    units and keep their two partial tiles in per-block workspace slots."""
+    a, b, c = oracle.fill_uniform((M, K), 2, 0), oracle.fill_uniform((K, N), 2, 1), oracle.fill_uniform((M, N), 2, 2)
+    for cc in (None, c):
+        d = _run(cuda, lib, a, b, cc, 6, split_k=0)
+        assert oracle.rel_frobenius(d, oracle.sgemm_f64(a, b, cc)) <= TOL_FRO
+        assert np.array_equal(d, _run(cuda, lib, a, b, cc, 6, split_k=0))    # counters are back at zero, same order
+        assert np.array_equal(d, _run(cuda, lib, a, b, cc, 4, split_k=0))    # the default picks the same kernel here
         assert oracle.rel_frobenius(d, oracle.sgemm_f32(a, b, cc).astype(np.float64)) <= 3 * TOL_FRO
 
 
