@@ -158,18 +158,33 @@ int ko_sgemm_f32_no_alloc(int64_t M, int64_t N, int64_t K, const float *A, const
                           const float *C, float *D, int split_k, void *stream);
 
 /* ------------------------------------------------------------------------------------------
- * Tensor-core GEMM: D[M,N] (FP32, row-major) = A[M,K] (row-major) * B[K,N] (column-major, i.e.
- * element (k,n) at B[n*K + k]) (+ C[M,N] FP32 when C != NULL); FP16 or BF16 inputs as raw
- * uint16, FP32 accumulate in tensor memory (tcgen05.mma), TMA-fed.
+ * Tensor-core GEMM: D[M,N] (row-major) = A[M,K] (row-major) * B[K,N] (+ C[M,N] when C != NULL);
+ * FP16 or BF16 inputs as raw uint16, FP32 accumulate in tensor memory (tcgen05.mma), TMA-fed.
  * Stands in for gemm<GemmKernelTensorCore<half,half,half,GemmShape<128,128,32>,
  * GemmShape<64,64,32>,GemmShape<16,8,8>,8,8,8>>: nn_operators/gemm/tensor_core_gemm.h:101-399
  * (disabled call at nn_operators/gemm/main.cu:344).
- * Requires K % 8 == 0, N % 4 == 0 and 16-byte aligned pointers; M, N, K tails are handled.
+ *
+ * B is column-major in the named entry points, i.e. element (k,n) at B[n*K + k] (what the
+ * reference's kernel multiplies after its transposing ldmatrix, tensor_core_gemm.h:171-179);
+ * ko_gemm_tc also takes the reference driver's row-major B[K,N] (element (k,n) at B[k*N + n],
+ * nn_operators/gemm/main.cu:201-203) with b_row_major = 1.
+ * D and C are FP32 (.._f32) or the input type (.._f16 / .._bf16: the reference's ElementC = half,
+ * nn_operators/gemm/main.cu:190-192; the FP32 sum plus C is rounded to nearest even once).
+ * Requires K % 8 == 0 (and N % 8 == 0 for row-major B) and 16-byte aligned A and B; M, N, K tails
+ * are handled; an unaligned or odd-pitch D falls back from 16-byte to scalar stores.
  * ---------------------------------------------------------------------------------------- */
 int ko_gemm_f16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
                     const float *C, float *D, void *stream);
 int ko_gemm_bf16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
                      const float *C, float *D, void *stream);
+int ko_gemm_f16_f16(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
+                    const uint16_t *C, uint16_t *D, void *stream);
+int ko_gemm_bf16_bf16(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
+                      const uint16_t *C, uint16_t *D, void *stream);
+/* in_fmt: 0 = FP16, 1 = BF16 (A and B); out_fmt: 0 = FP32, 1 = FP16, 2 = BF16 (D and C);
+ * b_row_major: 0 = column-major B, 1 = row-major B. */
+int ko_gemm_tc(int in_fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K,
+               const void *A, const void *B, const void *C, void *D, void *stream);
 
 #ifdef __cplusplus
 }

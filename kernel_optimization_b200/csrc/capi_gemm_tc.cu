@@ -47,6 +47,20 @@ int make_map(EncodeTiledFn encode, CUtensorMap *map, int fmt, const void *base, 
     return KO_OK;
 }
 
+// 2-D map over a row-major 16-bit B[K, N] (N contiguous); box = 64 columns x 64 K-rows, 128-byte swizzle
+int make_map_b_row_major(EncodeTiledFn encode, CUtensorMap *map, int fmt, const void *base, int64_t K, int64_t N) {
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
+    const cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)ko::tc::kBK};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUtensorMapDataType dt = fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUresult r = encode(map, dt, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KO_REQUIRE(r == CUDA_SUCCESS, KO_ERR_CUDA, "cuTensorMapEncodeTiled (row-major B) failed with CUresult %d", (int)r);
+    return KO_OK;
+}
+
 template <int BN, bool kTmaStore>
 int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &md, const ko::tc::GemmParams &p, int sm_count,
            cudaStream_t s) {
@@ -60,14 +74,18 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &md, 
     return KO_OK;
 }
 
-// FP32 [M, N] row-major output, boxes of 32 rows x 32 columns (128 bytes, 128-byte swizzle)
-int make_store_map(EncodeTiledFn encode, CUtensorMap *map, float *D, int64_t M, int64_t N) {
+// [M, N] row-major output, boxes of 32 rows x 32 columns: FP32 rows of 128 bytes with the 128-byte swizzle,
+// 16-bit rows of 64 bytes with the 64-byte swizzle
+int make_store_map(EncodeTiledFn encode, CUtensorMap *map, int out_fmt, void *D, int64_t M, int64_t N) {
     const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+    const cuuint64_t strides[1] = {(cuuint64_t)N * (out_fmt == 0 ? 4 : 2)};
     const cuuint32_t box[2] = {32, 32};
     const cuuint32_t elem_strides[2] = {1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, D, dims, strides, box, elem_strides,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+    const CUtensorMapDataType dt = out_fmt == 0   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : out_fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUresult r = encode(map, dt, 2, D, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              out_fmt == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     KO_REQUIRE(r == CUDA_SUCCESS, KO_ERR_CUDA, "cuTensorMapEncodeTiled (D) failed with CUresult %d", (int)r);
     return KO_OK;
@@ -83,21 +101,25 @@ double wave_efficiency(long long M, long long N, int bn, int sm_count) {
 
 extern "C" {
 
-// fmt: 0 = F16, 1 = BF16; bn: 0 = choose, else 64 / 128 / 256 columns per tile;
+// fmt: A and B, 0 = F16, 1 = BF16; out_fmt: D and C, 0 = FP32, 1 = F16, 2 = BF16; b_row_major: 0 = B[K,N]
+// column-major (K contiguous), 1 = row-major (N contiguous); bn: 0 = choose, else 64 / 128 / 256 columns per tile;
 // store_mode: 0 = choose, 1 = TMA-store epilogue (error if not possible), 2 = direct stores
-int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C,
-                     float *D, int bn, int store_mode, void *stream) {
+int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
+                     const void *C, void *D, int bn, int store_mode, void *stream) {
     KO_REQUIRE(fmt == 0 || fmt == 1, KO_ERR_INVALID_ARG, "gemm: fmt must be 0 (f16) or 1 (bf16)");
+    KO_REQUIRE(out_fmt >= 0 && out_fmt <= 2, KO_ERR_INVALID_ARG, "gemm: out_fmt must be 0 (f32), 1 (f16) or 2 (bf16)");
+    KO_REQUIRE(b_row_major == 0 || b_row_major == 1, KO_ERR_INVALID_ARG, "gemm: b_row_major must be 0 or 1");
     KO_REQUIRE(M >= 0 && N >= 0 && K >= 0, KO_ERR_INVALID_ARG, "gemm: negative shape {%lld,%lld,%lld}", (long long)M,
                (long long)N, (long long)K);
     if (M == 0 || N == 0) return KO_OK;
     KO_REQUIRE(M <= 0x7fffffff && N <= 0x7fffffff && K <= 0x7fffffff, KO_ERR_SHAPE, "gemm: dimension exceeds 2^31-1");
     KO_REQUIRE(K >= 8 && K % 8 == 0, KO_ERR_SHAPE, "gemm: K = %lld must be a positive multiple of 8 (16-byte row pitch)",
                (long long)K);
+    KO_REQUIRE(!b_row_major || N % 8 == 0, KO_ERR_SHAPE, "gemm: row-major B needs N = %lld to be a multiple of 8 (16-byte row pitch)",
+               (long long)N);
     KO_REQUIRE(A != nullptr && B != nullptr && D != nullptr, KO_ERR_INVALID_ARG, "gemm: NULL pointer");
     KO_REQUIRE(ko::aligned16(A) && ko::aligned16(B), KO_ERR_ALIGN, "gemm: A and B must be 16-byte aligned");
-    KO_REQUIRE((const void *)D != (const void *)A && (const void *)D != (const void *)B, KO_ERR_INVALID_ARG,
-               "gemm: D must not alias A or B");
+    KO_REQUIRE((const void *)D != A && (const void *)D != B, KO_ERR_INVALID_ARG, "gemm: D must not alias A or B");
     ko::DeviceInfo info;
     if (int st = ko::current_device_info(&info)) return st;
     EncodeTiledFn encode = nullptr;
@@ -113,19 +135,21 @@ int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A
 
     alignas(64) CUtensorMap map_a, map_b, map_d;
     if (int st = make_map(encode, &map_a, fmt, A, M, K, ko::tc::kBM)) return st;
-    if (int st = make_map(encode, &map_b, fmt, B, N, K, bn)) return st;
+    if (int st = b_row_major ? make_map_b_row_major(encode, &map_b, fmt, B, K, N) : make_map(encode, &map_b, fmt, B, N, K, bn))
+        return st;
     // TMA-store epilogue when D has a 16-byte pitch and nothing is added to it
-    const bool tma_store = store_mode != 2 && C == nullptr && N % 4 == 0 && ko::aligned16(D);
-    KO_REQUIRE(store_mode != 1 || tma_store, KO_ERR_SHAPE, "gemm: the TMA-store epilogue needs C == NULL, N %% 4 == 0 and a 16-byte aligned D");
+    const bool tma_store = store_mode != 2 && C == nullptr && N % (out_fmt == 0 ? 4 : 8) == 0 && ko::aligned16(D);
+    KO_REQUIRE(store_mode != 1 || tma_store, KO_ERR_SHAPE,
+               "gemm: the TMA-store epilogue needs C == NULL and a 16-byte row pitch and base for D");
     if (tma_store) {
-        if (int st = make_store_map(encode, &map_d, D, M, N)) return st;
+        if (int st = make_store_map(encode, &map_d, out_fmt, D, M, N)) return st;
     } else {
         map_d = map_a;  // unused by the direct-store epilogue
     }
 
     ko::tc::GemmParams p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
-    p.C = C; p.D = D; p.fmt = fmt;
+    p.C = C; p.D = D; p.fmt = fmt; p.out_fmt = out_fmt; p.b_row_major = b_row_major;
     if (int st = ko::device_status_word(0, &p.status)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (bn) {
@@ -135,14 +159,29 @@ int ko_gemm_tc_tuned(int fmt, int64_t M, int64_t N, int64_t K, const uint16_t *A
     }
 }
 
+int ko_gemm_tc(int in_fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
+               const void *C, void *D, void *stream) {
+    return ko_gemm_tc_tuned(in_fmt, out_fmt, b_row_major, M, N, K, A, B, C, D, 0, 0, stream);
+}
+
 int ko_gemm_f16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C, float *D,
                     void *stream) {
-    return ko_gemm_tc_tuned(0, M, N, K, A, B, C, D, 0, 0, stream);
+    return ko_gemm_tc_tuned(0, 0, 0, M, N, K, A, B, C, D, 0, 0, stream);
 }
 
 int ko_gemm_bf16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C, float *D,
                      void *stream) {
-    return ko_gemm_tc_tuned(1, M, N, K, A, B, C, D, 0, 0, stream);
+    return ko_gemm_tc_tuned(1, 0, 0, M, N, K, A, B, C, D, 0, 0, stream);
+}
+
+int ko_gemm_f16_f16(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const uint16_t *C, uint16_t *D,
+                    void *stream) {
+    return ko_gemm_tc_tuned(0, 1, 0, M, N, K, A, B, C, D, 0, 0, stream);
+}
+
+int ko_gemm_bf16_bf16(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const uint16_t *C, uint16_t *D,
+                      void *stream) {
+    return ko_gemm_tc_tuned(1, 2, 0, M, N, K, A, B, C, D, 0, 0, stream);
 }
 
 }  // extern "C"

@@ -55,6 +55,9 @@ PROTOTYPES = {
     "ko_sgemm_f32_no_alloc": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),
     "ko_gemm_f16_f32": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ko_gemm_bf16_f32": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "ko_gemm_f16_f16": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "ko_gemm_bf16_bf16": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "ko_gemm_tc": (_int, [_int, _int, _int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
 }
 
 class RowKnobs(C.Structure):
@@ -72,7 +75,7 @@ TUNING_PROTOTYPES = {
     "ko_layernorm_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),
     "ko_layernorm_bf16_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),
     "ko_sgemm_f32_tuned": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _int, _vp]),
-    "ko_gemm_tc_tuned": (_int, [_int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "ko_gemm_tc_tuned": (_int, [_int, _int, _int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _int, _vp]),
 }
 
 _lib = None

@@ -1,5 +1,5 @@
-// Tensor-core GEMM for sm_100a: D[M,N] (FP32) = A[M,K] (row-major) * B[K,N] (column-major) (+ C),
-// FP16 or BF16 inputs, FP32 accumulation in tensor memory.
+// Tensor-core GEMM for sm_100a: D[M,N] = A[M,K] (row-major) * B[K,N] (column- or row-major) (+ C),
+// FP16 or BF16 inputs, FP32 accumulation in tensor memory, D (and C) FP32 or rounded once to FP16 / BF16.
 //
 // Stands in for the reference's GemmKernelTensorCore (nn_operators/gemm/tensor_core_gemm.h:101-399),
 // a Turing mma.sync.m16n8k8 kernel with FP16 accumulation that is unfinished and disabled there.
@@ -20,7 +20,18 @@
 // (2 x BN columns) so the epilogue of one tile overlaps the MMAs of the next.
 //
 // M, N and K tails: TMA zero-fills out-of-range rows/columns, zero K-columns add nothing, and the
-// epilogue predicates its stores.  K must be a multiple of 8 (16-byte global row pitch for TMA).
+// epilogue predicates its stores.  K must be a multiple of 8 (16-byte global row pitch for TMA), and so
+// must N when B is row-major.
+//
+// B layouts.  Column-major B[K,N] (K contiguous, the layout the reference's kernel consumes after its
+// ldmatrix.trans, tensor_core_gemm.h:171-179) is a K-major operand: one TMA box of BN rows x 64 K.
+// Row-major B[K,N] (N contiguous) is an MN-major operand: BN/64 boxes of 64 K-rows x 64 columns, each
+// 8 swizzle atoms (8 K-rows x 128 bytes) stacked along K; the matrix descriptor then steps 1024 bytes
+// per 8 K and 8192 bytes per 64 columns, and the instruction descriptor marks B as MN-major.
+//
+// 16-bit output (the reference's ElementC = half, nn_operators/gemm/main.cu:190-192): the FP32
+// accumulator (plus C, read in D's type) is rounded to nearest even once, in the epilogue.  The
+// reference accumulates in FP16 inside mma.sync; that loss is not reproduced.
 //
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the waiting role records a code in the
 // device status word, raises the CTA's abort flag and all roles drain and leave; tensor memory is
@@ -160,14 +171,79 @@ __device__ __forceinline__ void tile_coords(long long t, int tiles_m, int tiles_
 
 struct GemmParams {
     int M, N, K;
-    const float *C;   // may be null
-    float *D;
+    const void *C;    // may be null; same element type as D
+    void *D;
     unsigned *status; // device status word
-    int fmt;          // 0 = F16, 1 = BF16
+    int fmt;          // A and B: 0 = F16, 1 = BF16
+    int out_fmt;      // D and C: 0 = FP32, 1 = F16, 2 = BF16
+    int b_row_major;  // 0: B[K,N] column-major (K contiguous); 1: row-major (N contiguous)
 };
 
-// kTmaStore: D is written by TMA stores staged through shared memory (needs N % 4 == 0, 16-byte aligned D,
-// no C operand); otherwise every thread stores its row segment directly (and adds C when given)
+// MN-major operand tile made of 64-column blocks of 64 K-rows x 128 bytes (128-byte swizzle): 8-K-row
+// atoms are 1024 bytes apart (stride offset), 64-column blocks 8192 bytes apart (leading offset).
+__device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)(8192 >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// two floats rounded to the 16-bit output type, low half first
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, int out_fmt) {
+    if (out_fmt == 1) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+    const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&b);
+}
+
+// one thread's 32 consecutive columns of row `row`, starting at column `col`: D = acc (+ C), predicated on N
+template <typename T>
+__device__ __forceinline__ void store_row_segment(const float (&v)[32], const GemmParams &p, int row, int col) {
+    constexpr int kVec = 16 / (int)sizeof(T);  // elements per 16-byte access
+    const T *C = static_cast<const T *>(p.C);
+    T *D = static_cast<T *>(p.D);
+    const bool vec_ok = (p.N % kVec == 0) && ((reinterpret_cast<uintptr_t>(D) & 15u) == 0) &&
+                        (C == nullptr || (reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+    const size_t off = (size_t)row * p.N + col;
+    if (vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j += kVec) {
+            if (col + j < p.N) {
+                alignas(16) T o[kVec];
+                if (C) {
+                    alignas(16) T c[kVec];
+                    *reinterpret_cast<uint4 *>(c) = *reinterpret_cast<const uint4 *>(C + off + j);
+#pragma unroll
+                    for (int e = 0; e < kVec; ++e) o[e] = from_float<T>(v[j + e] + to_float(c[e]));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < kVec; ++e) o[e] = from_float<T>(v[j + e]);
+                }
+                *reinterpret_cast<uint4 *>(D + off + j) = *reinterpret_cast<const uint4 *>(o);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col + j < p.N) D[off + j] = from_float<T>(C ? v[j] + to_float(C[off + j]) : v[j]);
+    }
+}
+
+// kTmaStore: D is written by TMA stores staged through shared memory (needs a 16-byte row pitch and base for D
+// and no C operand); otherwise every thread stores its row segment directly (and adds C when given)
 template <int BN, bool kTmaStore>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -237,7 +313,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
                     const uint32_t dst = ring + s * Cfg::kStageBytes;
                     tma_load_2d(dst, &map_a, kb * kBK, tm * kBM, full_bar(s));
-                    tma_load_2d(dst + Cfg::kBytesA, &map_b, kb * kBK, tn * BN, full_bar(s));
+                    if (!p.b_row_major) {
+                        tma_load_2d(dst + Cfg::kBytesA, &map_b, kb * kBK, tn * BN, full_bar(s));
+                    } else {
+#pragma unroll
+                        for (int nb = 0; nb < BN / 64; ++nb)
+                            tma_load_2d(dst + Cfg::kBytesA + nb * 8192, &map_b, tn * BN + nb * 64, kb * kBK, full_bar(s));
+                    }
                 }
             }
             if (!ok) {
@@ -254,7 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(p.fmt, kBM, BN);
+            const uint32_t idesc = make_idesc(p.fmt, kBM, BN) | (p.b_row_major ? 1u << 16 : 0u);  // bit 16: B is MN-major
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
             for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
@@ -272,7 +354,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
                         // advancing K inside the swizzled row: +32 bytes per 16 elements
                         const uint64_t da = smem_desc_k_major_sw128(a_addr + k * kUmmaK * 2);
-                        const uint64_t db = smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
+                        // row-major B: 16 K-rows further = two 8-row atoms = 2048 bytes
+                        const uint64_t db = p.b_row_major ? smem_desc_mn_major_sw128(b_addr + k * 2048)
+                                                          : smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
                         umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));  // the stage is reusable once these MMAs have read it
@@ -293,8 +377,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
-        const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0) &&
-                            (p.C == nullptr || (reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
         uint32_t local_tile = 0;
         bool ok = true;
         for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
@@ -322,12 +404,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t box = store_base + (uint32_t)(ep_warp * 2 + ((c0 >> 5) & 1)) * Cfg::kStoreBoxBytes;
                     if (lane == 0) bulk_wait_group_read<1>();  // the store issued from this box two chunks ago has read it
                     __syncwarp();
+                    if (p.out_fmt == 0) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint32_t dst = box + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
-                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]),
-                                     "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
-                                     : "memory");
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t dst = box + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                                         "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                                         : "memory");
+                        }
+                    } else {
+                        // 16-bit D: rows of 64 bytes, 4 chunks of 16 B, chunk j stored at j ^ ((row >> 1) & 3): the
+                        // 64-byte swizzle of the store's tensor map, conflict-free for 8 consecutive rows
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t dst = box + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                         "r"(pack16(v[8 * j], v[8 * j + 1], p.out_fmt)), "r"(pack16(v[8 * j + 2], v[8 * j + 3], p.out_fmt)),
+                                         "r"(pack16(v[8 * j + 4], v[8 * j + 5], p.out_fmt)), "r"(pack16(v[8 * j + 6], v[8 * j + 7], p.out_fmt))
+                                         : "memory");
+                        }
                     }
                     fence_proxy_async();
                     __syncwarp();
@@ -346,24 +441,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tmem_ld_32x32(t_row + c0, v);  // warp-collective: every lane takes part
                 const int col = tn * BN + c0;
                 if (row < p.M && col < p.N) {
-                    const size_t off = (size_t)row * p.N + col;
-                    if (vec_ok) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            if (col + j < p.N) {
-                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                                if (p.C) {
-                                    const float4 c = *reinterpret_cast<const float4 *>(p.C + off + j);
-                                    o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
-                                }
-                                *reinterpret_cast<float4 *>(p.D + off + j) = o;
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < p.N) p.D[off + j] = p.C ? v[j] + p.C[off + j] : v[j];
-                    }
+                    if (p.out_fmt == 0) store_row_segment<float>(v, p, row, col);
+                    else if (p.out_fmt == 1) store_row_segment<__half>(v, p, row, col);
+                    else store_row_segment<__nv_bfloat16>(v, p, row, col);
                 }
             }
             }

@@ -155,19 +155,30 @@ def sgemm(a, b, c=None, out=None, stream: int | None = None):
     return out
 
 
-def gemm_tc(a, b_colmajor, c=None, out=None, stream: int | None = None):
-    """D[M,N] (FP32) = A[M,K] @ B[K,N] (+ C) with FP16/BF16 inputs.
+def gemm_tc(a, b, c=None, out=None, stream: int | None = None, out_dtype=None, b_row_major: bool = False):
+    """D[M,N] = A[M,K] @ B[K,N] (+ C) with FP16/BF16 inputs and FP32 accumulation.
 
-    ``b_colmajor`` is the column-major [K,N] operand as stored, i.e. a contiguous [N,K] tensor.
+    ``b`` is the column-major [K,N] operand as stored, i.e. a contiguous [N,K] tensor, or with
+    ``b_row_major`` a contiguous [K,N] tensor.  ``out_dtype`` is float32 (default) or the input dtype;
+    ``c`` has the output dtype.
     """
     import torch
 
-    assert a.dtype == b_colmajor.dtype and a.dtype in (torch.float16, torch.bfloat16)
+    assert a.dtype == b.dtype and a.dtype in (torch.float16, torch.bfloat16)
     M, K = a.shape
-    N, K2 = b_colmajor.shape
+    if b_row_major:
+        K2, N = b.shape
+    else:
+        N, K2 = b.shape
     assert K == K2
-    out = torch.empty((M, N), dtype=torch.float32, device=a.device) if out is None else out
+    out_dtype = (out.dtype if out is not None else torch.float32) if out_dtype is None else out_dtype
+    assert out_dtype in (torch.float32, a.dtype), "D is FP32 or the input type"
+    assert c is None or c.dtype == out_dtype
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device) if out is None else out
+    assert out.dtype == out_dtype
     s = _current_stream_ptr() if stream is None else stream
-    fn = native.lib().ko_gemm_f16_f32 if a.dtype == torch.float16 else native.lib().ko_gemm_bf16_f32
-    native.check(fn(M, N, K, _ptr(a), _ptr(b_colmajor), _ptr(c), _ptr(out), s), "ko_gemm_tc")
+    in_fmt = 0 if a.dtype == torch.float16 else 1
+    out_fmt = 0 if out_dtype == torch.float32 else (1 if out_dtype == torch.float16 else 2)
+    native.check(native.lib().ko_gemm_tc(in_fmt, out_fmt, 1 if b_row_major else 0, M, N, K, _ptr(a), _ptr(b), _ptr(c), _ptr(out), s),
+                 "ko_gemm_tc")
     return out

@@ -23,17 +23,26 @@ def _dev16(cuda, bits, kind):
     return cuda.from_numpy(bits.view(np.int16)).cuda().view(cuda.float16 if kind == "f16" else cuda.bfloat16)
 
 
-def _run(cuda, lib, kind, ab, bb, c=None, bn=0, store_mode=0):
+def _run(cuda, lib, kind, ab, bb, c=None, bn=0, store_mode=0, out16=False, b_row_major=False):
+    """ab: [M,K] bits; bb: [N,K] bits (column-major B) or, with b_row_major, [K,N] bits; c: float32 [M,N] or, with
+    out16, bits of the input type.  Returns float32 D, or D's bits with out16."""
     M, K = ab.shape
-    N = bb.shape[0]
+    N = bb.shape[1] if b_row_major else bb.shape[0]
     ad, bd = _dev16(cuda, ab, kind), _dev16(cuda, bb, kind)
-    cd = None if c is None else cuda.from_numpy(c).cuda()
-    dd = cuda.full((M, N), float("nan"), dtype=cuda.float32, device="cuda")
-    rc = lib.ko_gemm_tc_tuned(0 if kind == "f16" else 1, M, N, K, ad.data_ptr(), bd.data_ptr(),
+    if out16:
+        cd = None if c is None else _dev16(cuda, c, kind)
+        dd = _dev16(cuda, np.full((M, N), 0x7e00 if kind == "f16" else 0x7fc0, dtype=np.uint16), kind)   # NaN
+    else:
+        cd = None if c is None else cuda.from_numpy(c).cuda()
+        dd = cuda.full((M, N), float("nan"), dtype=cuda.float32, device="cuda")
+    out_fmt = 0 if not out16 else (1 if kind == "f16" else 2)
+    rc = lib.ko_gemm_tc_tuned(0 if kind == "f16" else 1, out_fmt, 1 if b_row_major else 0, M, N, K, ad.data_ptr(), bd.data_ptr(),
                               None if cd is None else cd.data_ptr(), dd.data_ptr(), bn, store_mode, cuda.cuda.current_stream().cuda_stream)
     assert rc == 0, lib.ko_last_error_string()
     cuda.cuda.synchronize()
     assert lib.ko_poll_device_status() == 0, lib.ko_last_error_string()
+    if out16:
+        return dd.view(cuda.int16).cpu().numpy().view(np.uint16)
     return dd.cpu().numpy()
 
 
@@ -123,3 +132,80 @@ def test_argument_checks(cuda, lib):
     assert lib.ko_gemm_bf16_f32(128, 128, 64, a.data_ptr() + 2, a.data_ptr(), None, d.data_ptr(), s) == 2  # alignment
     assert lib.ko_gemm_bf16_f32(128, 128, 64, None, a.data_ptr(), None, d.data_ptr(), s) == 1
     assert lib.ko_gemm_bf16_f32(0, 128, 64, None, None, None, None, s) == 0
+
+
+# ---------------------------------------------------------------------------------------------------
+# row-major B (the reference driver's layout) and 16-bit D (the reference's ElementC = half)
+# ---------------------------------------------------------------------------------------------------
+# A 16-bit D carries its own rounding: half an ulp per element, 2^-11 relative for FP16 and 2^-9 for BF16, so the
+# 1e-3 bound (stated for FP32 output) holds for FP16 and becomes 2^-9 for BF16.  The sharp check is the other one:
+# the 16-bit result must equal the FP32 result rounded once, bit for bit.
+TOL_OUT16 = {"f16": TOL_FRO, "bf16": 2.0 ** -9}
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (128, 256, 16), (256, 512, 256), (100, 40, 56), (129, 264, 136),
+                                   (1000, 520, 200), (2048, 1024, 512), (131, 4104, 64), (5000, 16, 320)])
+def test_row_major_b_matches_column_major_bits(cuda, lib, oracle, kind, bn, M, N, K):
+    """Same products, same accumulation order: the two B layouts must agree bit for bit."""
+    to_bits, from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 3, 0)), to_bits(oracle.fill_uniform((N, K), 3, 1))
+    d_col = _run(cuda, lib, kind, ab, bb, bn=bn)
+    d_row = _run(cuda, lib, kind, ab, np.ascontiguousarray(bb.T), bn=bn, b_row_major=True)
+    assert np.array_equal(d_col, d_row)
+    err = oracle.rel_frobenius(d_row, oracle.gemm_tn_f64(from_bits(ab), from_bits(bb)))
+    assert err <= TOL_FRO and err <= tight(K)
+
+
+def test_row_major_b_needs_a_16_byte_pitch(cuda, lib):
+    a = cuda.zeros((128, 64), dtype=cuda.bfloat16, device="cuda")
+    b = cuda.zeros((64, 36), dtype=cuda.bfloat16, device="cuda")
+    d = cuda.zeros((128, 36), dtype=cuda.float32, device="cuda")
+    rc = lib.ko_gemm_tc(1, 0, 1, 128, 36, 64, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), cuda.cuda.current_stream().cuda_stream)
+    assert rc == 3 and "multiple of 8" in lib.ko_last_error_string().decode()
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("store_mode", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (256, 512, 256), (100, 40, 56), (129, 264, 136), (1000, 520, 200),
+                                   (2048, 1024, 512), (5000, 16, 320)])
+def test_16_bit_output_is_the_fp32_result_rounded_once(cuda, lib, oracle, kind, store_mode, M, N, K):
+    to_bits, from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 3, 0)), to_bits(oracle.fill_uniform((N, K), 3, 1))
+    d32 = _run(cuda, lib, kind, ab, bb)
+    for bn in (0, 64):
+        d16 = _run(cuda, lib, kind, ab, bb, bn=bn, store_mode=store_mode, out16=True)
+        assert np.array_equal(d16, to_bits(d32 if bn == 0 else _run(cuda, lib, kind, ab, bb, bn=bn)))
+    want = oracle.gemm_tn_f64(from_bits(ab), from_bits(bb))
+    assert oracle.rel_frobenius(from_bits(d16).astype(np.float64), want) <= TOL_OUT16[kind]
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (200, 37, 64), (129, 264, 136), (1000, 520, 200)])
+def test_16_bit_output_with_c_and_odd_pitch(cuda, lib, oracle, kind, M, N, K):
+    """D = round(acc + C) with C in D's type; N = 37 takes the scalar stores."""
+    to_bits, from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 3, 0)), to_bits(oracle.fill_uniform((N, K), 3, 1))
+    cb = to_bits(oracle.fill_uniform((M, N), 3, 2))
+    d16 = _run(cuda, lib, kind, ab, bb, c=cb, out16=True)
+    d32 = _run(cuda, lib, kind, ab, bb, c=from_bits(cb))       # FP32 path: acc + C in FP32
+    assert np.array_equal(d16, to_bits(d32))
+    want = oracle.gemm_tn_f64(from_bits(ab), from_bits(bb), from_bits(cb))
+    assert oracle.rel_frobenius(from_bits(d16).astype(np.float64), want) <= TOL_OUT16[kind]
+
+
+def test_named_16_bit_entry_points_and_row_major_16_bit(cuda, lib, oracle):
+    s = cuda.cuda.current_stream().cuda_stream
+    for kind, fn, out_fmt in (("f16", lib.ko_gemm_f16_f16, 1), ("bf16", lib.ko_gemm_bf16_bf16, 2)):
+        to_bits, from_bits = _bits(oracle, kind)
+        M, N, K = 384, 320, 192
+        ab, bb = to_bits(oracle.fill_uniform((M, K), 5, 0)), to_bits(oracle.fill_uniform((N, K), 5, 1))
+        ad, bd, btd = _dev16(cuda, ab, kind), _dev16(cuda, bb, kind), _dev16(cuda, np.ascontiguousarray(bb.T), kind)
+        d1 = _dev16(cuda, np.zeros((M, N), np.uint16), kind)
+        d2 = _dev16(cuda, np.zeros((M, N), np.uint16), kind)
+        assert fn(M, N, K, ad.data_ptr(), bd.data_ptr(), None, d1.data_ptr(), s) == 0
+        assert lib.ko_gemm_tc(0 if kind == "f16" else 1, out_fmt, 1, M, N, K, ad.data_ptr(), btd.data_ptr(), None, d2.data_ptr(), s) == 0
+        cuda.cuda.synchronize()
+        assert lib.ko_poll_device_status() == 0
+        assert cuda.equal(d1.view(cuda.int16), d2.view(cuda.int16))
+        got = from_bits(d1.view(cuda.int16).cpu().numpy().view(np.uint16)).astype(np.float64)
+        assert oracle.rel_frobenius(got, oracle.gemm_tn_f64(from_bits(ab), from_bits(bb))) <= TOL_OUT16[kind]
