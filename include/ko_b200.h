@@ -114,6 +114,12 @@ int ko_check_max_rowsum_err_f32(const float *got, int64_t rows, int32_t cols, do
  * cols % 4 == 0 and 16-byte aligned pointers, other inputs take a scalar path.
  * ---------------------------------------------------------------------------------------- */
 int ko_softmax_f32(const float *in, float *out, int64_t rows, int32_t cols, void *stream);
+/* FP16 / BF16 in and out (raw uint16 storage), FP32 arithmetic, one rounding on store: the element
+ * type the reference's Exp<half> (common/functors.h:71-77) and numeric_limits<half>
+ * (common/common.h:171-177) provide for and its driver never instantiates.  The 128-bit path needs
+ * cols % 8 == 0 and 16-byte aligned pointers. */
+int ko_softmax_f16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, void *stream);
+int ko_softmax_bf16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * LayerNorm forward over the last dimension, row-major [rows, cols].
@@ -129,6 +135,9 @@ int ko_layernorm_f32(const float *in, float *out, int64_t rows, int32_t cols, fl
 /* BF16 in/out (raw uint16 storage), FP32 statistics */
 int ko_layernorm_bf16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps,
                       const uint16_t *gamma, const uint16_t *beta, int ddof, void *stream);
+/* FP16 in/out (the reference's Rsqrt<half>, common/functors.h:105-111), FP32 statistics */
+int ko_layernorm_f16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps,
+                     const uint16_t *gamma, const uint16_t *beta, int ddof, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * SGEMM: D[M,N] = A[M,K] * B[K,N] (+ C[M,N] when C != NULL), all row-major FP32, FP32 FFMA.

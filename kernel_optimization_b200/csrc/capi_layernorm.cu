@@ -228,6 +228,15 @@ int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int
     return layernorm_dispatch<B>(a, knobs, static_cast<cudaStream_t>(stream));
 }
 
+int ko_layernorm_f16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps,
+                           const uint16_t *gamma, const uint16_t *beta, int ddof, const ko_row_knobs_t *knobs,
+                           void *stream) {
+    using H = __half;
+    const Args<H> a{reinterpret_cast<const H *>(in), reinterpret_cast<H *>(out), rows, cols, eps,
+                    reinterpret_cast<const H *>(gamma), reinterpret_cast<const H *>(beta), ddof};
+    return layernorm_dispatch<H>(a, knobs, static_cast<cudaStream_t>(stream));
+}
+
 int ko_layernorm_f32(const float *in, float *out, int64_t rows, int32_t cols, float eps, const float *gamma,
                      const float *beta, int ddof, void *stream) {
     return ko_layernorm_f32_tuned(in, out, rows, cols, eps, gamma, beta, ddof, nullptr, stream);
@@ -236,6 +245,11 @@ int ko_layernorm_f32(const float *in, float *out, int64_t rows, int32_t cols, fl
 int ko_layernorm_bf16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps, const uint16_t *gamma,
                       const uint16_t *beta, int ddof, void *stream) {
     return ko_layernorm_bf16_tuned(in, out, rows, cols, eps, gamma, beta, ddof, nullptr, stream);
+}
+
+int ko_layernorm_f16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps, const uint16_t *gamma,
+                     const uint16_t *beta, int ddof, void *stream) {
+    return ko_layernorm_f16_tuned(in, out, rows, cols, eps, gamma, beta, ddof, nullptr, stream);
 }
 
 }  // extern "C"

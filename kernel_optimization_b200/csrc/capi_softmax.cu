@@ -2,6 +2,7 @@
 #include "row_launch.h"
 
 #include "../nn_operators/softmax/softmax.h"
+#include "../nn_operators/softmax/softmax_16bit.h"
 
 namespace {
 
@@ -84,9 +85,59 @@ int dispatch_rows(int nvec, int slots, const float *in, float *out, long long ro
 #undef KO_GO
 }
 
+// FP16 / BF16 rows: warp tier up to 2048 columns, block tier up to 32768, stream tier for the rest
+template <typename T>
+int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStream_t s) {
+    KO_REQUIRE(rows >= 0 && cols >= 0, KO_ERR_INVALID_ARG, "softmax: negative shape [%lld, %d]", (long long)rows, cols);
+    if (rows == 0 || cols == 0) return KO_OK;
+    KO_REQUIRE(in != nullptr && out != nullptr, KO_ERR_INVALID_ARG, "softmax: NULL pointer");
+    DeviceInfo info;
+    if (int st = ko::current_device_info(&info)) return st;
+    const bool vec_ok = (cols % 8 == 0) && ko::aligned16(in) && ko::aligned16(out);
+    const int nvec = cols / 8;
+    if (vec_ok && nvec <= 32 * 8) {
+        auto warp = [&](auto kernel, int rows_per_step) -> int {
+            const long long groups = (rows + rows_per_step - 1) / rows_per_step;
+            kernel<<<ko::clamp_grid((groups + 7) / 8, 0), 256, 0, s>>>(in, out, rows, cols);
+            KO_CHECK_LAUNCH("softmax16_warp_kernel");
+            return KO_OK;
+        };
+        if (nvec <= 8) return warp(ko::softmax16_warp_kernel<T, 1, 2, 8>, 8);
+        if (nvec <= 16) return warp(ko::softmax16_warp_kernel<T, 2, 2, 8>, 8);
+        if (nvec <= 32) return warp(ko::softmax16_warp_kernel<T, 2, 2, 16>, 4);
+        if (nvec <= 64) return warp(ko::softmax16_warp_kernel<T, 2, 2, 32>, 2);
+        if (nvec <= 128) return warp(ko::softmax16_warp_kernel<T, 4, 2, 32>, 2);
+        return warp(ko::softmax16_warp_kernel<T, 8, 1, 32>, 1);
+    }
+    if (vec_ok && nvec <= 1024 * 4) {
+        auto block = [&](auto kernel, int threads) -> int {
+            kernel<<<ko::clamp_grid(rows, 0), threads, 0, s>>>(in, out, rows, cols);
+            KO_CHECK_LAUNCH("softmax16_block_kernel");
+            return KO_OK;
+        };
+        if (nvec <= 256 * 2) return block(ko::softmax16_block_kernel<T, 2, 256>, 256);
+        if (nvec <= 256 * 4) return block(ko::softmax16_block_kernel<T, 4, 256>, 256);
+        if (nvec <= 1024 * 2) return block(ko::softmax16_block_kernel<T, 2, 1024>, 1024);
+        return block(ko::softmax16_block_kernel<T, 4, 1024>, 1024);
+    }
+    ko::softmax16_stream_kernel<T><<<ko::clamp_grid(rows, (long long)info.sm_count * 8), 256, 0, s>>>(in, out, rows, cols);
+    KO_CHECK_LAUNCH("softmax16_stream_kernel");
+    return KO_OK;
+}
+
 }  // namespace
 
 extern "C" {
+
+int ko_softmax_f16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, void *stream) {
+    return softmax16_dispatch(reinterpret_cast<const __half *>(in), reinterpret_cast<__half *>(out), rows, cols,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int ko_softmax_bf16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, void *stream) {
+    return softmax16_dispatch(reinterpret_cast<const __nv_bfloat16 *>(in), reinterpret_cast<__nv_bfloat16 *>(out), rows, cols,
+                              static_cast<cudaStream_t>(stream));
+}
 
 int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols, const ko_row_knobs_t *knobs,
                          void *stream) {

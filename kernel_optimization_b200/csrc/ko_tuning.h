@@ -28,6 +28,9 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
                          void *stream);
 int ko_layernorm_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols, float eps, const float *gamma,
                            const float *beta, int ddof, const ko_row_knobs_t *knobs, void *stream);
+int ko_layernorm_f16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps,
+                           const uint16_t *gamma, const uint16_t *beta, int ddof, const ko_row_knobs_t *knobs,
+                           void *stream);
 int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int32_t cols, float eps,
                             const uint16_t *gamma, const uint16_t *beta, int ddof, const ko_row_knobs_t *knobs,
                             void *stream);

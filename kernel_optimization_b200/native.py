@@ -49,8 +49,11 @@ PROTOTYPES = {
     "ko_check_rel_frobenius_f32": (_int, [_vp, _vp, _i64, _f64p]),
     "ko_check_max_rowsum_err_f32": (_int, [_vp, _i64, _i32, _f64p]),
     "ko_softmax_f32": (_int, [_vp, _vp, _i64, _i32, _vp]),
+    "ko_softmax_f16": (_int, [_vp, _vp, _i64, _i32, _vp]),
+    "ko_softmax_bf16": (_int, [_vp, _vp, _i64, _i32, _vp]),
     "ko_layernorm_f32": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _vp]),
     "ko_layernorm_bf16": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _vp]),
+    "ko_layernorm_f16": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _vp]),
     "ko_sgemm_f32": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ko_sgemm_f32_no_alloc": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),
     "ko_gemm_f16_f32": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
@@ -74,6 +77,7 @@ TUNING_PROTOTYPES = {
     "ko_softmax_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _knobs_p, _vp]),
     "ko_layernorm_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),
     "ko_layernorm_bf16_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),
+    "ko_layernorm_f16_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),
     "ko_sgemm_f32_tuned": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _int, _vp]),
     "ko_gemm_tc_tuned": (_int, [_int, _int, _int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _int, _vp]),
 }

@@ -87,6 +87,41 @@ struct RowIo<__nv_bfloat16> {
     __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
 };
 
+// FP16 rows (the reference's Rsqrt<half> / MultiplyAdd<half> element type, common/functors.h:105-111, :280-290):
+// widened to FP32 on load, statistics and normalisation in FP32, rounded once on store
+template <>
+struct RowIo<__half> {
+    static constexpr int kPerVec = 8;
+    using Raw = uint4;
+    __device__ __forceinline__ static float2 widen2(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2 *>(&w)); }
+    __device__ __forceinline__ static uint32_t narrow2(float lo, float hi) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+    __device__ __forceinline__ static void unpack(const Raw &r, float (&f)[8]) {
+        const float2 a = widen2(r.x), b = widen2(r.y), c = widen2(r.z), d = widen2(r.w);
+        f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+    }
+    __device__ __forceinline__ static Raw pack(const float (&f)[8]) {
+        return make_uint4(narrow2(f[0], f[1]), narrow2(f[2], f[3]), narrow2(f[4], f[5]), narrow2(f[6], f[7]));
+    }
+    __device__ __forceinline__ static void unpack_pairs(const Raw &r, f32x2 *p) {
+        const float2 a = widen2(r.x), b = widen2(r.y), c = widen2(r.z), d = widen2(r.w);
+        p[0] = pair_of(a.x, a.y);
+        p[1] = pair_of(b.x, b.y);
+        p[2] = pair_of(c.x, c.y);
+        p[3] = pair_of(d.x, d.y);
+    }
+    __device__ __forceinline__ static Raw pack_pairs(const f32x2 *p) {
+        float lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pair_split(p[i], lo[i], hi[i]);
+        return make_uint4(narrow2(lo[0], hi[0]), narrow2(lo[1], hi[1]), narrow2(lo[2], hi[2]), narrow2(lo[3], hi[3]));
+    }
+    __device__ __forceinline__ static float to_float(__half v) { return __half2float(v); }
+    __device__ __forceinline__ static __half from_float(float v) { return __float2half_rn(v); }
+};
+
 // exact (count, mean, M2) of the valid_vecs * kPerVec values a thread holds as raw 16-byte vectors:
 // mean first, then the squared deviations from it (both passes run over registers)
 template <typename T, int kVecs>

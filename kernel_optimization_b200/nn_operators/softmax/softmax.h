@@ -16,8 +16,10 @@
 //   stream tier one thread block per row, three passes over global memory with scalar accesses; any
 //               column count and any alignment (correctness path).
 //
-// All tiers compute exp(x - rowmax) / sum in FP32 as 2^((x - rowmax) * log2 e) on the special-function
-// unit; a row's results do not depend on the tier's launch geometry.  (The reference's Subtract
+// All tiers compute exp(x - rowmax) / sum in FP32 as 2^(fma(x, log2 e, -fl(rowmax * log2 e))) on the
+// special-function unit; a row's results do not depend on the tier's launch geometry.  The rounding of
+// the shift is common to the whole row and cancels in the quotient; it is half an ulp of rowmax * log2 e,
+// negligible against the exponent range for |x| < 1e9 (the stated input range).  (The reference's Subtract
 // functor adds, common/functors.h:168, so it evaluates exp(x + rowmax); the two agree mathematically
 // but the reference overflows once 2*rowmax > 88.7.)
 //

@@ -116,28 +116,32 @@ def fill_causal_mask_(a: np.ndarray, row_offset: int = 0, block: int = 512, valu
 
 # ------------------------------------------------------------------ operators (torch tensors on the GPU)
 def softmax(x, out=None, stream: int | None = None):
-    """Row softmax over the last dimension of a 2-D FP32 CUDA tensor."""
+    """Row softmax over the last dimension of a 2-D FP32, FP16 or BF16 CUDA tensor (FP32 arithmetic)."""
     import torch
 
-    assert x.dtype == torch.float32 and x.dim() == 2
+    assert x.dim() == 2 and x.dtype in (torch.float32, torch.float16, torch.bfloat16)
     out = torch.empty_like(x) if out is None else out
+    assert out.dtype == x.dtype
     s = _current_stream_ptr() if stream is None else stream
     rows, cols = x.shape
-    native.check(native.lib().ko_softmax_f32(_ptr(x), _ptr(out), rows, cols, s), "ko_softmax_f32")
+    lib = native.lib()
+    fn = {torch.float32: lib.ko_softmax_f32, torch.float16: lib.ko_softmax_f16, torch.bfloat16: lib.ko_softmax_bf16}[x.dtype]
+    native.check(fn(_ptr(x), _ptr(out), rows, cols, s), "ko_softmax")
     return out
 
 
 def layernorm(x, eps: float, gamma=None, beta=None, ddof: int = 0, out=None, stream: int | None = None):
-    """LayerNorm forward over the last dimension of a 2-D FP32 or BF16 CUDA tensor."""
+    """LayerNorm forward over the last dimension of a 2-D FP32, FP16 or BF16 CUDA tensor (FP32 statistics)."""
     import torch
 
-    assert x.dim() == 2 and x.dtype in (torch.float32, torch.bfloat16)
+    assert x.dim() == 2 and x.dtype in (torch.float32, torch.float16, torch.bfloat16)
     for p in (gamma, beta):
         assert p is None or (p.dtype == x.dtype and p.numel() == x.shape[1])
     out = torch.empty_like(x) if out is None else out
     s = _current_stream_ptr() if stream is None else stream
     rows, cols = x.shape
-    fn = native.lib().ko_layernorm_f32 if x.dtype == torch.float32 else native.lib().ko_layernorm_bf16
+    lib = native.lib()
+    fn = {torch.float32: lib.ko_layernorm_f32, torch.float16: lib.ko_layernorm_f16, torch.bfloat16: lib.ko_layernorm_bf16}[x.dtype]
     native.check(fn(_ptr(x), _ptr(out), rows, cols, eps, _ptr(gamma), _ptr(beta), ddof, s), "ko_layernorm")
     return out
 
