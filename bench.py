@@ -170,6 +170,9 @@ def run_reference_arm(args):
 # --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
+E2E_CHUNKS = 8
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -271,20 +274,17 @@ def run_gpu_arm(args):
     t_ln_in.host_ref(np.float32)[:] = xl_host.reshape(-1)
 
     def e2e_step(_i):
-        s = stream()
-        t_sm_in.host_to_device_async(s)
-        t_ln_in.host_to_device_async(s)
-        native.check(lib.ko_softmax_f32(t_sm_in.device_ptr, t_sm_out.device_ptr, SOFTMAX_ROWS, SOFTMAX_COLS, s), "softmax")
-        native.check(lib.ko_layernorm_f32(t_ln_in.device_ptr, t_ln_out.device_ptr, LN_ROWS, LN_COLS, LN_EPS,
-                                          gamma.data_ptr(), beta.data_ptr(), 0, s), "layernorm")
-        t_sm_out.device_to_host_async(s)
-        t_ln_out.device_to_host_async(s)
+        # the public host-tensor calls: rows flow through copy-in / kernel / copy-out streams in chunks
+        ko.softmax_host(t_sm_in, t_sm_out, SOFTMAX_ROWS, SOFTMAX_COLS, E2E_CHUNKS)
+        ko.layernorm_host(t_ln_in, t_ln_out, LN_ROWS, LN_COLS, LN_EPS, gamma, beta, 0, E2E_CHUNKS)
 
     e2e_steps = max(3, min(args.steps, 20))
     ms_e2e = timed(e2e_step, e2e_steps, 3)
     h2d = SOFTMAX_BYTES // 2 + LN_ROWS * LN_COLS * 4
     e2e = {"value": STEP_BYTES * world / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": h2d, "ms_per_step": ms_e2e, "steps": e2e_steps}
+           "d2h_bytes_per_step": h2d, "ms_per_step": ms_e2e, "steps": e2e_steps,
+           "path": f"ko_softmax_f32_host + ko_layernorm_f32_host, {E2E_CHUNKS} chunks each: pinned host -> device -> kernel -> pinned host, "
+                   "copies of neighbouring chunks overlap (PCIe is full duplex); every step ends with all results on the host"}
     if rank == 0:
         from oracle import ko_oracle as oracle
 
@@ -592,6 +592,118 @@ def run_case(args):
           "unit": unit, "steps": args.steps, "note": "same buffers every launch (L2-warm for small cases)"})
 
 
+# --------------------------------------------------------------------------------------------------
+# --sweep: README-style rows (percent of the copy-bandwidth peak / of the vendor library) in one command
+# --------------------------------------------------------------------------------------------------
+SWEEP_ROW_SHAPES = {
+    # (rows, cols): the BASELINE configs, the shape the reference's drivers were written for (49152 x 1024,
+    # nn_operators/softmax/main.cu:78-79) and long rows for the block and cluster tiers
+    "softmax": {"f32": [(196608, 128), (49152, 1024), (196608, 512), (8192, 8192), (512, 65536)],
+                "f16": [(196608, 128), (49152, 1024)], "bf16": [(196608, 512), (49152, 1024)]},
+    "layernorm": {"f32": [(16384, 768), (49152, 1024), (8192, 4096), (512, 65536)],
+                  "f16": [(16384, 768), (32768, 4096)], "bf16": [(16384, 768), (32768, 4096)]},
+}
+SWEEP_SGEMM = [512, 1024, 2048, 4096]
+SWEEP_TC = [("bf16", "f32", False, (4096, 4096, 4096)), ("f16", "f32", False, (4096, 4096, 4096)),
+            ("bf16", "f32", False, (16384, 3072, 768)), ("bf16", "f32", False, (8192, 8192, 8192)),
+            ("bf16", "f32", True, (4096, 4096, 4096)), ("bf16", "bf16", False, (4096, 4096, 4096)),
+            ("f16", "f16", False, (4096, 4096, 4096)), ("bf16", "bf16", True, (16384, 3072, 768))]
+
+
+def run_sweep(args):
+    """Every operator over a list of shapes next to the vendor library's kernel for the same job
+    (torch.softmax / layer_norm / matmul), one JSON line with all rows and a table on stderr."""
+    import torch
+
+    from kernel_optimization_b200 import native
+
+    lib = native.lib()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    s = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    torch.backends.cuda.matmul.allow_tf32 = False
+    hbm_peak, tc_peak, peak_kind = measured_peaks()
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+    iters = max(5, min(args.steps, 30))
+
+    def timed(fn, nsets):
+        for i in range(3):
+            fn(i % nsets)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i % nsets)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3  # us
+
+    rows_out = []
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    for op, by_type in SWEEP_ROW_SHAPES.items():
+        for kind, shapes in by_type.items():
+            for rows, cols in shapes:
+                esz = 4 if kind == "f32" else 2
+                nbytes = 2.0 * rows * cols * esz
+                nsets = max(2, min(8, int(300e6 // nbytes) + 1))  # more distinct bytes than the 126 MB L2
+                xs = [(torch.randn((rows, cols), device=dev, generator=gen) * 2).to(tdt[kind]) for _ in range(nsets)]
+                ys = [torch.empty_like(xs[0]) for _ in range(nsets)]
+                if op == "softmax":
+                    fn = {"f32": lib.ko_softmax_f32, "f16": lib.ko_softmax_f16, "bf16": lib.ko_softmax_bf16}[kind]
+                    ours = lambda i: native.check(fn(xs[i].data_ptr(), ys[i].data_ptr(), rows, cols, s()), "softmax")  # noqa: E731
+                    theirs = lambda i: torch.softmax(xs[i], dim=1, out=ys[i])  # noqa: E731
+                else:
+                    g = (torch.rand(cols, device=dev, generator=gen) + 0.5).to(tdt[kind])
+                    b = (torch.randn(cols, device=dev, generator=gen) * 0.1).to(tdt[kind])
+                    fn = {"f32": lib.ko_layernorm_f32, "f16": lib.ko_layernorm_f16, "bf16": lib.ko_layernorm_bf16}[kind]
+                    ours = lambda i: native.check(fn(xs[i].data_ptr(), ys[i].data_ptr(), rows, cols, 1e-5, g.data_ptr(), b.data_ptr(), 0, s()), "layernorm")  # noqa: E731
+                    theirs = lambda i: torch.nn.functional.layer_norm(xs[i], (cols,), g, b, 1e-5)  # noqa: E731
+                us_o, us_t = timed(ours, nsets), timed(theirs, nsets)
+                gbs = nbytes / us_o / 1e3
+                rows_out.append({"op": op, "dtype": kind, "shape": [rows, cols], "us": us_o, "gbs": gbs, "of_hbm_peak": gbs / hbm_peak,
+                                 "library_us": us_t, "vs_library": us_t / us_o})
+                del xs, ys
+    for n in SWEEP_SGEMM:
+        nsets = 8 if n <= 1024 else 2
+        As = [torch.rand((n, n), device=dev, generator=gen) * 2 - 1 for _ in range(nsets)]
+        Bs = [torch.rand((n, n), device=dev, generator=gen) * 2 - 1 for _ in range(nsets)]
+        Ds = [torch.empty((n, n), device=dev) for _ in range(nsets)]
+        us_o = timed(lambda i: native.check(lib.ko_sgemm_f32(n, n, n, As[i].data_ptr(), Bs[i].data_ptr(), None, Ds[i].data_ptr(), s()), "sgemm"), nsets)
+        us_t = timed(lambda i: torch.matmul(As[i], Bs[i], out=Ds[i]), nsets)
+        rows_out.append({"op": "sgemm", "dtype": "f32", "shape": [n, n, n], "us": us_o, "tflops": 2.0 * n ** 3 / us_o / 1e6,
+                         "library_us": us_t, "vs_library": us_t / us_o})
+        del As, Bs, Ds
+    for kin, kout, b_row_major, (M, N, K) in SWEEP_TC:
+        nsets = 3
+        As = [(torch.rand((M, K), device=dev, generator=gen) * 2 - 1).to(tdt[kin]) for _ in range(nsets)]
+        Bs = [(torch.rand((K, N) if b_row_major else (N, K), device=dev, generator=gen) * 2 - 1).to(tdt[kin]) for _ in range(nsets)]
+        Ds = [torch.empty((M, N), device=dev, dtype=tdt[kout]) for _ in range(nsets)]
+        fi, fo = (0 if kin == "f16" else 1), {"f32": 0, "f16": 1, "bf16": 2}[kout]
+        us_o = timed(lambda i: native.check(lib.ko_gemm_tc(fi, fo, 1 if b_row_major else 0, M, N, K, As[i].data_ptr(), Bs[i].data_ptr(), None,
+                                                           Ds[i].data_ptr(), s()), "gemm_tc"), nsets)
+        if kout == "f32":
+            theirs = lambda i: torch.mm(As[i], Bs[i] if b_row_major else Bs[i].t(), out_dtype=torch.float32)  # noqa: E731
+        else:
+            theirs = lambda i: torch.mm(As[i], Bs[i] if b_row_major else Bs[i].t(), out=Ds[i])  # noqa: E731
+        us_t = timed(theirs, nsets)
+        tf = 2.0 * M * N * K / us_o / 1e6
+        rows_out.append({"op": "gemm_tc", "dtype": f"{kin}->{kout}", "b": "row-major" if b_row_major else "column-major", "shape": [M, N, K],
+                         "us": us_o, "tflops": tf, "of_bf16_peak": tf / tc_peak, "library_us": us_t, "vs_library": us_t / us_o})
+        del As, Bs, Ds
+    native.check(lib.ko_poll_device_status(), "ko_poll_device_status")
+    print(f"{'op':10s} {'dtype':10s} {'shape':22s} {'us':>9s} {'rate':>14s} {'of peak':>8s} {'library us':>11s} {'vs library':>10s}", file=sys.stderr)
+    for r in rows_out:
+        rate = f"{r['gbs']:.0f} GB/s" if "gbs" in r else f"{r['tflops']:.1f} TFLOP/s"
+        frac = r.get("of_hbm_peak", r.get("of_bf16_peak"))
+        tag = r["dtype"] + (" rowB" if r.get("b") == "row-major" else "")
+        print(f"{r['op']:10s} {tag:10s} {'x'.join(map(str, r['shape'])):22s} {r['us']:9.1f} {rate:>14s} "
+              f"{'' if frac is None else format(frac, '.1%'):>8s} {r['library_us']:11.1f} {r['vs_library']:10.2f}", file=sys.stderr)
+    emit({"sweep": rows_out, "peaks": {"hbm_gbs": hbm_peak, "bf16_tflops": tc_peak, "source": peak_kind}, "launches_per_row": iters,
+          "library": "torch.softmax / torch.nn.functional.layer_norm / torch.matmul (cuBLAS, TF32 off)",
+          "l2": "row operators rotate over buffer sets larger than the 126 MB L2"})
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -604,6 +716,8 @@ def main():
                     help="buffer sets to rotate over (0 = default 4/8); 1 keeps a profiler capture small")
     ap.add_argument("--workload", choices=["bert_base", "scaled"], default="bert_base",
                     help="bert_base: configs 1+2 per GPU, weak scaling (default); scaled: config 5 totals, strong scaling")
+    ap.add_argument("--sweep", action="store_true",
+                    help="every operator over a list of shapes next to the vendor library (one JSON line, table on stderr)")
     ap.add_argument("--case", choices=sorted(CASES), default=None,
                     help="run a single operator case a few times instead of the benchmark (for profiler captures)")
     args = ap.parse_args()
@@ -632,6 +746,9 @@ def emit(line: dict) -> None:
 def _dispatch(args):
     if args.case:
         run_case(args)
+        return
+    if args.sweep:
+        run_sweep(args)
         return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

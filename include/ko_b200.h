@@ -140,6 +140,21 @@ int ko_layernorm_f16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t co
                      const uint16_t *gamma, const uint16_t *beta, int ddof, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * The same operators for a caller whose rows live in HOST memory: `in` is copied to the device,
+ * the operator runs and `out` is copied back, cut into `chunks` row ranges (0 = 8, at most 64) that
+ * flow through three streams, so that the copy in, the kernel and the copy out of neighbouring
+ * chunks overlap and a call costs about one direction of the PCIe link.  Ordered like any other
+ * work on `stream` (it starts after what `stream` holds and `stream` continues after the last
+ * copy).  The tensors' first rows*cols elements are used; both must live on the current device;
+ * gamma and beta are DEVICE pointers.  No counterpart in the reference, whose drivers copy whole
+ * tensors before and after the launch (nn_operators/softmax/main.cu:38, :55, :62).
+ * ---------------------------------------------------------------------------------------- */
+int ko_softmax_f32_host(ko_tensor_t *in, ko_tensor_t *out, int64_t rows, int32_t cols, int chunks,
+                        void *stream);
+int ko_layernorm_f32_host(ko_tensor_t *in, ko_tensor_t *out, int64_t rows, int32_t cols, float eps,
+                          const float *gamma, const float *beta, int ddof, int chunks, void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * SGEMM: D[M,N] = A[M,K] * B[K,N] (+ C[M,N] when C != NULL), all row-major FP32, FP32 FFMA.
  * Stands in for gemm<GemmKernelSimt<float,float,float,GemmShape<64,64,8>,GemmShape<32,32,8>,
  * 4,4,4>><<<grid, 128, smem, stream>>>(GemmCoord, A, B, C, D): nn_operators/gemm/gemm.h:11-21,

@@ -14,8 +14,10 @@ from .ops import (  # noqa: F401
     fill_uniform,
     gemm_tc,
     layernorm,
+    layernorm_host,
     sgemm,
     softmax,
+    softmax_host,
 )
 
 __version__ = "0.1.0"

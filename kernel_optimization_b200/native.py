@@ -54,6 +54,8 @@ PROTOTYPES = {
     "ko_layernorm_f32": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _vp]),
     "ko_layernorm_bf16": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _vp]),
     "ko_layernorm_f16": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _vp]),
+    "ko_softmax_f32_host": (_int, [_vp, _vp, _i64, _i32, _int, _vp]),
+    "ko_layernorm_f32_host": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _int, _vp]),
     "ko_sgemm_f32": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ko_sgemm_f32_no_alloc": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),
     "ko_gemm_f16_f32": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),

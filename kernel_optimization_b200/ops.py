@@ -146,6 +146,21 @@ def layernorm(x, eps: float, gamma=None, beta=None, ddof: int = 0, out=None, str
     return out
 
 
+def softmax_host(t_in: Tensor, t_out: Tensor, rows: int, cols: int, chunks: int = 0, stream: int | None = None) -> None:
+    """FP32 row softmax of the HOST contents of ``t_in`` into the host buffer of ``t_out``: copy in, kernel and
+    copy out are pipelined over ``chunks`` row ranges (0 = 8).  Stream-ordered like a kernel launch."""
+    s = _current_stream_ptr() if stream is None else stream
+    native.check(native.lib().ko_softmax_f32_host(t_in._h, t_out._h, rows, cols, chunks, s), "ko_softmax_f32_host")
+
+
+def layernorm_host(t_in: Tensor, t_out: Tensor, rows: int, cols: int, eps: float, gamma=None, beta=None, ddof: int = 0,
+                   chunks: int = 0, stream: int | None = None) -> None:
+    """FP32 LayerNorm of the HOST contents of ``t_in`` into the host buffer of ``t_out`` (gamma / beta: CUDA tensors)."""
+    s = _current_stream_ptr() if stream is None else stream
+    native.check(native.lib().ko_layernorm_f32_host(t_in._h, t_out._h, rows, cols, eps, _ptr(gamma), _ptr(beta), ddof, chunks, s),
+                 "ko_layernorm_f32_host")
+
+
 def sgemm(a, b, c=None, out=None, stream: int | None = None):
     """D = A @ B (+ C); row-major FP32 CUDA tensors."""
     import torch

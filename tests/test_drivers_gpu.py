@@ -1,6 +1,8 @@
 """GPU: the stand-alone C++ drivers (kernel_optimization_b200/nn_operators/*/main.cu, built by CMake into
 kernel_optimization_b200/bin/) run, time their operator and pass their built-in checks."""
 import json
+
+import numpy as np
 import os
 import subprocess
 
@@ -37,3 +39,28 @@ def test_gemm_driver():
     assert _run("gemm_driver", "--iters", 5)["tflops"] > 5
     _run("gemm_driver", "--bf16", "--m", 1024, "--n", 1024, "--k", 512, "--iters", 3)
     _run("gemm_driver", "--f16", "--m", 1000, "--n", 520, "--k", 200, "--iters", 3)
+
+
+@pytest.mark.parametrize("chunks", [0, 1, 3, 64])
+def test_host_tensor_pipeline_matches_the_device_call(cuda, lib, ko, oracle, chunks):
+    """ko_softmax_f32_host / ko_layernorm_f32_host: chunked copy-in / kernel / copy-out over three streams gives the
+    bits of the plain device call (rows are independent), for any chunk count, also more chunks than rows."""
+    for rows, cols in ((1000, 128), (37, 768), (5, 1024)):
+        x = oracle.fill_normal((rows, cols), 9, 0, 0.0, 2.0)
+        g, b = oracle.fill_uniform((cols,), 9, 1, 0.5, 1.5), oracle.fill_normal((cols,), 9, 2, 0.0, 0.1)
+        gd, bd = cuda.from_numpy(g).cuda(), cuda.from_numpy(b).cuda()
+        t_in, t_out = ko.Tensor(x.nbytes), ko.Tensor(x.nbytes)
+        t_in.host_ref(np.float32)[:] = x.reshape(-1)
+        xd = cuda.from_numpy(x).cuda()
+        for op in ("softmax", "layernorm"):
+            t_out.host_ref(np.float32)[:] = np.nan
+            if op == "softmax":
+                ko.softmax_host(t_in, t_out, rows, cols, chunks)
+                want = ko.softmax(xd).cpu().numpy()
+            else:
+                ko.layernorm_host(t_in, t_out, rows, cols, 1e-5, gd, bd, 0, chunks)
+                want = ko.layernorm(xd, 1e-5, gd, bd).cpu().numpy()
+            cuda.cuda.current_stream().synchronize()   # the call is ordered on the current stream
+            assert np.array_equal(t_out.host_ref(np.float32).reshape(rows, cols), want)
+    bad = ko.Tensor(16)
+    assert lib.ko_softmax_f32_host(bad._h, bad._h, 100, 100, 0, None) == 3   # larger than the tensors
