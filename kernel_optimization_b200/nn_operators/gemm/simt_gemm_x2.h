@@ -74,6 +74,13 @@ __device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src, bool v
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, bool valid) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
 }
+// unconditional forms for tiles that lie inside the matrices
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -144,10 +151,42 @@ __global__ void __launch_bounds__(32 * kWarpsM * kWarpsN * kGroups) sgemm_x2_ker
 
     const uint32_t smem_base = smem_u32(smem);
     int m_base = 0, n_base = 0;
+    bool inner_mn = false;  // the tile lies inside M and N: K-tiles inside K need no bounds checks
     auto issue_tile = [&](int kt, int stage) {
         const int k0 = kt * BK;
         const uint32_t as = smem_base + (uint32_t)stage * kStageFloats * 4u;
         const uint32_t bs = as + BK * kStrideA * 4u;
+        if (inner_mn && k0 + BK <= p.K) {
+            // same element-to-thread mapping as below, addresses by pointer steps, no predicates
+            constexpr int kRowsPerCopy = GT / 8, kCopiesPerHalf = BM / kRowsPerCopy;
+            const int mt = tid >> 3, kl = tid & 7;
+            const float *a_src = p.A + (size_t)(m_base + mt) * p.K + (k0 + kl);
+            const size_t a_step = (size_t)kRowsPerCopy * p.K;
+            const uint32_t a_dst = as + (uint32_t)(kl * kStrideA + mt) * 4u;
+#pragma unroll
+            for (int i = 0; i < kCopiesPerHalf; ++i) {
+                cp_async_4(a_dst + (uint32_t)(i * kRowsPerCopy) * 4u, a_src + i * a_step);
+                cp_async_4(a_dst + (uint32_t)(8 * kStrideA + i * kRowsPerCopy) * 4u, a_src + i * a_step + 8);
+            }
+            if (kVecB) {
+                constexpr int kVecsPerRow = BN / 4, kRowsPerStep = GT / kVecsPerRow;
+                const int kb = tid / kVecsPerRow, nb = (tid % kVecsPerRow) * 4;
+                const float *b_src = p.B + (size_t)(k0 + kb) * p.N + (n_base + nb);
+                const size_t b_step = (size_t)kRowsPerStep * p.N;
+                const uint32_t b_dst = bs + (uint32_t)(kb * BN + nb) * 4u;
+#pragma unroll
+                for (int i = 0; i < BK / kRowsPerStep; ++i) cp_async_16(b_dst + (uint32_t)(i * kRowsPerStep * BN) * 4u, b_src + i * b_step);
+                return;
+            }
+            // B by 4-byte copies: fall through to the checked loop for B only
+#pragma unroll
+            for (int i = 0; i < (BK * BN) / GT; ++i) {
+                const int e = tid + i * GT;
+                const int k = e / BN, n = e % BN;
+                cp_async_4(bs + (uint32_t)(k * BN + n) * 4u, p.B + (size_t)(k0 + k) * p.N + (n_base + n));
+            }
+            return;
+        }
         // A: a warp instruction covers 4 rows x 8 consecutive k (4 full 32-byte sectors)
 #pragma unroll
         for (int i = 0; i < (BM * BK) / GT; ++i) {
@@ -192,6 +231,7 @@ __global__ void __launch_bounds__(32 * kWarpsM * kWarpsN * kGroups) sgemm_x2_ker
     const bool whole_tile = seg_ktiles == ktiles_total;
     m_base = (tile / tiles_n) * BM;
     n_base = (tile % tiles_n) * BN;
+    inner_mn = m_base + BM <= p.M && n_base + BN <= p.N;
     // this group's contiguous part of the segment
     const int kt_first = kt_begin + seg_ktiles * group / kGroups;
     const int ktiles = kt_begin + seg_ktiles * (group + 1) / kGroups - kt_first;
