@@ -227,6 +227,15 @@ __device__ __forceinline__ Welford warp_allreduce_welford(Welford w) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// programmatic dependent launch: a kernel launched with the stream-serialization attribute may have
+// its blocks placed on SMs while the previous kernel of the stream is still draining; it must not
+// touch global memory before grid_dependency_wait() (which returns once that kernel has completed
+// and its writes are visible).  Both are no-ops in a kernel launched the ordinary way.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
 // fast scalar math for the memory-bound row kernels
 // ---------------------------------------------------------------------------------------------
 // 2^x on the special-function unit (relative error <= 2^-22; -inf and large negative x give +0)

@@ -69,9 +69,7 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &md, 
     if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), Cfg::kSmemBytes)) return st;
     const long long tiles = (long long)((p.M + ko::tc::kBM - 1) / ko::tc::kBM) * ((p.N + BN - 1) / BN);
     const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
-    kernel<<<grid, ko::tc::kThreads, Cfg::kSmemBytes, s>>>(ma, mb, md, p);
-    KO_CHECK_LAUNCH("gemm_tcgen05_kernel");
-    return KO_OK;
+    return ko::launch_overlapped(kernel, grid, (unsigned)ko::tc::kThreads, (size_t)Cfg::kSmemBytes, s, ma, mb, md, p);
 }
 
 // [M, N] row-major output, boxes of 32 rows x 32 columns: FP32 rows of 128 bytes with the 128-byte swizzle,

@@ -23,9 +23,8 @@ int launch_warp(const Args<T> &a, const ko_row_knobs_t &k, cudaStream_t s) {
     const int block = (k.block > 0 && k.block <= 256) ? k.block : 128;
     const long long groups = (a.rows + kRows - 1) / kRows;
     const unsigned grid = ko::clamp_grid((groups + block / 32 - 1) / (block / 32), k.grid_cap);
-    ko::layernorm_warp_kernel<T, kVecs, kRows><<<grid, block, 0, s>>>(a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
-    KO_CHECK_LAUNCH("layernorm_warp_kernel");
-    return KO_OK;
+    return ko::launch_overlapped(ko::layernorm_warp_kernel<T, kVecs, kRows>, grid, (unsigned)block, 0, s, a.in, a.out,
+                                 (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
 }
 
 template <typename T, int kVecs, int kRows>
@@ -46,10 +45,8 @@ int launch_staged(const Args<T> &a, const ko_row_knobs_t &k, const DeviceInfo &i
 
 template <typename T, int kVecs, int kThreads>
 int launch_block(const Args<T> &a, long long grid_cap, cudaStream_t s) {
-    ko::layernorm_block_kernel<T, kVecs, kThreads><<<ko::clamp_grid(a.rows, grid_cap), kThreads, 0, s>>>(
-        a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
-    KO_CHECK_LAUNCH("layernorm_block_kernel");
-    return KO_OK;
+    return ko::launch_overlapped(ko::layernorm_block_kernel<T, kVecs, kThreads>, ko::clamp_grid(a.rows, grid_cap), kThreads, 0, s,
+                                 a.in, a.out, (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
 }
 
 template <typename T, int kThreads>
@@ -65,11 +62,10 @@ int launch_resident(const Args<T> &a, long long grid_cap, int sm_count, cudaStre
     const long long cap = grid_cap > 0 ? grid_cap : (long long)sm_count * (kThreads <= 256 ? 8 : (kThreads <= 512 ? 4 : 2));
     const unsigned grid = ko::clamp_grid(a.rows, cap);
     if (a.gamma || a.beta)
-        ko::layernorm_resident_kernel<T, kVecs, kThreads, true><<<grid, kThreads, 0, s>>>(a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
-    else
-        ko::layernorm_resident_kernel<T, kVecs, kThreads, false><<<grid, kThreads, 0, s>>>(a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
-    KO_CHECK_LAUNCH("layernorm_resident_kernel");
-    return KO_OK;
+        return ko::launch_overlapped(ko::layernorm_resident_kernel<T, kVecs, kThreads, true>, grid, kThreads, 0, s, a.in, a.out,
+                                     (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+    return ko::launch_overlapped(ko::layernorm_resident_kernel<T, kVecs, kThreads, false>, grid, kThreads, 0, s, a.in, a.out,
+                                 (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
 }
 
 template <typename T, int kThreads>

@@ -124,13 +124,10 @@ int launch_x2_shape(int M, int N, int K, const float *A, const float *B, const f
     constexpr int smem_bytes = S::smem_bytes(kGroups);
     auto go = [&](auto kernel) -> int {
         if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), smem_bytes)) return st;
-        kernel<<<(unsigned)ctas, S::kGroupThreads * kGroups, smem_bytes, s>>>(p);
-        return KO_OK;
+        return ko::launch_overlapped(kernel, (unsigned)ctas, (unsigned)(S::kGroupThreads * kGroups), (size_t)smem_bytes, s, p);
     };
     const int st = vec_b ? go(x2::sgemm_x2_kernel<true, kWarpsM, kWarpsN, kGroups>) : go(x2::sgemm_x2_kernel<false, kWarpsM, kWarpsN, kGroups>);
-    if (st) return st;
-    KO_CHECK_LAUNCH("sgemm_x2_kernel");
-    return KO_OK;
+    return st;
 }
 
 // shape: 0 = choose; 1 = 128 x 128 tiles, 128-thread blocks (two per SM); 2 = 128 x 128 tiles, two groups of

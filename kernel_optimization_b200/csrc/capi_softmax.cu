@@ -14,9 +14,7 @@ int launch_warp(const float *in, float *out, long long rows, int cols, const ko_
     const int block = (k.block > 0 && k.block <= 256) ? k.block : 256;
     const long long groups = (rows + kRowsPerStep - 1) / kRowsPerStep;
     const unsigned grid = ko::clamp_grid((groups + block / 32 - 1) / (block / 32), k.grid_cap);
-    ko::softmax_warp_kernel<kVecs, kSlots, G><<<grid, block, 0, s>>>(in, out, rows, cols);
-    KO_CHECK_LAUNCH("softmax_warp_kernel");
-    return KO_OK;
+    return ko::launch_overlapped(ko::softmax_warp_kernel<kVecs, kSlots, G>, grid, (unsigned)block, 0, s, in, out, rows, cols);
 }
 
 template <int kVecs, int kSlots, int G>
@@ -37,9 +35,8 @@ int launch_staged(const float *in, float *out, long long rows, int cols, const k
 
 template <int kVecs, int kThreads>
 int launch_block(const float *in, float *out, long long rows, int cols, long long grid_cap, cudaStream_t s) {
-    ko::softmax_block_kernel<kVecs, kThreads><<<ko::clamp_grid(rows, grid_cap), kThreads, 0, s>>>(in, out, rows, cols);
-    KO_CHECK_LAUNCH("softmax_block_kernel");
-    return KO_OK;
+    return ko::launch_overlapped(ko::softmax_block_kernel<kVecs, kThreads>, ko::clamp_grid(rows, grid_cap), kThreads, 0, s, in, out,
+                                 rows, cols);
 }
 
 // one row per cluster of `c` blocks of 1024 threads, up to 8 vectors per thread
@@ -98,9 +95,7 @@ int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStre
     if (vec_ok && nvec <= 32 * 8) {
         auto warp = [&](auto kernel, int rows_per_step) -> int {
             const long long groups = (rows + rows_per_step - 1) / rows_per_step;
-            kernel<<<ko::clamp_grid((groups + 7) / 8, 0), 256, 0, s>>>(in, out, rows, cols);
-            KO_CHECK_LAUNCH("softmax16_warp_kernel");
-            return KO_OK;
+            return ko::launch_overlapped(kernel, ko::clamp_grid((groups + 7) / 8, 0), 256, 0, s, in, out, (long long)rows, (int)cols);
         };
         if (nvec <= 8) return warp(ko::softmax16_warp_kernel<T, 1, 2, 8>, 8);
         if (nvec <= 16) return warp(ko::softmax16_warp_kernel<T, 2, 2, 8>, 8);
@@ -111,9 +106,7 @@ int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStre
     }
     if (vec_ok && nvec <= 1024 * 4) {
         auto block = [&](auto kernel, int threads) -> int {
-            kernel<<<ko::clamp_grid(rows, 0), threads, 0, s>>>(in, out, rows, cols);
-            KO_CHECK_LAUNCH("softmax16_block_kernel");
-            return KO_OK;
+            return ko::launch_overlapped(kernel, ko::clamp_grid(rows, 0), (unsigned)threads, 0, s, in, out, (long long)rows, (int)cols);
         };
         if (nvec <= 256 * 2) return block(ko::softmax16_block_kernel<T, 2, 256>, 256);
         if (nvec <= 256 * 4) return block(ko::softmax16_block_kernel<T, 4, 256>, 256);

@@ -72,6 +72,24 @@ int launch_clustered(void (*kernel)(KernelArgs...), unsigned grid, unsigned bloc
     return KO_OK;
 }
 
+// Launch `kernel` so that its blocks may be scheduled while the stream's previous kernel drains
+// (programmatic dependent launch); the kernel orders itself with ko::grid_dependency_wait().
+template <typename... KernelArgs, typename... Args>
+int launch_overlapped(void (*kernel)(KernelArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    KO_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...));
+    return KO_OK;
+}
+
 // cluster size (power of two, <= 8) so that a block's slice of `nvec` vectors fits `per_block` vectors;
 // 0 when even 8 blocks are not enough
 inline int cluster_size_for(int nvec, int per_block, int wanted) {

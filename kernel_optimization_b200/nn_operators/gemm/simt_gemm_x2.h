@@ -149,6 +149,10 @@ __global__ void __launch_bounds__(32 * kWarpsM * kWarpsN * kGroups) sgemm_x2_ker
     const long long units = (long long)((p.M + BM - 1) / BM) * tiles_n * ktiles_total;
     const long long unit_begin = units * blockIdx.x / p.ctas, unit_end = units * (blockIdx.x + 1) / p.ctas;
 
+    // launched with programmatic stream serialization: this block may have been placed while the stream's
+    // previous kernel was draining; nothing global is touched before that kernel's writes are visible
+    grid_launch_dependents();
+    grid_dependency_wait();
     const uint32_t smem_base = smem_u32(smem);
     int m_base = 0, n_base = 0;
     bool inner_mn = false;  // the tile lies inside M and N: K-tiles inside K need no bounds checks

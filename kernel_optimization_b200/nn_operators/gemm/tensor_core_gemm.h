@@ -287,11 +287,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         prefetch_tensormap(&map_b);
         if (kTmaStore) prefetch_tensormap(&map_d);
     }
+    grid_launch_dependents();  // the stream's next kernel may set up while this one drains
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // launched with programmatic stream serialization: barriers, tensor memory and descriptor prefetch above
+    // overlap the previous kernel's tail; operands and D are touched only after its writes are visible
+    grid_dependency_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer

@@ -648,6 +648,8 @@ __device__ __forceinline__ void layernorm_stream_tier(const T *in, T *out, long 
 template <typename T, int kVecs, int kRows>
 __global__ void __launch_bounds__(256) layernorm_warp_kernel(const T *in, T *out, long long rows, int cols, float eps,
                                                              const T *gamma, const T *beta, int ddof) {
+    grid_launch_dependents();  // the next kernel of the stream may take SMs as this one's blocks retire
+    grid_dependency_wait();    // nothing is read before the previous kernel's writes are visible
     layernorm_warp_tier<T, kVecs, kRows>(in, out, rows, cols, eps, gamma, beta, ddof);
 }
 template <typename T, int kVecs, int kRows, int kConsumerWarps>
@@ -662,12 +664,16 @@ template <typename T, int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) layernorm_block_kernel(const T *in, T *out, long long rows, int cols,
                                                                    float eps, const T *gamma, const T *beta, int ddof) {
     __shared__ float s_exchange[96];
+    grid_launch_dependents();
+    grid_dependency_wait();
     layernorm_block_tier<T, kVecs>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
 }
 template <typename T, int kVecs, int kThreads, bool kAffine>
 __global__ void __launch_bounds__(kThreads) layernorm_resident_kernel(const T *in, T *out, long long rows, int cols,
                                                                       float eps, const T *gamma, const T *beta, int ddof) {
     __shared__ float s_exchange[96];
+    grid_launch_dependents();
+    grid_dependency_wait();
     layernorm_resident_tier<T, kVecs, kThreads, kAffine>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
 }
 template <typename T, int kVecs, int kThreads>

@@ -315,6 +315,8 @@ __device__ __forceinline__ void softmax_stream_tier(const float *in, float *out,
 // runtime-shape kernels used by the C ABI
 template <int kVecs, int kSlots, int G>
 __global__ void __launch_bounds__(256) softmax_warp_kernel(const float *in, float *out, long long rows, int cols) {
+    grid_launch_dependents();  // the next kernel of the stream may take SMs as this one's blocks retire
+    grid_dependency_wait();    // nothing is read before the previous kernel's writes are visible
     softmax_warp_tier<kVecs, kSlots, G>(in, out, rows, cols);
 }
 template <int kVecs, int kSlots, int G, int kConsumerWarps>
@@ -326,6 +328,8 @@ softmax_staged_kernel(const float *in, float *out, long long rows, int cols, con
 template <int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) softmax_block_kernel(const float *in, float *out, long long rows, int cols) {
     __shared__ float s_exchange[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
     softmax_block_tier<kVecs>(in, out, rows, cols, s_exchange);
 }
 template <int kVecs, int kThreads>

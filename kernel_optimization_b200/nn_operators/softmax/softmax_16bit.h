@@ -83,6 +83,8 @@ __global__ void __launch_bounds__(256) softmax16_warp_kernel(const T *in, T *out
     const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint4 *in_v = reinterpret_cast<const uint4 *>(in);
     uint4 *out_v = reinterpret_cast<uint4 *>(out);
+    grid_launch_dependents();  // launched with programmatic stream serialization: see common.h
+    grid_dependency_wait();
 
     for (long long row0 = warp_global * kRowsPerStep; row0 < rows; row0 += warps_per_grid * kRowsPerStep) {
         // every load of the step is issued before the first use
@@ -140,6 +142,8 @@ __global__ void __launch_bounds__(kThreads) softmax16_block_kernel(const T *in, 
     const int nvec = cols >> 3;
     const uint4 *in_v = reinterpret_cast<const uint4 *>(in);
     uint4 *out_v = reinterpret_cast<uint4 *>(out);
+    grid_launch_dependents();
+    grid_dependency_wait();
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
         float x[kVecs][8];
         float m = kNegInf;
