@@ -61,13 +61,13 @@ int make_map_b_row_major(EncodeTiledFn encode, CUtensorMap *map, int fmt, const 
     return KO_OK;
 }
 
-template <int BN, bool kTmaStore>
+template <int BN, bool kTmaStore, int MT = 1>
 int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &md, const ko::tc::GemmParams &p, int sm_count,
            cudaStream_t s) {
-    using Cfg = ko::tc::TileConfig<BN>;
-    auto kernel = ko::tc::gemm_tcgen05_kernel<BN, kTmaStore>;
+    using Cfg = ko::tc::TileConfig<BN, MT>;
+    auto kernel = ko::tc::gemm_tcgen05_kernel<BN, kTmaStore, MT>;
     if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), Cfg::kSmemBytes)) return st;
-    const long long tiles = (long long)((p.M + ko::tc::kBM - 1) / ko::tc::kBM) * ((p.N + BN - 1) / BN);
+    const long long tiles = (long long)((p.M + MT * ko::tc::kBM - 1) / (MT * ko::tc::kBM)) * ((p.N + BN - 1) / BN);
     const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
     return ko::launch_overlapped(kernel, grid, (unsigned)ko::tc::kThreads, (size_t)Cfg::kSmemBytes, s, ma, mb, md, p);
 }
@@ -89,10 +89,10 @@ int make_store_map(EncodeTiledFn encode, CUtensorMap *map, int out_fmt, void *D,
     return KO_OK;
 }
 
-double wave_efficiency(long long M, long long N, int bn, int sm_count) {
-    const long long tiles = ((M + 127) / 128) * ((N + bn - 1) / bn);
+double wave_efficiency(long long M, long long N, int bn, int sm_count, int bm = 128) {
+    const long long tiles = ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
     const long long waves = (tiles + sm_count - 1) / sm_count;
-    return (double)(M * N) / (double)(waves * sm_count * 128LL * bn);
+    return (double)(M * N) / (double)(waves * sm_count * (long long)bm * bn);
 }
 
 }  // namespace
@@ -101,7 +101,8 @@ extern "C" {
 
 // fmt: A and B, 0 = F16, 1 = BF16; out_fmt: D and C, 0 = FP32, 1 = F16, 2 = BF16; b_row_major: 0 = B[K,N]
 // column-major (K contiguous), 1 = row-major (N contiguous); bn: 0 = choose, else 64 / 128 / 256 columns per tile;
-// store_mode: 0 = choose, 1 = TMA-store epilogue (error if not possible), 2 = direct stores
+// store_mode: 0 = choose, 1 = TMA-store epilogue (error if not possible), 2 = direct stores;
+// bn = 512 selects the 256 x 256 tile (two 128-row halves per CTA share every B tile)
 int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
                      const void *C, void *D, int bn, int store_mode, void *stream) {
     KO_REQUIRE(fmt == 0 || fmt == 1, KO_ERR_INVALID_ARG, "gemm: fmt must be 0 (f16) or 1 (bf16)");
@@ -128,11 +129,22 @@ int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N
         const double e128 = 0.80 * wave_efficiency(M, N, 128, info.sm_count);
         bn = (N > 128 && e256 >= e128) ? 256 : 128;
         if (N <= 64) bn = 64;
+        if (bn == 256 && M > 128) {
+            // 256 x 256 tiles (two halves share each B tile) against 128 x 256: the 128-row tile is limited by operand
+            // delivery (measured 0.87 of the 256-row tile's rate on long K), the 256-row tile pays its epilogue
+            // un-overlapped (about 2.5 K-blocks' worth of time per tile) and has half as many tiles to fill the waves.
+            // 4096^3: 0.83 vs 0.75 (measured 101 vs 109 us); 16384 x 3072 x 768: 0.72 vs 0.82 (114 vs 97 us).
+            const double k_blocks = (double)((K + ko::tc::kBK - 1) / ko::tc::kBK);
+            const double tall = wave_efficiency(M, N, 256, info.sm_count, 256) / (1.0 + 2.5 / k_blocks);
+            if (tall > 0.87 * e256) bn = 512;
+        }
     }
-    KO_REQUIRE(bn == 64 || bn == 128 || bn == 256, KO_ERR_INVALID_ARG, "gemm: tile width %d not in {64,128,256}", bn);
+    KO_REQUIRE(bn == 64 || bn == 128 || bn == 256 || bn == 512, KO_ERR_INVALID_ARG, "gemm: tile width %d not in {64,128,256,512}", bn);
+    const int mt = bn == 512 ? 2 : 1;
+    if (bn == 512) bn = 256;
 
     alignas(64) CUtensorMap map_a, map_b, map_d;
-    if (int st = make_map(encode, &map_a, fmt, A, M, K, ko::tc::kBM)) return st;
+    if (int st = make_map(encode, &map_a, fmt, A, M, K, mt * ko::tc::kBM)) return st;
     if (int st = b_row_major ? make_map_b_row_major(encode, &map_b, fmt, B, K, N) : make_map(encode, &map_b, fmt, B, N, K, bn))
         return st;
     // TMA-store epilogue when D has a 16-byte pitch and nothing is added to it
@@ -150,6 +162,9 @@ int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N
     p.C = C; p.D = D; p.fmt = fmt; p.out_fmt = out_fmt; p.b_row_major = b_row_major;
     if (int st = ko::device_status_word(0, &p.status)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (mt == 2)
+        return tma_store ? launch<256, true, 2>(map_a, map_b, map_d, p, info.sm_count, s)
+                         : launch<256, false, 2>(map_a, map_b, map_d, p, info.sm_count, s);
     switch (bn) {
         case 64: return tma_store ? launch<64, true>(map_a, map_b, map_d, p, info.sm_count, s) : launch<64, false>(map_a, map_b, map_d, p, info.sm_count, s);
         case 128: return tma_store ? launch<128, true>(map_a, map_b, map_d, p, info.sm_count, s) : launch<128, false>(map_a, map_b, map_d, p, info.sm_count, s);

@@ -41,7 +41,8 @@ int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int
  * 1 = one block per tile, n > 1 = n K-slices per tile */
 int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
                        int variant, int split_k, void *stream);
-/* fmt: 0 = F16, 1 = BF16 (A, B); out_fmt: 0 = FP32, 1 = F16, 2 = BF16 (D, C); b_row_major: 0 / 1; bn: 0 = choose, else 64 / 128 / 256 columns of D per tile;
+/* fmt: 0 = F16, 1 = BF16 (A, B); out_fmt: 0 = FP32, 1 = F16, 2 = BF16 (D, C); b_row_major: 0 / 1; bn: 0 = choose,
+ * 64 / 128 / 256 = columns of D per 128-row tile, 512 = the 256 x 256 tile (two 128-row halves per CTA share each B tile);
  * store_mode: 0 = choose, 1 = TMA-store epilogue (KO_ERR_SHAPE when not possible), 2 = direct stores */
 int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
                      const void *C, void *D, int bn, int store_mode, void *stream);

@@ -53,14 +53,18 @@ constexpr int kThreads = 192;     // 6 warps: producer, MMA, 4 x epilogue
 // codes written to the status word (first failure wins)
 enum : unsigned { kStatusOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3, kTimeoutDrain = 4 };
 
-template <int BN>
+// MT: 128-row halves of the tile that share every B tile (1 or 2).  With MT = 2 a CTA computes 256 x BN: the
+// operand bytes brought into shared memory per MMA drop by a third (A 32 KB + B 32 KB per 8 MMAs instead of
+// A 16 KB + B 32 KB per 4), which is what limits the 128-row tile on long K; the two halves then fill tensor
+// memory (2 x BN columns), so the epilogue of a tile no longer overlaps the next tile's MMAs.
+template <int BN, int MT = 1>
 struct TileConfig {
     static constexpr int kBN = BN;
-    static constexpr int kBytesA = kBM * kBK * 2;
+    static constexpr int kBytesA = MT * kBM * kBK * 2;
     static constexpr int kBytesB = BN * kBK * 2;
     static constexpr int kStageBytes = kBytesA + kBytesB;
-    static constexpr int kStages = BN >= 256 ? 4 : 6;
-    static constexpr int kTmemCols = 2 * BN;  // double-buffered FP32 accumulator (power of two >= 32)
+    static constexpr int kStages = MT == 2 ? 3 : (BN >= 256 ? 4 : 6);
+    static constexpr int kTmemCols = 2 * BN;  // MT = 1: double-buffered FP32 accumulator; MT = 2: one per half (power of two >= 32)
     static constexpr int kBarrierBytes = 256;
     // epilogue staging for TMA stores: per epilogue warp two 32-row x 32-column FP32 boxes (4 KB each)
     static constexpr int kStoreBoxBytes = 32 * 32 * 4;
@@ -68,6 +72,8 @@ struct TileConfig {
     // + 1024 so the stage ring can be aligned to the 1024-byte swizzle period
     static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBarrierBytes + 1024;
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN must keep 2*BN a power of two <= 512");
+    static_assert(MT == 1 || MT == 2, "one or two 128-row halves");
+    static_assert(kSmemBytes <= 232448, "stage ring exceeds the shared memory of an SM");
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -244,11 +250,12 @@ __device__ __forceinline__ void store_row_segment(const float (&v)[32], const Ge
 
 // kTmaStore: D is written by TMA stores staged through shared memory (needs a 16-byte row pitch and base for D
 // and no C operand); otherwise every thread stores its row segment directly (and adds C when given)
-template <int BN, bool kTmaStore>
+template <int BN, bool kTmaStore, int MT = 1>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
-    using Cfg = TileConfig<BN>;
+    using Cfg = TileConfig<BN, MT>;
+    constexpr int kTileM = MT * kBM;
     extern __shared__ uint8_t ko_tc_smem_raw[];
     // stage ring on a 1024-byte boundary (swizzle period), barriers behind it
     const uint32_t raw = smem_u32(ko_tc_smem_raw);
@@ -266,7 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_m = (p.M + kBM - 1) / kBM, tiles_n = (p.N + BN - 1) / BN;
+    const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + BN - 1) / BN;
     const long long num_tiles = (long long)tiles_m * tiles_n;
     const int k_blocks = (p.K + kBK - 1) / kBK;
 
@@ -316,7 +323,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                     mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
                     const uint32_t dst = ring + s * Cfg::kStageBytes;
-                    tma_load_2d(dst, &map_a, kb * kBK, tm * kBM, full_bar(s));
+                    tma_load_2d(dst, &map_a, kb * kBK, tm * kTileM, full_bar(s));  // one box of kTileM rows
                     if (!p.b_row_major) {
                         tma_load_2d(dst + Cfg::kBytesA, &map_b, kb * kBK, tn * BN, full_bar(s));
                     } else {
@@ -344,7 +351,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
             for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
-                const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+                // MT = 1: two accumulators used in turn; MT = 2: one accumulator per half, both busy with every tile
+                const uint32_t acc = MT == 1 ? (local_tile & 1u) : 0u, acc_phase = (MT == 1 ? (local_tile >> 1) : local_tile) & 1u;
                 if (!mbar_wait(acc_free_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
@@ -362,6 +370,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         const uint64_t db = p.b_row_major ? smem_desc_mn_major_sw128(b_addr + k * 2048)
                                                           : smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
                         umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (MT == 2) {  // rows 128..255 of the tile: 16 KB further in the stage, accumulator columns BN..2BN-1
+                            const uint64_t da1 = smem_desc_k_major_sw128(a_addr + kBM * kBK * 2 + k * kUmmaK * 2);
+                            umma_f16(d_tmem + BN, da1, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
                     umma_commit(empty_bar(s));  // the stage is reusable once these MMAs have read it
                 }
@@ -386,7 +398,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
             int tm, tn;
             tile_coords(t, tiles_m, tiles_n, tm, tn);
-            const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+            const uint32_t acc = MT == 1 ? (local_tile & 1u) : 0u, acc_phase = (MT == 1 ? (local_tile >> 1) : local_tile) & 1u;
             if (!mbar_wait(acc_ready_bar(acc), acc_phase, abort_flag)) {
                 if (lane == 0 && !*abort_flag) atomicCAS(p.status, kStatusOk, kTimeoutEpilogue);
                 *abort_flag = 1;
@@ -394,13 +406,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 break;
             }
             tc_fence_after();
-            const int row = tm * kBM + quad * 32 + lane;
-            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int half = 0; half < MT; ++half) {
+            const int row = tm * kTileM + half * kBM + quad * 32 + lane;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (MT == 1 ? acc * BN : half * BN);
             if constexpr (kTmaStore) {
                 // registers -> swizzled shared box (row = lane, 8 chunks of 16 B, chunk j stored at j ^ (row & 7):
                 // conflict-free, and exactly the 128-byte swizzle the store's tensor map undoes) -> TMA store
                 const int ep_warp = warp - 2;
-                const int row_base = tm * kBM + quad * 32;
+                const int row_base = tm * kTileM + half * kBM + quad * 32;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     float v[32];
@@ -451,6 +465,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
             }
+            }  // halves
             // the accumulator buffer may be overwritten once all four warps have read it
             tc_fence_before();
             __syncwarp();

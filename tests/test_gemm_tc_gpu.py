@@ -58,10 +58,12 @@ def _case(cuda, lib, oracle, kind, M, N, K, with_c=False, bn=0, seed=3, store_mo
 
 
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
-@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("bn", [64, 128, 256, 512])   # 512: the 256 x 256 tile (two 128-row halves per CTA)
 def test_single_tile_and_k_steps(cuda, lib, oracle, kind, bn):
     for K in (64, 128, 8, 72, 1024):
-        _case(cuda, lib, oracle, kind, 128, bn, K, bn=bn)
+        _case(cuda, lib, oracle, kind, 128, min(bn, 256), K, bn=bn)
+        if bn == 512:
+            _case(cuda, lib, oracle, kind, 256, 256, K, bn=bn)
 
 
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
@@ -73,7 +75,7 @@ def test_tails_and_multiple_tiles(cuda, lib, oracle, kind, M, N, K):
     _case(cuda, lib, oracle, kind, M, N, K, with_c=True)
 
 
-@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("bn", [64, 128, 256, 512])
 def test_both_epilogues_give_the_same_bits(cuda, lib, oracle, bn):
     for M, N, K in ((128, 256, 64), (1000, 520, 200), (129, 260, 136), (4096, 1024, 128)):
         d_tma = _case(cuda, lib, oracle, "bf16", M, N, K, bn=bn, store_mode=1)
@@ -142,7 +144,7 @@ def test_argument_checks(cuda, lib):
 # the 16-bit result must equal the FP32 result rounded once, bit for bit.
 TOL_OUT16 = {"f16": TOL_FRO, "bf16": 2.0 ** -9}
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
-@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256, 512])
 @pytest.mark.parametrize("M,N,K", [(128, 64, 64), (128, 256, 16), (256, 512, 256), (100, 40, 56), (129, 264, 136),
                                    (1000, 520, 200), (2048, 1024, 512), (131, 4104, 64), (5000, 16, 320)])
 def test_row_major_b_matches_column_major_bits(cuda, lib, oracle, kind, bn, M, N, K):
@@ -209,3 +211,22 @@ def test_named_16_bit_entry_points_and_row_major_16_bit(cuda, lib, oracle):
         assert cuda.equal(d1.view(cuda.int16), d2.view(cuda.int16))
         got = from_bits(d1.view(cuda.int16).cpu().numpy().view(np.uint16)).astype(np.float64)
         assert oracle.rel_frobenius(got, oracle.gemm_tn_f64(from_bits(ab), from_bits(bb))) <= TOL_OUT16[kind]
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (1000, 520, 200), (129, 264, 136), (2048, 1024, 512), (300, 8, 64),
+                                   (5000, 300, 320), (38000, 256, 64)])
+def test_256_row_tile_gives_the_bits_of_the_128_row_tile(cuda, lib, oracle, kind, M, N, K):
+    """bn = 512: a CTA computes 256 x 256 (two 128-row halves share each B tile, single-buffered accumulators); every
+    output still sees the same MMAs in the same order.  (38000 rows: more tiles than SMs, both accumulator phases.)"""
+    to_bits, from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 3, 0)), to_bits(oracle.fill_uniform((N, K), 3, 1))
+    c = oracle.fill_uniform((M, N), 3, 2)
+    base = _run(cuda, lib, kind, ab, bb, bn=256)
+    assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=512), base)
+    assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=512, store_mode=2), base)
+    assert np.array_equal(_run(cuda, lib, kind, ab, bb, c, bn=512), _run(cuda, lib, kind, ab, bb, c, bn=256))
+    assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=512, out16=True), _run(cuda, lib, kind, ab, bb, bn=256, out16=True))
+    if M <= 5000:
+        err = oracle.rel_frobenius(base, oracle.gemm_tn_f64(from_bits(ab), from_bits(bb)))
+        assert err <= TOL_FRO and err <= tight(K)
