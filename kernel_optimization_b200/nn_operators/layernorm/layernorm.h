@@ -259,8 +259,7 @@ __device__ __forceinline__ void layernorm_rows_from_registers(const typename Row
                 st_stream(out_v + (row0 + r) * nvec + v, Io::pack_pairs(y2));
             }
         }
-        return;
-    }
+    } else {
     Welford stats[kRows];
 #pragma unroll
     for (int r = 0; r < kRows; ++r) stats[r] = welford_of_vectors<T, kVecs>(raw[r], my_vecs);
@@ -282,6 +281,7 @@ __device__ __forceinline__ void layernorm_rows_from_registers(const typename Row
             st_stream(out_v + (row0 + r) * nvec + v, normalise_vector<T>(raw[r][j], mean[r], rstd[r], gamma_v, beta_v, v));
         }
     }
+    }  // long rows
 }
 
 // ---------------------------------------------------------------------------------------------
