@@ -113,6 +113,27 @@ __device__ __forceinline__ void row_pipeline(const void *in, long long rows, con
     __syncthreads();
 }
 
+// ---------------------------------------------------------------------------------------------
+// one-row prefetch used by the block- and cluster-per-row tiers: warp 0 copies a block's next row (or its
+// slice of it) into a shared-memory buffer with 1-D bulk copies while the current row is processed from
+// registers; one mbarrier counts the bytes, the consumers' wait is bounded (mbar_wait)
+// ---------------------------------------------------------------------------------------------
+constexpr unsigned kRowPrefetchTimeout = 3;  // status code (row-operator status word)
+constexpr uint32_t kBulkPiece = 16384;       // bytes per bulk copy: the lanes of warp 0 issue the pieces of a row in parallel
+
+__device__ __forceinline__ void prefetch_row(const void *row_ptr, uint32_t row_bytes, uint32_t buf, uint32_t bar) {
+    // warp 0 only; row_bytes is a multiple of 16
+    const int lane = threadIdx.x & 31;
+    fence_proxy_async();  // the buffer's previous contents were read through the generic proxy (ordered by the block barrier)
+    if (lane == 0) mbar_expect_tx(bar, row_bytes);
+    __syncwarp();
+    for (uint32_t off = (uint32_t)lane * kBulkPiece; off < row_bytes; off += 32u * kBulkPiece) {
+        const uint32_t n = min(kBulkPiece, row_bytes - off);
+        bulk_load_1d(buf + off, reinterpret_cast<const uint8_t *>(row_ptr) + off, n, bar);
+    }
+}
+
+
 // Work split inside a stage: the stage's rows form groups of `rows_per_group` (what one warp takes
 // at a time); groups are dealt round-robin over the consumer warps, continuing across stages so that
 // stages smaller than one group per warp still keep every warp busy.

@@ -79,8 +79,16 @@ int launch_resident_vecs(int vecs, const Args<T> &a, long long grid_cap, int sm_
 template <typename T>
 int launch_cluster(const Args<T> &a, int c, long long grid_cap, int sm_count, cudaStream_t s) {
     const int slice = (a.cols / ko::RowIo<T>::kPerVec + c - 1) / c;
+    const int threads = slice <= 256 * 4 ? 256 : 1024;
+    // clusters that can be resident at once (a cluster lives inside one GPC: fewer than SMs / c); more than that
+    // would run as a second wave behind grid-stride loops that already cover every row
+    const void *probe = threads == 256 ? reinterpret_cast<const void *>(ko::layernorm_cluster_kernel<T, 4, 256>)
+                                       : reinterpret_cast<const void *>(ko::layernorm_cluster_kernel<T, 8, 1024>);
+    int resident = 0;
+    if (int st = ko::max_resident_clusters(probe, (unsigned)threads, (unsigned)c, 0, &resident)) return st;
+    (void)sm_count;
     long long clusters = a.rows;
-    const long long cap = grid_cap > 0 ? grid_cap / c : (long long)(sm_count / c) * 2;
+    const long long cap = grid_cap > 0 ? grid_cap / c : (long long)resident * (threads == 256 ? 2 : 1);
     if (clusters > cap) clusters = cap > 0 ? cap : 1;
     const unsigned grid = (unsigned)(clusters * c);
     if (slice <= 256 * 4)
@@ -138,7 +146,8 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         // (16 of FP32); beyond that the resident tier (row unpacked once, packed FP32 math) is faster
         else if (warp_ok && (sizeof(T) == 4 || nvec <= 256)) tier = 1;
         else if (nvec <= 1024 * 4) tier = 5;
-        else if (nvec <= 1024 * kMaxVecsPerThread) tier = 2;
+        else if (nvec <= 1024 * kMaxVecsPerThread) tier = 2;  // (prefetching the next row, as softmax does, measured no gain here:
+                                                                // gamma and beta, re-read from L2 for every row, set the pace)
         else if (nvec <= 8 * 1024 * kMaxVecsPerThread) tier = 6;  // beyond one block's registers: a cluster holds the row
         else tier = 3;
     }

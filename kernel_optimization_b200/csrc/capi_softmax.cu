@@ -39,16 +39,57 @@ int launch_block(const float *in, float *out, long long rows, int cols, long lon
                                  rows, cols);
 }
 
-// one row per cluster of `c` blocks of 1024 threads, up to 8 vectors per thread
-int launch_cluster(const float *in, float *out, long long rows, int cols, int c, long long grid_cap, int sm_count,
-                   cudaStream_t s) {
+// one row per block in registers, the next row prefetched into shared memory by a bulk copy; one block per SM
+template <int kVecs, int kThreads>
+int launch_block_prefetch(const float *in, float *out, long long rows, int cols, long long grid_cap, int sm_count, cudaStream_t s) {
+    unsigned *status = nullptr;
+    if (int st = ko::device_status_word(1, &status)) return st;
+    auto kernel = ko::softmax_block_prefetch_kernel<kVecs, kThreads>;
+    const size_t smem = (size_t)cols * 4;
+    if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), smem)) return st;
+    const int per_sm = smem <= 100 * 1024 && kThreads <= 512 ? 2 : 1;
+    const long long cap = grid_cap > 0 ? grid_cap : (long long)sm_count * per_sm;
+    return ko::launch_overlapped(kernel, ko::clamp_grid(rows, cap), (unsigned)kThreads, smem, s, in, out, rows, cols, status);
+}
+
+// one row per cluster of `c` blocks; a block holds up to 8 vectors per thread.  256-thread blocks when the slice
+// allows: several clusters (rows) then share an SM and one row's reductions and cluster barriers overlap another's
+// loads, which a single 1024-thread block per SM cannot do.  threads: 0 = choose, 256 or 1024.
+int launch_cluster(const float *in, float *out, long long rows, int cols, int c, int threads, bool prefetch, long long grid_cap,
+                   int sm_count, cudaStream_t s) {
     const int slice = (cols / 4 + c - 1) / c;
+    if (threads == 0) threads = slice <= 256 * 8 ? 256 : (slice <= 512 * 8 ? 512 : 1024);
+    KO_REQUIRE((threads == 256 || threads == 512 || threads == 1024) && slice <= threads * 8, KO_ERR_SHAPE,
+               "softmax: a cluster of %d blocks of %d threads holds at most %d columns", c, threads, c * threads * 32);
+    const bool use_prefetch = prefetch && threads == 1024 && slice > 1024 * 4;
+    const size_t smem = use_prefetch ? (size_t)slice * 16 : 0;
+    // clusters that can be resident at once: a cluster lives inside one GPC, so this can be fewer than SMs / c;
+    // more clusters than that would run as a second wave behind grid-stride loops that already cover every row
+    const void *probe = use_prefetch ? reinterpret_cast<const void *>(ko::softmax_cluster_prefetch_kernel<8, 1024>)
+                        : threads == 1024 ? reinterpret_cast<const void *>(ko::softmax_cluster_kernel<8, 1024>)
+                        : threads == 512  ? reinterpret_cast<const void *>(ko::softmax_cluster_kernel<8, 512>)
+                                          : reinterpret_cast<const void *>(ko::softmax_cluster_kernel<8, 256>);
+    if (smem) {
+        if (int st = ko::ensure_dynamic_smem(probe, smem)) return st;
+    }
+    int resident = 0;
+    if (int st = ko::max_resident_clusters(probe, (unsigned)threads, (unsigned)c, smem, &resident)) return st;
     long long clusters = rows;
-    const long long cap = grid_cap > 0 ? grid_cap / c : (long long)(sm_count / c) * 2;
+    const long long cap = grid_cap > 0 ? grid_cap / c : (long long)resident;
     if (clusters > cap) clusters = cap > 0 ? cap : 1;
     const unsigned grid = (unsigned)(clusters * c);
-    if (slice <= 256 * 4) return ko::launch_clustered(ko::softmax_cluster_kernel<4, 256>, grid, 256, c, s, in, out, rows, cols);
+    if (threads == 256) {
+        if (slice <= 256 * 4) return ko::launch_clustered(ko::softmax_cluster_kernel<4, 256>, grid, 256, c, s, in, out, rows, cols);
+        return ko::launch_clustered(ko::softmax_cluster_kernel<8, 256>, grid, 256, c, s, in, out, rows, cols);
+    }
+    if (threads == 512) return ko::launch_clustered(ko::softmax_cluster_kernel<8, 512>, grid, 512, c, s, in, out, rows, cols);
     if (slice <= 1024 * 4) return ko::launch_clustered(ko::softmax_cluster_kernel<4, 1024>, grid, 1024, c, s, in, out, rows, cols);
+    if (use_prefetch) {
+        // one 1024-thread block per SM: the slice of the next row is prefetched into shared memory meanwhile
+        unsigned *status = nullptr;
+        if (int st = ko::device_status_word(1, &status)) return st;
+        return ko::launch_clustered_smem(ko::softmax_cluster_prefetch_kernel<8, 1024>, grid, 1024, c, smem, s, in, out, rows, cols, status);
+    }
     return ko::launch_clustered(ko::softmax_cluster_kernel<8, 1024>, grid, 1024, c, s, in, out, rows, cols);
 }
 
@@ -138,7 +179,7 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
     if (rows == 0 || cols == 0) return KO_OK;
     KO_REQUIRE(in != nullptr && out != nullptr, KO_ERR_INVALID_ARG, "softmax: NULL pointer");
     const ko_row_knobs_t k = knobs ? *knobs : ko_row_knobs_t{};
-    KO_REQUIRE((k.tier >= 0 && k.tier <= 4) || k.tier == 6, KO_ERR_INVALID_ARG, "softmax: unknown tier %d", k.tier);
+    KO_REQUIRE((k.tier >= 0 && k.tier <= 4) || k.tier == 6 || k.tier == 7, KO_ERR_INVALID_ARG, "softmax: unknown tier %d", k.tier);
     KO_REQUIRE(k.cluster == 0 || k.cluster == 2 || k.cluster == 4 || k.cluster == 8, KO_ERR_INVALID_ARG,
                "softmax: cluster size %d not in {2,4,8}", k.cluster);
     KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
@@ -153,15 +194,18 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
     if (tier == 0) {
         if (!vec_ok) tier = 3;
         else if (nvec <= 32 * 16) tier = 1;  // measured faster than the staged tier at every BASELINE shape
-        else if (nvec <= 1024 * 8) tier = 2;
+        else if (nvec <= 1024 * 4) tier = 2;
+        else if (nvec <= 1024 * 8) tier = 7;  // beyond 16384 columns one block per SM: prefetch the next row (5.8 vs 4.4 TB/s at 32768)
         else if (nvec <= 8 * 1024 * 8) tier = 6;  // beyond one block's registers: a cluster holds the row
         else tier = 3;
     }
     if (tier == 6) {
         KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "softmax: the cluster tier needs cols %% 4 == 0 and 16-byte aligned pointers");
-        const int c = ko::cluster_size_for(nvec, 1024 * 8, k.cluster);
-        KO_REQUIRE(c > 0, KO_ERR_SHAPE, "softmax: %d columns exceed what a cluster of 8 blocks holds (262144)", cols);
-        return launch_cluster(in, out, rows, cols, c, k.grid_cap, info.sm_count, s);
+        // the smallest cluster that holds the row (larger clusters measured slower: every row costs two cluster barriers)
+        const int c = ko::cluster_size_for(nvec, 1024 * 8, k.cluster);  // k.cluster: where the search starts
+        KO_REQUIRE(c > 0 && (nvec + c - 1) / c <= 1024 * 8, KO_ERR_SHAPE, "softmax: %d columns exceed what a cluster of %d blocks holds", cols, c ? c : 8);
+        const int threads = (k.block == 256 || k.block == 512 || k.block == 1024) ? k.block : 0;
+        return launch_cluster(in, out, rows, cols, c, threads, k.stages != 1, k.grid_cap, info.sm_count, s);  // stages = 1: no prefetch
     }
     if (tier == 4) {
         KO_REQUIRE(vec_ok && nvec <= 32 * 16, KO_ERR_SHAPE, "softmax: the staged tier needs cols %% 4 == 0, cols <= 2048 and 16-byte aligned pointers");
@@ -175,6 +219,13 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
         KO_REQUIRE(vec_ok && nvec <= 32 * 16, KO_ERR_SHAPE, "softmax: the warp tier needs cols %% 4 == 0, cols <= 2048 and 16-byte aligned pointers");
         bool used = false;
         return dispatch_rows<false>(nvec, k.rows_per_warp, in, out, rows, cols, k, info, s, &used);
+    }
+    if (tier == 7) {
+        KO_REQUIRE(vec_ok && nvec > 0 && nvec <= 1024 * 8, KO_ERR_SHAPE,
+                   "softmax: the prefetching block tier needs cols %% 4 == 0, cols <= 32768 and 16-byte aligned pointers");
+        if (nvec <= 512 * 4) return launch_block_prefetch<4, 512>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+        if (nvec <= 1024 * 4) return launch_block_prefetch<4, 1024>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+        return launch_block_prefetch<8, 1024>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
     }
     if (tier == 2) {
         KO_REQUIRE(vec_ok && nvec <= 1024 * 8, KO_ERR_SHAPE, "softmax: the block tier needs cols %% 4 == 0, cols <= 32768 and 16-byte aligned pointers");

@@ -13,7 +13,9 @@ extern "C" {
 typedef struct ko_row_knobs {
     int tier;            /* 0 = choose, 1 = warp, 2 = block, 3 = stream (scalar), 4 = staged (TMA ring),
                             5 = resident (LayerNorm only: persistent blocks, packed FP32 math),
-                            6 = cluster (one row per thread-block cluster, partials through DSMEM) */
+                            6 = cluster (one row per thread-block cluster, partials through DSMEM; softmax: stages = 1
+                                turns the shared-memory prefetch of the next row's slice off),
+                            7 = prefetching block (softmax only: row in registers, next row bulk-copied to shared memory) */
     int rows_per_warp;   /* warp / staged tier: independent row slots a warp processes together (a slot is
                             one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows) */
     int block;           /* warp tier: threads per block (<= 256); block / resident tier: threads per row (128..1024) */

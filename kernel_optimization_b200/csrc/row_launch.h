@@ -54,12 +54,12 @@ int ensure_dynamic_smem(const void *kernel, size_t bytes);
 
 // Launch `kernel` with thread-block clusters of `cluster` blocks along x (grid must be a multiple of it).
 template <typename... KernelArgs, typename... Args>
-int launch_clustered(void (*kernel)(KernelArgs...), unsigned grid, unsigned block, unsigned cluster, cudaStream_t s,
-                     Args... args) {
+int launch_clustered_smem(void (*kernel)(KernelArgs...), unsigned grid, unsigned block, unsigned cluster, size_t smem,
+                          cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(block, 1, 1);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -88,6 +88,31 @@ int launch_overlapped(void (*kernel)(KernelArgs...), unsigned grid, unsigned blo
     cfg.numAttrs = 1;
     KO_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...));
     return KO_OK;
+}
+
+// how many clusters of `cluster` blocks of `kernel` the current device can hold at once (at least 1)
+inline int max_resident_clusters(const void *kernel, unsigned block, unsigned cluster, size_t smem, int *out) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cluster, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    KO_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+    *out = n > 0 ? n : 1;
+    return KO_OK;
+}
+
+template <typename... KernelArgs, typename... Args>
+int launch_clustered(void (*kernel)(KernelArgs...), unsigned grid, unsigned block, unsigned cluster, cudaStream_t s,
+                     Args... args) {
+    return launch_clustered_smem(kernel, grid, block, cluster, 0, s, args...);
 }
 
 // cluster size (power of two, <= 8) so that a block's slice of `nvec` vectors fits `per_block` vectors;

@@ -236,6 +236,66 @@ __device__ __forceinline__ void softmax_block_tier(const float *in, float *out, 
 }
 
 // ---------------------------------------------------------------------------------------------
+// prefetching block tier: one row per block in registers, the block's NEXT row landing in shared memory
+// ---------------------------------------------------------------------------------------------
+// A block that holds a long row in registers has nothing in flight while it reduces, and with 1024 threads
+// there is one block per SM, so nobody else covers for it: the plain block tier moves 4.4 TB/s at 32768
+// columns.  Here warp 0 starts a 1-D bulk copy (TMA) of the block's next row into a shared-memory row buffer as
+// soon as the current row has been lifted from that buffer into registers; the copy runs under the reductions,
+// the exponentials and the stores of the current row.  One mbarrier counts the bytes; the wait is bounded.
+template <int kVecs, int kThreads>
+__device__ __forceinline__ void softmax_block_prefetch_tier(const float *in, float *out, long long rows, int cols, float4 *row_buf,
+                                                            uint64_t *bar_word, float *s_exchange, unsigned *status) {
+    const int nvec = cols >> 2;
+    const uint32_t row_bytes = (uint32_t)cols * 4u;
+    const uint32_t buf = smem_u32(row_buf), bar = smem_u32(bar_word);
+    float4 *out4 = reinterpret_cast<float4 *>(out);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+    long long row = blockIdx.x;
+    if (row < rows && threadIdx.x < 32) prefetch_row(in + row * cols, row_bytes, buf, bar);
+    volatile int never_aborted = 0;
+    uint32_t parity = 0;
+    for (; row < rows; row += gridDim.x, parity ^= 1u) {
+        const bool landed = mbar_wait(bar, parity, &never_aborted);
+        if (!__syncthreads_and(landed)) {  // the whole block leaves together
+            if (threadIdx.x == 0) atomicCAS(status, 0u, kRowPrefetchTimeout);
+            break;
+        }
+        float4 x[kVecs];
+        float m = kNegInf;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = threadIdx.x + kThreads * j;
+            x[j] = v < nvec ? row_buf[v] : neg_inf4();
+            m = fmaxf(m, max4(x[j]));
+        }
+        __syncthreads();  // the buffer has been read by everyone: it may be refilled
+        const long long next = row + gridDim.x;
+        if (next < rows && threadIdx.x < 32) prefetch_row(in + next * cols, row_bytes, buf, bar);
+        m = block_allreduce<true>(m, s_exchange);
+        const float neg = -m * kLog2e;
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) s += exp_shifted4(x[j], neg);
+        s = block_allreduce<false>(s, s_exchange);
+        const float inv = rcp_approx(s);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = threadIdx.x + kThreads * j;
+            if (v < nvec) {
+                scale4(x[j], inv);
+                st_stream(out4 + row * nvec + v, x[j]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // cluster tier: one row per thread-block CLUSTER, the row in the registers of all its blocks
 // ---------------------------------------------------------------------------------------------
 // For rows beyond one block's registers (more than 32768 columns) or few very long rows: each of the
@@ -243,9 +303,13 @@ __device__ __forceinline__ void softmax_block_tier(const float *in, float *out, 
 // through distributed shared memory (every block reads its peers' partials with plain loads from
 // their shared memory), so the row is still read from HBM exactly once.  Two cluster barriers per row;
 // the exchange slots are double buffered by row parity so no third barrier is needed.
-template <int kVecs>
+// kPrefetch: the block's slice of the cluster's NEXT row is brought into a shared-memory buffer by a bulk copy while
+// the current row is reduced, exchanged and stored (see the prefetching block tier); row_buf / bar_word / status are
+// used only then.
+template <int kVecs, bool kPrefetch>
 __device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out, long long rows, int cols,
-                                                     float *s_exchange, float (*s_part)[2]) {
+                                                     float *s_exchange, float (*s_part)[2], float4 *row_buf = nullptr,
+                                                     uint64_t *bar_word = nullptr, unsigned *status = nullptr) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned nblocks = cluster.num_blocks(), rank = cluster.block_rank();
@@ -255,15 +319,53 @@ __device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out
     const float4 *in4 = reinterpret_cast<const float4 *>(in);
     float4 *out4 = reinterpret_cast<float4 *>(out);
     const long long clusters = gridDim.x / nblocks, first = blockIdx.x / nblocks;
+    const uint32_t slice_bytes = v_end > v_begin ? (uint32_t)(v_end - v_begin) * 16u : 0u;
+    const uint32_t buf = kPrefetch ? smem_u32(row_buf) : 0u, bar = kPrefetch ? smem_u32(bar_word) : 0u;
+    if (kPrefetch) {
+        if (threadIdx.x == 0) {
+            mbar_init(bar, 1);
+            fence_barrier_init();
+            fence_proxy_async();
+        }
+        __syncthreads();
+        if (first < rows && slice_bytes && threadIdx.x < 32)
+            prefetch_row(reinterpret_cast<const float *>(in4 + first * nvec + v_begin), slice_bytes, buf, bar);
+    }
+    volatile int never_aborted = 0;
+    uint32_t landed_parity = 0;
+    bool gave_up = false;
     int parity = 0;
     for (long long row = first; row < rows; row += clusters, parity ^= 1) {
         float4 x[kVecs];
         float m = kNegInf;
+        if (kPrefetch) {
+            // a block that gives up still takes part in every cluster barrier below (its peers must not hang):
+            // it works on padding from here on and the status word reports the call as failed
+            if (slice_bytes && !gave_up) {
+                const bool landed = mbar_wait(bar, landed_parity, &never_aborted);
+                landed_parity ^= 1u;
+                if (!__syncthreads_and(landed)) {
+                    if (threadIdx.x == 0) atomicCAS(status, 0u, kRowPrefetchTimeout);
+                    gave_up = true;
+                }
+            }
 #pragma unroll
-        for (int j = 0; j < kVecs; ++j) {
-            const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
-            x[j] = v < v_end ? ld_stream(in4 + row * nvec + v) : neg_inf4();
-            m = fmaxf(m, max4(x[j]));
+            for (int j = 0; j < kVecs; ++j) {
+                const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
+                x[j] = (v < v_end && !gave_up) ? row_buf[v - v_begin] : neg_inf4();
+                m = fmaxf(m, max4(x[j]));
+            }
+            __syncthreads();  // the buffer has been read by everyone: it may be refilled
+            const long long next = row + clusters;
+            if (next < rows && slice_bytes && !gave_up && threadIdx.x < 32)
+                prefetch_row(reinterpret_cast<const float *>(in4 + next * nvec + v_begin), slice_bytes, buf, bar);
+        } else {
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
+                x[j] = v < v_end ? ld_stream(in4 + row * nvec + v) : neg_inf4();
+                m = fmaxf(m, max4(x[j]));
+            }
         }
         m = block_allreduce<true>(m, s_exchange);
         if (threadIdx.x == 0) s_part[parity][0] = m;
@@ -282,7 +384,7 @@ __device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
             const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
-            if (v < v_end) {
+            if (v < v_end && !gave_up) {
                 scale4(x[j], inv);
                 st_stream(out4 + row * nvec + v, x[j]);
             }
@@ -333,10 +435,30 @@ __global__ void __launch_bounds__(kThreads) softmax_block_kernel(const float *in
     softmax_block_tier<kVecs>(in, out, rows, cols, s_exchange);
 }
 template <int kVecs, int kThreads>
+__global__ void __launch_bounds__(kThreads) softmax_block_prefetch_kernel(const float *in, float *out, long long rows, int cols,
+                                                                         unsigned *status) {
+    extern __shared__ __align__(128) uint8_t ko_row_buffer[];  // one row
+    __shared__ float s_exchange[33];
+    __shared__ __align__(8) uint64_t s_bar;
+    grid_launch_dependents();
+    grid_dependency_wait();
+    softmax_block_prefetch_tier<kVecs, kThreads>(in, out, rows, cols, reinterpret_cast<float4 *>(ko_row_buffer), &s_bar, s_exchange,
+                                                 status);
+}
+template <int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) softmax_cluster_kernel(const float *in, float *out, long long rows, int cols) {
     __shared__ float s_exchange[33];
     __shared__ float s_part[2][2];
-    softmax_cluster_tier<kVecs>(in, out, rows, cols, s_exchange, s_part);
+    softmax_cluster_tier<kVecs, false>(in, out, rows, cols, s_exchange, s_part);
+}
+template <int kVecs, int kThreads>
+__global__ void __launch_bounds__(kThreads) softmax_cluster_prefetch_kernel(const float *in, float *out, long long rows, int cols,
+                                                                           unsigned *status) {
+    extern __shared__ __align__(128) uint8_t ko_row_buffer[];  // this block's slice of one row
+    __shared__ float s_exchange[33];
+    __shared__ float s_part[2][2];
+    __shared__ __align__(8) uint64_t s_bar;
+    softmax_cluster_tier<kVecs, true>(in, out, rows, cols, s_exchange, s_part, reinterpret_cast<float4 *>(ko_row_buffer), &s_bar, status);
 }
 __global__ void __launch_bounds__(256) softmax_stream_kernel(const float *in, float *out, long long rows, int cols) {
     __shared__ float s_exchange[33];

@@ -84,6 +84,29 @@ def test_cluster_tier_exchanges_partials_through_dsmem(cuda, lib, oracle, cluste
         assert np.array_equal(y, _run(cuda, lib, x, tier=6, cluster=cluster, grid_cap=16))  # fewer clusters, more rows each
 
 
+@pytest.mark.parametrize("rows,cols", [(5, 4096), (37, 8192), (3, 20000), (7, 32768), (300, 16388), (2, 4)])
+def test_prefetching_block_tier_matches_the_block_tier(cuda, lib, oracle, rows, cols):
+    """tier 7: the block's next row lands in shared memory (bulk copy) while the current one is reduced from registers;
+    same arithmetic as the block tier, so the same bits, for any number of rows per block (phase bit flips)."""
+    x = oracle.fill_normal((rows, cols), 0, 0, 0.0, 2.0)
+    y = _run(cuda, lib, x, tier=7)
+    assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS and oracle.max_rowsum_err(y) <= TOL_ROWSUM
+    assert np.array_equal(y, _run(cuda, lib, x, tier=2))
+    assert np.array_equal(y, _run(cuda, lib, x, tier=7, grid_cap=2))   # two blocks take all rows: many refills each
+    assert lib.ko_poll_device_status() == 0
+
+
+def test_cluster_tier_with_and_without_prefetch(cuda, lib, oracle):
+    """Slices beyond 4096 vectors per block are prefetched into shared memory (stages=1 turns that off): same bits."""
+    for rows, cols in ((5, 65536), (40, 40000), (3, 262144), (300, 36864)):
+        x = oracle.fill_normal((rows, cols), 0, 0, 0.0, 2.0)
+        y = _run(cuda, lib, x, tier=6)
+        assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS
+        assert np.array_equal(y, _run(cuda, lib, x, tier=6, stages=1))
+        assert np.array_equal(y, _run(cuda, lib, x, tier=6, grid_cap=4))
+    assert lib.ko_poll_device_status() == 0
+
+
 def test_staged_tier_many_stages_per_block(cuda, lib, oracle):
     """Enough rows that every persistent block wraps its ring several times (phase bits flip)."""
     x = oracle.fill_normal((148 * 8 * 40 + 13, 128), 0, 0, 0.0, 2.0)
