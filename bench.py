@@ -156,7 +156,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3 * (STEP_BYTES / sample_bytes),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic (seeded Philox4x32-10 fills of the BASELINE shapes)",
+        "data": "synthetic (seeded Philox4x32-10 fills of the benchmark shapes)",
         "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": what},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -353,7 +353,7 @@ def run_gpu_arm(args):
         yl = [torch.empty_like(xl[0]) for _ in range(8)]
         ms = timed(lambda i: ref.ko_ref_layernorm_f32(xl[i % 8].data_ptr(), yl[i % 8].data_ptr(), LN_ROWS, LN_COLS, 1e-4, None, None, 0, stream()), 30, 3)
         ref_rows["layernorm_gbs"] = LN_BYTES / (ms * 1e-3) / 1e9
-        ref_rows["note"] = "SoftMaxWarpImpl / LayerNormWarpImpl at the reference driver's launch geometry; the LayerNorm result is not LayerNorm (see DESIGN.md)"
+        ref_rows["note"] = "SoftMaxWarpImpl / LayerNormWarpImpl at the reference driver's launch geometry; the LayerNorm result is not LayerNorm (its Welford merge divides at every level)"
         del xl, yl
 
     # ---- CPU baseline beside it (rank 0, single-GPU runs only)
@@ -373,7 +373,7 @@ def run_gpu_arm(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic (seeded Philox4x32-10 fills of the BASELINE shapes and distributions; no dataset involved)",
+            "data": "synthetic (seeded Philox4x32-10 fills of the benchmark shapes and distributions; no dataset involved)",
             "config": {"workload": WORKLOAD, "rows_per_gpu": {"softmax": SOFTMAX_ROWS, "layernorm": LN_ROWS},
                        "l2": f"inputs and outputs rotate over {n_sm_sets} (softmax) / {n_ln_sets} (layernorm) buffer sets "
                              f"({n_sm_sets * SOFTMAX_BYTES / 1e6:.0f} / {n_ln_sets * LN_BYTES / 1e6:.0f} MB of distinct addresses "
@@ -393,7 +393,7 @@ def run_gpu_arm(args):
 
 
 # --------------------------------------------------------------------------------------------------
-# BASELINE config 5: the scaled sweep, strong scaling (the totals are fixed, every rank takes 1/N)
+# benchmark config 5: the scaled sweep, strong scaling (the totals are fixed, every rank takes 1/N)
 # --------------------------------------------------------------------------------------------------
 C5_SOFTMAX_ROWS, C5_SOFTMAX_COLS = 8 * 196608, 512
 C5_LN_ROWS, C5_LN_COLS = 262144, 4096
@@ -512,7 +512,7 @@ def run_scaled(args):
         worst = {k: max(g[k] for g in gathered) for k in parity}
         row_bytes = out["softmax_f32_causal"]["bytes"] + out["layernorm_bf16"]["bytes"]
         row_ms = out["softmax_f32_causal"]["ms"] + out["layernorm_bf16"]["ms"]
-        emit({"metric": "scaled sweep (BASELINE config 5): softmax+layernorm HBM throughput", "value": row_bytes / (row_ms * 1e-3) / 1e9,
+        emit({"metric": "scaled sweep (benchmark config 5): softmax+layernorm HBM throughput", "value": row_bytes / (row_ms * 1e-3) / 1e9,
               "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": row_ms, "higher_is_better": True,
               "scaling": "strong", "vs_baseline": None, "dtype": "f32 softmax / bf16 layernorm (f32 statistics) / bf16 gemm (f32 accumulate)",
               "data": "synthetic (seeded Philox4x32-10, seed 4)",
@@ -526,11 +526,11 @@ def run_scaled(args):
 
 CASES = {
     "sgemm_2048": "FP32 SGEMM 2048^3 (48 MB of operands)",
-    "sgemm_1024": "FP32 SGEMM 1024^3 (BASELINE config 3)",
-    "gemm_bf16_4096": "BF16 tcgen05 GEMM 4096^3 (BASELINE config 4)",
-    "gemm_bf16_ffn": "BF16 tcgen05 GEMM 16384x3072x768 (BASELINE config 4, FFN shape)",
-    "softmax_c5_shard": "softmax FP32 [196608,512] with the causal -1e4 pattern (1/8 of BASELINE config 5)",
-    "layernorm_bf16_c5_shard": "LayerNorm BF16 [32768,4096] (1/8 of BASELINE config 5)",
+    "sgemm_1024": "FP32 SGEMM 1024^3 (benchmark config 3)",
+    "gemm_bf16_4096": "BF16 tcgen05 GEMM 4096^3 (benchmark config 4)",
+    "gemm_bf16_ffn": "BF16 tcgen05 GEMM 16384x3072x768 (benchmark config 4, FFN shape)",
+    "softmax_c5_shard": "softmax FP32 [196608,512] with the causal -1e4 pattern (1/8 of benchmark config 5)",
+    "layernorm_bf16_c5_shard": "LayerNorm BF16 [32768,4096] (1/8 of benchmark config 5)",
 }
 
 
@@ -596,7 +596,7 @@ def run_case(args):
 # --sweep: README-style rows (percent of the copy-bandwidth peak / of the vendor library) in one command
 # --------------------------------------------------------------------------------------------------
 SWEEP_ROW_SHAPES = {
-    # (rows, cols): the BASELINE configs, the shape the reference's drivers were written for (49152 x 1024,
+    # (rows, cols): the benchmark configs, the shape the reference's drivers were written for (49152 x 1024,
     # nn_operators/softmax/main.cu:78-79) and long rows for the block and cluster tiers
     "softmax": {"f32": [(196608, 128), (49152, 1024), (196608, 512), (8192, 8192), (512, 65536)],
                 "f16": [(196608, 128), (49152, 1024)], "bf16": [(196608, 512), (49152, 1024)]},

@@ -193,7 +193,7 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
     int tier = k.tier;
     if (tier == 0) {
         if (!vec_ok) tier = 3;
-        else if (nvec <= 32 * 16) tier = 1;  // measured faster than the staged tier at every BASELINE shape
+        else if (nvec <= 32 * 16) tier = 1;  // measured faster than the staged tier at every benchmark shape
         else if (nvec <= 1024 * 4) tier = 2;
         else if (nvec <= 1024 * 8) tier = 7;  // beyond 16384 columns one block per SM: prefetch the next row (5.8 vs 4.4 TB/s at 32768)
         else if (nvec <= 8 * 1024 * 8) tier = 6;  // beyond one block's registers: a cluster holds the row

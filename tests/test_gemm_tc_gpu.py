@@ -1,5 +1,5 @@
 """GPU parity of ko_gemm_f16_f32 / ko_gemm_bf16_f32 (tcgen05, through the C ABI) against the float64
-oracle on the rounded inputs.  Tolerance (BASELINE): relative Frobenius error <= 1e-3; with exact
+oracle on the rounded inputs.  Tolerance (benchmark specification): relative Frobenius error <= 1e-3; with exact
 products and FP32 accumulation the kernel actually lands near 1e-6, which is asserted too so that
 a dropped K-step or a mis-addressed tile cannot hide under the loose bound."""
 import numpy as np

@@ -1,7 +1,7 @@
 """GPU parity of ko_layernorm_f32 / ko_layernorm_bf16 (through the C ABI) against the float64
 oracle and size-independent properties at the full shapes.
 
-Tolerance (BASELINE): max-rel <= 1e-5 with max-rel = max |y - ref| / max(|ref|, 1).  BF16 output is
+Tolerance (benchmark specification): max-rel <= 1e-5 with max-rel = max |y - ref| / max(|ref|, 1).  BF16 output is
 compared with the BF16-rounded oracle: at most a rounding-boundary flip (one BF16 ulp) is allowed
 and only on a small fraction of the elements."""
 import numpy as np

@@ -24,7 +24,7 @@ def test_softmax_port_and_literal_against_reference_kernel(oracle, golden):
         # the reference is built with -use_fast_math: agreement to a few 1e-7, not bit for bit
         assert np.abs(oracle.softmax_f32(x, literal=True) - ref).max() <= 5e-7
         assert np.abs(oracle.softmax_f32(x) - ref).max() <= 5e-7
-        assert oracle.max_abs_err(ref, oracle.softmax_f64(x)) <= 1e-6      # BASELINE tolerance
+        assert oracle.max_abs_err(ref, oracle.softmax_f64(x)) <= 1e-6      # the benchmark's tolerance
         assert oracle.max_abs_err(oracle.softmax_f32(x), oracle.softmax_f64(x)) <= 1e-6
         assert oracle.max_rowsum_err(oracle.softmax_f32(x)) <= 1e-5
 

@@ -1,5 +1,5 @@
 """GPU parity of ko_sgemm_f32 (through the C ABI): relative Frobenius error <= 1e-6 against float64
-(BASELINE tolerance); without a K split also bit-identical to the FP32 oracle port (one FFMA per k in
+(the benchmark's tolerance); without a K split also bit-identical to the FP32 oracle port (one FFMA per k in
 ascending k, the reference's order) and to the committed outputs of the reference's own kernel."""
 import numpy as np
 import pytest

@@ -1,7 +1,7 @@
 """GPU parity of ko_softmax_f32 (through the C ABI) against the float64 oracle, the committed
 outputs of the reference's own kernel, and size-independent properties at the full shapes.
 
-Tolerances (BASELINE): max-abs <= 1e-6, every row sum within 1e-5 of 1."""
+Tolerances (benchmark specification): max-abs <= 1e-6, every row sum within 1e-5 of 1."""
 import numpy as np
 import pytest
 
