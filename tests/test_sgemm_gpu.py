@@ -81,7 +81,10 @@ def test_unit_ranges_that_straddle_tiles(cuda, lib, oracle, M, N, K):
 
 
 def test_default_dispatch(cuda, lib, oracle):
-    for M, N, K in SHAPES:
+    # the second group exercises the launcher's choices: grouped shapes with a split across blocks, tails in M, N
+    # and K, short K, a single tile row / column, more than two waves of tiles
+    for M, N, K in SHAPES + [(100, 3000, 5000), (1000, 130, 700), (2000, 2000, 40), (64, 64, 10000), (65, 4000, 129),
+                             (4000, 65, 1000), (3000, 3000, 24)]:
         a, b = oracle.fill_uniform((M, K), 2, 0), oracle.fill_uniform((K, N), 2, 1)
         assert oracle.rel_frobenius(_run(cuda, lib, a, b), oracle.sgemm_f64(a, b)) <= TOL_FRO
 
