@@ -275,15 +275,15 @@ def run_gpu_arm(args):
 
     def e2e_step(_i):
         # the public host-tensor calls: rows flow through copy-in / kernel / copy-out streams in chunks
-        ko.softmax_host(t_sm_in, t_sm_out, SOFTMAX_ROWS, SOFTMAX_COLS, E2E_CHUNKS)
-        ko.layernorm_host(t_ln_in, t_ln_out, LN_ROWS, LN_COLS, LN_EPS, gamma, beta, 0, E2E_CHUNKS)
+        ko.softmax_host(t_sm_in, t_sm_out, SOFTMAX_ROWS, SOFTMAX_COLS, args.e2e_chunks)
+        ko.layernorm_host(t_ln_in, t_ln_out, LN_ROWS, LN_COLS, LN_EPS, gamma, beta, 0, args.e2e_chunks)
 
     e2e_steps = max(3, min(args.steps, 20))
     ms_e2e = timed(e2e_step, e2e_steps, 3)
     h2d = SOFTMAX_BYTES // 2 + LN_ROWS * LN_COLS * 4
     e2e = {"value": STEP_BYTES * world / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": h2d, "ms_per_step": ms_e2e, "steps": e2e_steps,
-           "path": f"ko_softmax_f32_host + ko_layernorm_f32_host, {E2E_CHUNKS} chunks each: pinned host -> device -> kernel -> pinned host, "
+           "path": f"ko_softmax_f32_host + ko_layernorm_f32_host, {args.e2e_chunks} chunks each: pinned host -> device -> kernel -> pinned host, "
                    "copies of neighbouring chunks overlap (PCIe is full duplex); every step ends with all results on the host"}
     if rank == 0:
         from oracle import ko_oracle as oracle
@@ -716,6 +716,8 @@ def main():
                     help="buffer sets to rotate over (0 = default 4/8); 1 keeps a profiler capture small")
     ap.add_argument("--workload", choices=["bert_base", "scaled"], default="bert_base",
                     help="bert_base: configs 1+2 per GPU, weak scaling (default); scaled: config 5 totals, strong scaling")
+    ap.add_argument("--e2e-chunks", type=int, default=E2E_CHUNKS,
+                    help="row chunks per host-tensor call in the end-to-end leg (copy-in / kernel / copy-out pipeline depth)")
     ap.add_argument("--sweep", action="store_true",
                     help="every operator over a list of shapes next to the vendor library (one JSON line, table on stderr)")
     ap.add_argument("--case", choices=sorted(CASES), default=None,
