@@ -59,9 +59,15 @@ int launch_block_vecs(int vecs, const Args<T> &a, long long grid_cap, cudaStream
 
 template <typename T, int kVecs, int kThreads>
 int launch_resident(const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
-    const long long cap = grid_cap > 0 ? grid_cap : (long long)sm_count * (kThreads <= 256 ? 8 : (kThreads <= 512 ? 4 : 2));
+    // persistent blocks: exactly as many as the device holds at once, so that no block waits for a slot and the
+    // rows are dealt evenly (more blocks than that would run as a partly filled second wave)
+    const bool affine = a.gamma || a.beta;
+    int per_sm = 0;
+    if (affine) KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ko::layernorm_resident_kernel<T, kVecs, kThreads, true>, kThreads, 0));
+    else KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ko::layernorm_resident_kernel<T, kVecs, kThreads, false>, kThreads, 0));
+    const long long cap = grid_cap > 0 ? grid_cap : (long long)sm_count * (per_sm > 0 ? per_sm : 1);
     const unsigned grid = ko::clamp_grid(a.rows, cap);
-    if (a.gamma || a.beta)
+    if (affine)
         return ko::launch_overlapped(ko::layernorm_resident_kernel<T, kVecs, kThreads, true>, grid, kThreads, 0, s, a.in, a.out,
                                      (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
     return ko::launch_overlapped(ko::layernorm_resident_kernel<T, kVecs, kThreads, false>, grid, kThreads, 0, s, a.in, a.out,
