@@ -94,7 +94,7 @@ int launch_cluster(const Args<T> &a, int c, long long grid_cap, int sm_count, cu
     if (int st = ko::max_resident_clusters(probe, (unsigned)threads, (unsigned)c, 0, &resident)) return st;
     (void)sm_count;
     long long clusters = a.rows;
-    const long long cap = grid_cap > 0 ? grid_cap / c : (long long)resident * (threads == 256 ? 2 : 1);
+    const long long cap = grid_cap > 0 ? grid_cap / c : (long long)resident;
     if (clusters > cap) clusters = cap > 0 ? cap : 1;
     const unsigned grid = (unsigned)(clusters * c);
     if (slice <= 256 * 4)
