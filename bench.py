@@ -531,6 +531,7 @@ CASES = {
     "gemm_bf16_ffn": "BF16 tcgen05 GEMM 16384x3072x768 (benchmark config 4, FFN shape)",
     "softmax_c5_shard": "softmax FP32 [196608,512] with the causal -1e4 pattern (1/8 of benchmark config 5)",
     "layernorm_bf16_c5_shard": "LayerNorm BF16 [32768,4096] (1/8 of benchmark config 5)",
+    "softmax_long_rows": "softmax FP32 [2048,32768]: one row per block in registers, the next row prefetched by a bulk copy",
 }
 
 
@@ -560,6 +561,12 @@ def run_case(args):
         d = torch.empty((M, N), device=dev)
         launch = lambda: native.check(lib.ko_gemm_bf16_f32(M, N, K, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s()), name)  # noqa: E731
         work, unit = 2.0 * M * N * K, "TFLOP/s"
+    elif name == "softmax_long_rows":
+        rows, cols = 2048, 32768
+        xd = torch.from_numpy(ko.fill_normal((rows, cols), 0, 0, 0.0, 2.0)).to(dev)
+        yd = torch.empty_like(xd)
+        launch = lambda: native.check(lib.ko_softmax_f32(xd.data_ptr(), yd.data_ptr(), rows, cols, s()), name)  # noqa: E731
+        work, unit = 2.0 * rows * cols * 4, "GB/s"
     elif name == "softmax_c5_shard":
         rows, cols = 196608, 512
         x = ko.fill_normal((rows, cols), 4, 0, 0.0, 2.0)
