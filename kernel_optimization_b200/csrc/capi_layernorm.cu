@@ -150,7 +150,8 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         if (!vec_ok) tier = 3;
         // measured on B200: the warp tier wins while a lane holds at most 8 vectors of 16-bit data
         // (16 of FP32); beyond that the resident tier (row unpacked once, packed FP32 math) is faster
-        else if (warp_ok && (sizeof(T) == 4 || nvec <= 256)) tier = 1;
+        // (BF16 [32768,2048]: resident tier with 128-thread blocks 46.0 us, warp tier 51.8 us; at 1024 columns they tie)
+        else if (warp_ok && (sizeof(T) == 4 || nvec <= 128)) tier = 1;
         else if (nvec <= 1024 * 4) tier = 5;
         else if (nvec <= 1024 * kMaxVecsPerThread) tier = 2;  // (prefetching the next row, as softmax does, measured no gain here:
                                                                 // gamma and beta, re-read from L2 for every row, set the pace)
@@ -168,7 +169,7 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         KO_REQUIRE(vec_ok && nvec <= 1024 * 4, KO_ERR_SHAPE, "layernorm: the resident tier needs 16-byte aligned rows of at most 4096 vectors");
         int threads = k.block;
         if (threads == 0) {
-            threads = 256;  // two vectors per thread at 4096 BF16 columns
+            threads = nvec <= 256 ? 128 : 256;  // two vectors per thread at 2048 and 4096 columns of 16-bit data
             while (threads < 1024 && nvec > threads * 4) threads *= 2;
         }
         KO_REQUIRE(nvec <= threads * 4, KO_ERR_SHAPE, "layernorm: %d threads hold at most %d vectors per row", threads, threads * 4);

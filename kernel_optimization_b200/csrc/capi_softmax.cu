@@ -55,8 +55,8 @@ int launch_block_prefetch(const float *in, float *out, long long rows, int cols,
 // one row per cluster of `c` blocks; a block holds up to 8 vectors per thread.  256-thread blocks when the slice
 // allows: several clusters (rows) then share an SM and one row's reductions and cluster barriers overlap another's
 // loads, which a single 1024-thread block per SM cannot do.  threads: 0 = choose, 256 or 1024.
-int launch_cluster(const float *in, float *out, long long rows, int cols, int c, int threads, bool prefetch, long long grid_cap,
-                   int sm_count, cudaStream_t s) {
+int launch_cluster(const float *in, float *out, long long rows, int cols, int c, int threads, bool prefetch, bool mailbox,
+                   long long grid_cap, int sm_count, cudaStream_t s) {
     const int slice = (cols / 4 + c - 1) / c;
     if (threads == 0) threads = slice <= 256 * 8 ? 256 : (slice <= 512 * 8 ? 512 : 1024);
     KO_REQUIRE((threads == 256 || threads == 512 || threads == 1024) && slice <= threads * 8, KO_ERR_SHAPE,
@@ -88,7 +88,8 @@ int launch_cluster(const float *in, float *out, long long rows, int cols, int c,
         // one 1024-thread block per SM: the slice of the next row is prefetched into shared memory meanwhile
         unsigned *status = nullptr;
         if (int st = ko::device_status_word(1, &status)) return st;
-        return ko::launch_clustered_smem(ko::softmax_cluster_prefetch_kernel<8, 1024>, grid, 1024, c, smem, s, in, out, rows, cols, status);
+        return ko::launch_clustered_smem(ko::softmax_cluster_prefetch_kernel<8, 1024>, grid, 1024, c, smem, s, in, out, rows, cols, status,
+                                         mailbox ? 1 : 0);
     }
     return ko::launch_clustered(ko::softmax_cluster_kernel<8, 1024>, grid, 1024, c, s, in, out, rows, cols);
 }
@@ -205,7 +206,8 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
         const int c = ko::cluster_size_for(nvec, 1024 * 8, k.cluster);  // k.cluster: where the search starts
         KO_REQUIRE(c > 0 && (nvec + c - 1) / c <= 1024 * 8, KO_ERR_SHAPE, "softmax: %d columns exceed what a cluster of %d blocks holds", cols, c ? c : 8);
         const int threads = (k.block == 256 || k.block == 512 || k.block == 1024) ? k.block : 0;
-        return launch_cluster(in, out, rows, cols, c, threads, k.stages != 1, k.grid_cap, info.sm_count, s);  // stages = 1: no prefetch
+        // stages = 1: no prefetch; stages = 2: prefetch, partials exchanged with cluster barriers instead of mailboxes
+        return launch_cluster(in, out, rows, cols, c, threads, k.stages != 1, k.stages != 2, k.grid_cap, info.sm_count, s);
     }
     if (tier == 4) {
         KO_REQUIRE(vec_ok && nvec <= 32 * 16, KO_ERR_SHAPE, "softmax: the staged tier needs cols %% 4 == 0, cols <= 2048 and 16-byte aligned pointers");

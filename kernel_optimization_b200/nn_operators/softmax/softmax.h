@@ -306,10 +306,21 @@ __device__ __forceinline__ void softmax_block_prefetch_tier(const float *in, flo
 // kPrefetch: the block's slice of the cluster's NEXT row is brought into a shared-memory buffer by a bulk copy while
 // the current row is reduced, exchanged and stored (see the prefetching block tier); row_buf / bar_word / status are
 // used only then.
+// Partial (max, sum) exchange without cluster-wide barriers: every block pushes its value into each peer's mailbox
+// (a plain store into the peer's shared memory) and arrives on that peer's mbarrier; a block waits only for its own
+// mailbox to fill.  value[parity][kind][rank], one mbarrier per (parity, kind) expecting one arrival per block; row
+// parity double-buffers the slots -- a peer can be at most one exchange ahead, because every exchange needs
+// everybody's arrival.  A cluster barrier costs about 1.3 us per row and use here, this about a third of it.
+struct ClusterMailbox {
+    uint64_t bar[2][2];
+    float value[2][2][8];
+};
+
 template <int kVecs, bool kPrefetch>
 __device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out, long long rows, int cols,
                                                      float *s_exchange, float (*s_part)[2], float4 *row_buf = nullptr,
-                                                     uint64_t *bar_word = nullptr, unsigned *status = nullptr) {
+                                                     uint64_t *bar_word = nullptr, unsigned *status = nullptr,
+                                                     ClusterMailbox *mail = nullptr) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned nblocks = cluster.num_blocks(), rank = cluster.block_rank();
@@ -331,11 +342,28 @@ __device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out
         if (first < rows && slice_bytes && threadIdx.x < 32)
             prefetch_row(reinterpret_cast<const float *>(in4 + first * nvec + v_begin), slice_bytes, buf, bar);
     }
+    if (mail) {
+        if (threadIdx.x == 0) {
+            for (int q = 0; q < 4; ++q) mbar_init(smem_u32(&mail->bar[q >> 1][q & 1]), nblocks);
+            fence_barrier_init();
+        }
+        cluster.sync();  // every mailbox is ready before anybody pushes into it
+    }
+    // all blocks call this with their block-wide value; returns once every block's value has arrived here
+    auto exchange = [&](int par, int kind, float v, uint32_t phase) -> bool {
+        if (threadIdx.x < nblocks) {
+            const uint32_t peer = threadIdx.x;
+            st_cluster_f32(map_to_cluster_rank(smem_u32(&mail->value[par][kind][rank]), peer), v);
+            mbar_arrive_cluster(map_to_cluster_rank(smem_u32(&mail->bar[par][kind]), peer));
+        }
+        return mbar_wait_cluster(smem_u32(&mail->bar[par][kind]), phase);
+    };
     volatile int never_aborted = 0;
     uint32_t landed_parity = 0;
     bool gave_up = false;
     int parity = 0;
-    for (long long row = first; row < rows; row += clusters, parity ^= 1) {
+    uint32_t use = 0;  // rows done by this cluster: the mailbox of a parity is on its (use / 2)-th phase
+    for (long long row = first; row < rows; row += clusters, parity ^= 1, ++use) {
         float4 x[kVecs];
         float m = kNegInf;
         if (kPrefetch) {
@@ -368,18 +396,35 @@ __device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out
             }
         }
         m = block_allreduce<true>(m, s_exchange);
-        if (threadIdx.x == 0) s_part[parity][0] = m;
-        cluster.sync();
-        for (unsigned r = 0; r < nblocks; ++r) m = fmaxf(m, cluster.map_shared_rank(&s_part[parity][0], r)[0]);
+        const uint32_t mail_phase = (use >> 1) & 1u;
+        if (mail) {
+            if (!exchange(parity, 0, m, mail_phase) && !gave_up) {
+                if (threadIdx.x == 0) atomicCAS(status, 0u, kRowPrefetchTimeout);
+                gave_up = true;  // keeps pushing (the peers wait for it) but writes nothing
+            }
+            for (unsigned r = 0; r < nblocks; ++r) m = fmaxf(m, mail->value[parity][0][r]);
+        } else {
+            if (threadIdx.x == 0) s_part[parity][0] = m;
+            cluster.sync();
+            for (unsigned r = 0; r < nblocks; ++r) m = fmaxf(m, cluster.map_shared_rank(&s_part[parity][0], r)[0]);
+        }
         const float neg = -m * kLog2e;
         float s = 0.f;
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) s += exp_shifted4(x[j], neg);  // padding: 2^(-inf) = 0
         s = block_allreduce<false>(s, s_exchange);
-        if (threadIdx.x == 0) s_part[parity][1] = s;
-        cluster.sync();
         float total = 0.f;
-        for (unsigned r = 0; r < nblocks; ++r) total += cluster.map_shared_rank(&s_part[parity][1], r)[0];  // rank order
+        if (mail) {
+            if (!exchange(parity, 1, s, mail_phase) && !gave_up) {
+                if (threadIdx.x == 0) atomicCAS(status, 0u, kRowPrefetchTimeout);
+                gave_up = true;
+            }
+            for (unsigned r = 0; r < nblocks; ++r) total += mail->value[parity][1][r];  // rank order
+        } else {
+            if (threadIdx.x == 0) s_part[parity][1] = s;
+            cluster.sync();
+            for (unsigned r = 0; r < nblocks; ++r) total += cluster.map_shared_rank(&s_part[parity][1], r)[0];  // rank order
+        }
         const float inv = rcp_approx(total);
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
@@ -453,12 +498,14 @@ __global__ void __launch_bounds__(kThreads) softmax_cluster_kernel(const float *
 }
 template <int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) softmax_cluster_prefetch_kernel(const float *in, float *out, long long rows, int cols,
-                                                                           unsigned *status) {
+                                                                           unsigned *status, int use_mailbox) {
     extern __shared__ __align__(128) uint8_t ko_row_buffer[];  // this block's slice of one row
     __shared__ float s_exchange[33];
     __shared__ float s_part[2][2];
     __shared__ __align__(8) uint64_t s_bar;
-    softmax_cluster_tier<kVecs, true>(in, out, rows, cols, s_exchange, s_part, reinterpret_cast<float4 *>(ko_row_buffer), &s_bar, status);
+    __shared__ __align__(8) ClusterMailbox s_mail;
+    softmax_cluster_tier<kVecs, true>(in, out, rows, cols, s_exchange, s_part, reinterpret_cast<float4 *>(ko_row_buffer), &s_bar, status,
+                                      use_mailbox ? &s_mail : nullptr);
 }
 __global__ void __launch_bounds__(256) softmax_stream_kernel(const float *in, float *out, long long rows, int cols) {
     __shared__ float s_exchange[33];

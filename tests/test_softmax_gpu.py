@@ -102,8 +102,10 @@ def test_cluster_tier_with_and_without_prefetch(cuda, lib, oracle):
         x = oracle.fill_normal((rows, cols), 0, 0, 0.0, 2.0)
         y = _run(cuda, lib, x, tier=6)
         assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS
-        assert np.array_equal(y, _run(cuda, lib, x, tier=6, stages=1))
+        assert np.array_equal(y, _run(cuda, lib, x, tier=6, stages=1))   # no prefetch, cluster barriers
+        assert np.array_equal(y, _run(cuda, lib, x, tier=6, stages=2))   # prefetch, cluster barriers instead of mailboxes
         assert np.array_equal(y, _run(cuda, lib, x, tier=6, grid_cap=4))
+
     assert lib.ko_poll_device_status() == 0
 
 
