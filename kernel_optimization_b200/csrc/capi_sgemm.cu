@@ -143,8 +143,16 @@ int launch_x2(int M, int N, int K, const float *A, const float *B, const float *
         // from 2048^3 on two 128-thread blocks per SM are faster).
         const long long wide_tiles = (long long)((M + 127) / 128) * ((N + 127) / 128);
         const int ktiles = (K + ko::sgemm2::BK - 1) / ko::sgemm2::BK;
+        // many tiles: the 64 x 128 shape with four groups (one 256-thread block per SM) also beats two 128-thread
+        // blocks per SM on long K (4096^3: 2334 vs 2431 us; 3072^3: 1011 vs 1074 us) as long as its waves are full;
+        // a partly empty last wave goes to the 128 x 128 shape, whose unit ranges balance it (2048^3: 341 vs 349 us),
+        // and so does short K, where a group's quarter of K is too few K-tiles (8192 x 8192 x 1024: 2486 vs 2549 us)
+        const long long narrow_tiles = (long long)((M + 63) / 64) * ((N + 127) / 128);
+        const long long waves = (narrow_tiles + sm_count - 1) / sm_count;
+        const bool full_waves = narrow_tiles * 100 >= waves * sm_count * 95;
         shape = 1;
-        if (split_k == 0 && wide_tiles <= sm_count && ktiles >= 8) shape = (M > 64 && ktiles >= 16) ? 3 : 2;
+        if (split_k == 0 && ktiles >= 8 && (wide_tiles <= sm_count || (full_waves && ktiles >= 128 && M > 64)))
+            shape = (M > 64 && ktiles >= 16) ? 3 : 2;
     }
     switch (shape) {
         case 1: return launch_x2_shape<2, 2, 1>(M, N, K, A, B, C, D, split_k, sm_count, s);

@@ -230,3 +230,21 @@ def test_256_row_tile_gives_the_bits_of_the_128_row_tile(cuda, lib, oracle, kind
     if M <= 5000:
         err = oracle.rel_frobenius(base, oracle.gemm_tn_f64(from_bits(ab), from_bits(bb)))
         assert err <= TOL_FRO and err <= tight(K)
+
+
+def test_general_entry_point_validates_its_arguments(cuda, lib):
+    s = cuda.cuda.current_stream().cuda_stream
+    a = cuda.zeros((128, 64), dtype=cuda.bfloat16, device="cuda")
+    b = cuda.zeros((64, 64), dtype=cuda.bfloat16, device="cuda")
+    d = cuda.zeros((128, 64), dtype=cuda.float32, device="cuda")
+    ok = (1, 0, 0, 128, 64, 64, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s)
+    assert lib.ko_gemm_tc(*ok) == 0
+    assert lib.ko_gemm_tc(2, *ok[1:]) == 1                                   # unknown input format
+    assert lib.ko_gemm_tc(1, 3, *ok[2:]) == 1                                # unknown output format
+    assert lib.ko_gemm_tc(1, 0, 2, *ok[3:]) == 1                             # unknown B layout
+    assert lib.ko_gemm_tc(1, 0, 0, 128, 64, 60, *ok[6:]) == 3                # K not a multiple of 8
+    assert lib.ko_gemm_tc(1, 0, 0, 0, 64, 64, *ok[6:]) == 0                  # empty output
+    assert lib.ko_gemm_tc(1, 0, 0, 128, 64, 64, a.data_ptr(), b.data_ptr(), None, a.data_ptr(), s) == 1   # D aliases A
+    assert lib.ko_gemm_tc(1, 0, 0, 128, 64, 64, a.data_ptr() + 2, b.data_ptr(), None, d.data_ptr(), s) == 2  # unaligned A
+    cuda.cuda.synchronize()
+    assert lib.ko_poll_device_status() == 0

@@ -150,3 +150,17 @@ def test_python_wrappers_accept_16bit_tensors(cuda, oracle, ko):
         y = ko.layernorm(xh, 1e-5)
         ref = cuda.nn.functional.layer_norm(xh.float(), (512,), eps=1e-5)
         assert y.dtype == dt and cuda.allclose(y.float(), ref, atol=3e-2)
+
+
+def test_16bit_entry_points_validate_their_arguments(cuda, lib):
+    s = cuda.cuda.current_stream().cuda_stream
+    x = cuda.zeros((4, 64), dtype=cuda.float16, device="cuda")
+    for fn in (lib.ko_softmax_f16, lib.ko_softmax_bf16):
+        assert fn(x.data_ptr(), x.data_ptr(), 0, 64, s) == 0            # empty: nothing to do
+        assert fn(x.data_ptr(), x.data_ptr(), 4, 0, s) == 0
+        assert fn(None, x.data_ptr(), 4, 64, s) == 1                    # NULL pointer
+        assert fn(x.data_ptr(), x.data_ptr(), -1, 64, s) == 1           # negative shape
+    assert lib.ko_layernorm_f16(x.data_ptr(), x.data_ptr(), 0, 64, 1e-5, None, None, 0, s) == 0
+    assert lib.ko_layernorm_f16(None, x.data_ptr(), 4, 64, 1e-5, None, None, 0, s) == 1
+    assert lib.ko_layernorm_f16(x.data_ptr(), x.data_ptr(), 4, 64, 1e-5, None, None, 2, s) == 1   # ddof outside {0, 1}
+    cuda.cuda.synchronize()
