@@ -160,6 +160,10 @@ int ko_layernorm_f32_host(ko_tensor_t *in, ko_tensor_t *out, int64_t rows, int32
  * 4,4,4>><<<grid, 128, smem, stream>>>(GemmCoord, A, B, C, D): nn_operators/gemm/gemm.h:11-21,
  * nn_operators/gemm/simt_gemm.h:46-375 (launched at nn_operators/gemm/main.cu:111-117).
  * Any M, N, K >= 1 (edges are predicated).  D must not alias A or B; D may equal C.
+ * Every output is a chain of FP32 FMAs in ascending k, as in the reference; depending on the shape the
+ * K range of a tile may be cut into parts that are accumulated that way and then added in K order
+ * (deterministic: the same call gives the same bits; relative Frobenius error <= 1e-6 either way).
+ * The first call on a (device, stream) that needs partial-tile scratch allocates it with cudaMalloc.
  * ---------------------------------------------------------------------------------------- */
 int ko_sgemm_f32(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C,
                  float *D, void *stream);
