@@ -8,14 +8,15 @@
 // exactly when it saturates the FMA pipe; 16 x 8 leaves 25% slack.  fma.rn.f32x2 performs two
 // IEEE-rounded FMAs per instruction.  (Measured alternatives that lost: the same tile with scalar FFMA,
 // 43 against 55 TFLOP/s at 4096^3; 16 x 4 per thread with twice the warps, shared-memory bound; A
-// stored twice in shared memory so that no register moves are needed to build {b, b} pairs, 43 TFLOP/s.)
+// stored twice in shared memory so that no register moves are needed to build {b, b} pairs, 43 TFLOP/s;
+// 32 x 4 per thread, which halves those moves at the price of three more shared loads per k, 54 TFLOP/s.)
 //
 // Data path: A[M,K] row-major is copied 4 bytes at a time straight into a TRANSPOSED shared tile
 // As[k][m] (cp.async with a source size of 0 zero-fills out-of-range elements, so every M, N, K is
 // legal and nothing is read out of bounds -- the reference prefetches past the end,
 // nn_operators/gemm/simt_gemm.h:287-292); B[K,N] goes in 16-byte pieces.  kStages tiles are in flight.
 //
-// Warp groups.  A block is kGroups independent groups of 2 x kWarpsN warps.  Every group has its own
+// Warp groups.  A block is kGroups independent groups of kWarpsM x kWarpsN warps.  Every group has its own
 // shared-memory ring and its own named barrier and accumulates a contiguous part of the block's K range
 // of the tile; at the end the groups exchange their partial tiles through the (then idle) rings, each
 // group finishing the chunks c with c % kGroups == group, summed in K order.  One group of 4 warps
