@@ -83,7 +83,7 @@ int launch_resident_vecs(int vecs, const Args<T> &a, long long grid_cap, int sm_
 
 // one row per cluster of `c` blocks of 1024 threads, up to 8 vectors per thread
 template <typename T>
-int launch_cluster(const Args<T> &a, int c, long long grid_cap, int sm_count, cudaStream_t s) {
+int launch_cluster(const Args<T> &a, int c, bool mailbox, long long grid_cap, int sm_count, cudaStream_t s) {
     const int slice = (a.cols / ko::RowIo<T>::kPerVec + c - 1) / c;
     const int threads = slice <= 256 * 4 ? 256 : 1024;
     // clusters that can be resident at once (a cluster lives inside one GPC: fewer than SMs / c); more than that
@@ -97,11 +97,17 @@ int launch_cluster(const Args<T> &a, int c, long long grid_cap, int sm_count, cu
     const long long cap = grid_cap > 0 ? grid_cap / c : (long long)resident;
     if (clusters > cap) clusters = cap > 0 ? cap : 1;
     const unsigned grid = (unsigned)(clusters * c);
+    unsigned *status = nullptr;
+    if (int st = ko::device_status_word(1, &status)) return st;
+    const int mail = mailbox ? 1 : 0;
     if (slice <= 256 * 4)
-        return ko::launch_clustered(ko::layernorm_cluster_kernel<T, 4, 256>, grid, 256, c, s, a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+        return ko::launch_clustered(ko::layernorm_cluster_kernel<T, 4, 256>, grid, 256, c, s, a.in, a.out, a.rows, a.cols, a.eps, a.gamma,
+                                    a.beta, a.ddof, status, mail);
     if (slice <= 1024 * 4)
-        return ko::launch_clustered(ko::layernorm_cluster_kernel<T, 4, 1024>, grid, 1024, c, s, a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
-    return ko::launch_clustered(ko::layernorm_cluster_kernel<T, 8, 1024>, grid, 1024, c, s, a.in, a.out, a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+        return ko::launch_clustered(ko::layernorm_cluster_kernel<T, 4, 1024>, grid, 1024, c, s, a.in, a.out, a.rows, a.cols, a.eps, a.gamma,
+                                    a.beta, a.ddof, status, mail);
+    return ko::launch_clustered(ko::layernorm_cluster_kernel<T, 8, 1024>, grid, 1024, c, s, a.in, a.out, a.rows, a.cols, a.eps, a.gamma,
+                                a.beta, a.ddof, status, mail);
 }
 
 template <typename T, bool kStaged>
@@ -162,7 +168,7 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "layernorm: the cluster tier needs 16-byte aligned rows");
         const int c = ko::cluster_size_for(nvec, 1024 * kMaxVecsPerThread, k.cluster);
         KO_REQUIRE(c > 0, KO_ERR_SHAPE, "layernorm: %d columns exceed what a cluster of 8 blocks holds", a.cols);
-        return launch_cluster<T>(a, c, k.grid_cap, info.sm_count, s);
+        return launch_cluster<T>(a, c, k.stages != 2, k.grid_cap, info.sm_count, s);  // stages = 2: cluster barriers instead of mailboxes
     }
     if (tier == 5) {
         // resident tier: at most 4 vectors per thread

@@ -562,10 +562,19 @@ __device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, lon
 // (n, mean, M2) triple; the triples sit in each block's shared memory and every block merges all of
 // them, in rank order, reading its peers' copies through distributed shared memory.  One cluster
 // barrier per row (slots double buffered by row parity); the row is read from HBM once.
+// mail: every block pushes its (n, mean, M2) into each peer's mailbox and arrives on that peer's mbarrier, a block
+// waits only for its own mailbox (bounded; a timeout is reported through `status`); nullptr: partials are read from
+// the peers' shared memory between cluster barriers.
+struct WelfordMailbox {
+    uint64_t bar[2];
+    float value[2][8][3];
+};
+
 template <typename T, int kVecs>
 __device__ __forceinline__ void layernorm_cluster_tier(const T *in, T *out, long long rows, int cols, float eps,
                                                        const T *gamma, const T *beta, int ddof, float *s_exchange,
-                                                       float (*s_part)[3]) {
+                                                       float (*s_part)[3], WelfordMailbox *mail = nullptr,
+                                                       unsigned *status = nullptr) {
     namespace cg = cooperative_groups;
     using Raw = typename RowIo<T>::Raw;
     cg::cluster_group cluster = cg::this_cluster();
@@ -581,8 +590,18 @@ __device__ __forceinline__ void layernorm_cluster_tier(const T *in, T *out, long
 #pragma unroll
     for (int j = 0; j < kVecs; ++j) my_vecs += (v_begin + (int)threadIdx.x + (int)blockDim.x * j < v_end) ? 1 : 0;
     const long long clusters = gridDim.x / nblocks, first = blockIdx.x / nblocks;
+    if (mail) {
+        if (threadIdx.x == 0) {
+            mbar_init(smem_u32(&mail->bar[0]), nblocks);
+            mbar_init(smem_u32(&mail->bar[1]), nblocks);
+            fence_barrier_init();
+        }
+        cluster.sync();  // every mailbox is ready before anybody pushes into it
+    }
     int parity = 0;
-    for (long long row = first; row < rows; row += clusters, parity ^= 1) {
+    uint32_t use = 0;  // rows done by this cluster: the mailbox of a parity is on its (use / 2)-th phase
+    bool gave_up = false;
+    for (long long row = first; row < rows; row += clusters, parity ^= 1, ++use) {
         Raw raw[kVecs];
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
@@ -592,25 +611,42 @@ __device__ __forceinline__ void layernorm_cluster_tier(const T *in, T *out, long
         }
         Welford w = welford_of_vectors<T, kVecs>(raw, my_vecs);
         w = block_allreduce_welford(w, s_exchange);
-        if (threadIdx.x == 0) {
-            s_part[parity][0] = w.n;
-            s_part[parity][1] = w.mean;
-            s_part[parity][2] = w.m2;
-        }
-        cluster.sync();
         Welford all{0.f, 0.f, 0.f};
-        for (unsigned r = 0; r < nblocks; ++r) {
-            const float *peer = cluster.map_shared_rank(&s_part[parity][0], r);
-            all = welford_merge(all, Welford{peer[0], peer[1], peer[2]});
+        if (mail) {
+            if (threadIdx.x < nblocks) {
+                const uint32_t peer = threadIdx.x;
+                const uint32_t slot = map_to_cluster_rank(smem_u32(&mail->value[parity][rank][0]), peer);
+                st_cluster_f32(slot, w.n);
+                st_cluster_f32(slot + 4, w.mean);
+                st_cluster_f32(slot + 8, w.m2);
+                mbar_arrive_cluster(map_to_cluster_rank(smem_u32(&mail->bar[parity]), peer));
+            }
+            if (!mbar_wait_cluster(smem_u32(&mail->bar[parity]), (use >> 1) & 1u) && !gave_up) {
+                if (threadIdx.x == 0) atomicCAS(status, 0u, kRowPrefetchTimeout);
+                gave_up = true;  // keeps pushing (the peers wait for it) but writes nothing
+            }
+            for (unsigned r = 0; r < nblocks; ++r)
+                all = welford_merge(all, Welford{mail->value[parity][r][0], mail->value[parity][r][1], mail->value[parity][r][2]});
+        } else {
+            if (threadIdx.x == 0) {
+                s_part[parity][0] = w.n;
+                s_part[parity][1] = w.mean;
+                s_part[parity][2] = w.m2;
+            }
+            cluster.sync();
+            for (unsigned r = 0; r < nblocks; ++r) {
+                const float *peer = cluster.map_shared_rank(&s_part[parity][0], r);
+                all = welford_merge(all, Welford{peer[0], peer[1], peer[2]});
+            }
         }
         const float mean = all.mean, rstd = rstd_from(all, cols, ddof, eps);
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
             const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
-            if (v < v_end) st_stream(out_v + row * nvec + v, normalise_vector<T>(raw[j], mean, rstd, gamma_v, beta_v, v));
+            if (v < v_end && !gave_up) st_stream(out_v + row * nvec + v, normalise_vector<T>(raw[j], mean, rstd, gamma_v, beta_v, v));
         }
     }
-    cluster.sync();  // no block may exit while a peer can still read its shared memory
+    cluster.sync();  // no block may exit while a peer can still read (or write) its shared memory
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -678,10 +714,13 @@ __global__ void __launch_bounds__(kThreads) layernorm_resident_kernel(const T *i
 }
 template <typename T, int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) layernorm_cluster_kernel(const T *in, T *out, long long rows, int cols, float eps,
-                                                                     const T *gamma, const T *beta, int ddof) {
+                                                                     const T *gamma, const T *beta, int ddof, unsigned *status,
+                                                                     int use_mailbox) {
     __shared__ float s_exchange[96];
     __shared__ float s_part[2][3];
-    layernorm_cluster_tier<T, kVecs>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange, s_part);
+    __shared__ __align__(8) WelfordMailbox s_mail;
+    layernorm_cluster_tier<T, kVecs>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange, s_part, use_mailbox ? &s_mail : nullptr,
+                                     status);
 }
 template <typename T>
 __global__ void __launch_bounds__(256) layernorm_stream_kernel(const T *in, T *out, long long rows, int cols, float eps,

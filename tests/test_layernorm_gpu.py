@@ -158,6 +158,17 @@ BF16_SHAPES = [(3, 1), (5, 8), (7, 100), (100, 256), (1000, 768), (64, 2048), (9
                (3, 40000)]
 
 
+def test_cluster_tier_mailboxes_and_barriers_agree(cuda, lib, oracle):
+    """The cluster tier exchanges (n, mean, M2) through peer mailboxes + mbarriers (default) or between cluster barriers
+    (stages=2): same values in the same rank order, so the same bits."""
+    for rows, cols in ((5, 65536), (40, 40000), (3, 262144), (37, 8192)):
+        x, g, b = _inputs(oracle, rows, cols)
+        y = _run_f32(cuda, lib, x, 1e-12, g, b, tier=6)
+        assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+        assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, tier=6, stages=2))
+        assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, tier=6, grid_cap=8))   # one cluster, many rows: phases flip
+
+
 @pytest.mark.parametrize("rows,cols", BF16_SHAPES)
 def test_bf16_against_rounded_oracle(cuda, lib, oracle, rows, cols):
     x, g, b = _inputs(oracle, rows, cols)
