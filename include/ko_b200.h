@@ -214,6 +214,50 @@ int ko_gemm_bf16_bf16(int64_t M, int64_t N, int64_t K, const uint16_t *A, const 
 int ko_gemm_tc(int in_fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K,
                const void *A, const void *B, const void *C, void *D, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Probes of the source-level helper templates (kernel_optimization_b200/common/{common,functors}.h
+ * and the Welford combiners of nn_operators/layernorm/layernorm.h).  The reference exposes these
+ * helpers only as device templates; each probe instantiates them in a small kernel and runs them
+ * on DEVICE buffers of the caller, so that a host can check them against its own arithmetic.
+ * ---------------------------------------------------------------------------------------- */
+/* Functors of common/functors.h:13-301 applied elementwise: out[i] = F(a[i] [, b[i] [, c[i]]]).
+ * functor: 0 ReduceMax, 1 ReduceSum, 2 Exp, 3 Rsqrt, 4 Add, 5 Subtract, 6 Multiply, 7 Divide,
+ *          8 MultiplyAdd (a * b + c);
+ * form:    0 scalar functor F<T>; 1 F<AlignedArray<T, 16 / sizeof(T)>> on (vector, vector);
+ *          2 the same on (vector, scalar), binary functors only: vector i is paired with b[i];
+ * dtype:   KO_DTYPE_F32 / F16 / BF16 (16-bit types compute in their own precision, as the
+ *          reference's half specialisations do).  Vector forms need n % (16 / sizeof(T)) == 0. */
+int ko_probe_functor(int functor, int form, int dtype, const void *a, const void *b, const void *c,
+                     void *out, int64_t n, void *stream);
+/* kind 0: WarpReduce<Op, float> (common/common.h:37-46): groups x 32 inputs, out[g] read from lane 0;
+ * kind 1: BlockReduce<Op, float> (:48-65) with `width` threads per block (32..1024, multiple of 32),
+ *         run twice on the same cache: out[g] = first result, out[groups + g] = second, thread 0;
+ * kind 2: to_scalar<Op<float>, float, 4> (:138-149): groups x 4 inputs;
+ * kind 3: WarpReduce<ReduceMax, int32_t> from the identity -numeric_limits<int32_t>::max()
+ *         (:151-178) over the inputs rounded to integers.
+ * op: 0 = ReduceMax, 1 = ReduceSum. */
+int ko_probe_reduce(int kind, int op, const float *in, float *out, int64_t groups, int width,
+                    void *stream);
+/* limits::numeric_limits<float | int32_t | half | __nv_bfloat16>::max() as device code sees them
+ * (common/common.h:151-178); 16-bit values as raw bits. */
+int ko_probe_limits(float *f32_max, int32_t *i32_max, uint16_t *f16_max, uint16_t *bf16_max,
+                    void *stream);
+/* Welford helpers over the rows of in[rows, cols]; out[rows, 3] = (count, mean, M2), M2 = sum of
+ * squared deviations.  kind 0: WelfordUpdate<float> serially (nn_operators/layernorm/layernorm.h:13-23);
+ * 1: 32-element chunks joined by WelfordMerge (:36-50); 2: WelfordUpdate<AlignedArray<float,4>>
+ * (:25-34) + WelfordWarpAllReduce (:80-91), read from lane 31; 3: + WelfordWarpReduce, six-argument
+ * form (:64-78), lane 0; 4: scalar updates + in-place WelfordWarpReduce (:52-62), lane 0;
+ * 5: WelfordBlockAllReduce (:128-143) with `block` threads, read from the last thread;
+ * 6: WelfordBlockReduce (:93-126), thread 0.  Kinds 2, 3, 5, 6 need cols % 4 == 0. */
+int ko_probe_welford(int kind, const float *in, int64_t rows, int32_t cols, float *out, int block,
+                     void *stream);
+/* A whole row operator written only with those helper names, one block of `block` threads per row:
+ * op 0 = softmax (ReduceMax / Subtract / Exp / ReduceSum / Divide, to_scalar, BlockReduce),
+ * op 1 = LayerNorm with population variance (WelfordUpdate, WelfordBlockAllReduce, Rsqrt, Subtract,
+ * Multiply, MultiplyAdd; gamma and beta both NULL or both given).  cols % 4 == 0. */
+int ko_probe_composed_rowop(int op, const float *in, float *out, int64_t rows, int32_t cols,
+                            float eps, const float *gamma, const float *beta, int block, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

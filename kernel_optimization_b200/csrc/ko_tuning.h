@@ -15,7 +15,10 @@ typedef struct ko_row_knobs {
                             5 = resident (LayerNorm only: persistent blocks, packed FP32 math),
                             6 = cluster (one row per thread-block cluster, partials through DSMEM; softmax: stages = 1
                                 turns the shared-memory prefetch of the next row's slice off),
-                            7 = prefetching block (softmax only: row in registers, next row bulk-copied to shared memory) */
+                            7 = prefetching block (softmax only: row in registers, next row bulk-copied to shared memory),
+                            8 = persistent warp (LayerNorm only, rows of at most 1024 columns: one resident grid, each warp
+                                walks its rows with the next row's loads in flight; stages = 1 re-reads gamma / beta per
+                                row instead of holding them in registers) */
     int rows_per_warp;   /* warp / staged tier: independent row slots a warp processes together (a slot is
                             one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows) */
     int block;           /* warp tier: threads per block (<= 256); block / resident tier: threads per row (128..1024) */

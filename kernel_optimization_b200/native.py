@@ -63,6 +63,11 @@ PROTOTYPES = {
     "ko_gemm_f16_f16": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ko_gemm_bf16_bf16": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ko_gemm_tc": (_int, [_int, _int, _int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "ko_probe_functor": (_int, [_int, _int, _int, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "ko_probe_reduce": (_int, [_int, _int, _vp, _vp, _i64, _int, _vp]),
+    "ko_probe_limits": (_int, [_vp, _vp, _vp, _vp, _vp]),
+    "ko_probe_welford": (_int, [_int, _vp, _i64, _i32, _vp, _int, _vp]),
+    "ko_probe_composed_rowop": (_int, [_int, _vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _vp]),
 }
 
 class RowKnobs(C.Structure):

@@ -189,7 +189,11 @@ __device__ __forceinline__ void layernorm_rows_from_registers(const typename Row
                                                               int nvec, int lane, long long row0, long long row_limit,
                                                               typename RowIo<T>::Raw *out_v, int cols, float eps,
                                                               const typename RowIo<T>::Raw *gamma_v,
-                                                              const typename RowIo<T>::Raw *beta_v, int ddof) {
+                                                              const typename RowIo<T>::Raw *beta_v, int ddof,
+                                                              const f32x2 *held_gamma = nullptr,
+                                                              const f32x2 *held_beta = nullptr) {
+    // held_gamma / held_beta (short rows only): this lane's gamma / beta already unpacked to FP32 pairs by a
+    // caller that loops over rows, kVecs * kPer / 2 pairs each; the values are the ones __ldg would fetch
     using Io = RowIo<T>;
     constexpr int kPer = Io::kPerVec, kPairsPerVec = kPer / 2;
     if constexpr (kVecs * kPer <= 32) {  // depends on the row length only, so a row's bits do not depend on kRows
@@ -242,8 +246,14 @@ __device__ __forceinline__ void layernorm_rows_from_registers(const typename Row
             const int v = lane + 32 * j;
             if (v >= nvec) continue;
             f32x2 g2[kPairsPerVec], b2[kPairsPerVec];
-            if (gamma_v) Io::unpack_pairs(__ldg(gamma_v + v), g2);
-            if (beta_v) Io::unpack_pairs(__ldg(beta_v + v), b2);
+            if (held_gamma) {
+#pragma unroll
+                for (int q = 0; q < kPairsPerVec; ++q) g2[q] = held_gamma[j * kPairsPerVec + q];
+            } else if (gamma_v) Io::unpack_pairs(__ldg(gamma_v + v), g2);
+            if (held_beta) {
+#pragma unroll
+                for (int q = 0; q < kPairsPerVec; ++q) b2[q] = held_beta[j * kPairsPerVec + q];
+            } else if (beta_v) Io::unpack_pairs(__ldg(beta_v + v), b2);
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
                 if (row0 + r >= row_limit) continue;
@@ -315,6 +325,64 @@ __device__ __forceinline__ void layernorm_warp_tier(const T *in, T *out, long lo
         layernorm_rows_from_registers<T, kVecs, kRows>(raw, my_vecs, nvec, lane, row0, rows, reinterpret_cast<Raw *>(out),
                                                        cols, eps, reinterpret_cast<const Raw *>(gamma),
                                                        reinterpret_cast<const Raw *>(beta), ddof);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// persistent warp tier (short rows): the grid is sized to what the device holds at once and every
+// warp walks rows warp, warp + W, warp + 2W, ...  The next row's loads are issued before the current
+// row is reduced, so a warp always has a row in flight (a one-row-per-warp grid has nothing in flight
+// for a block slot between one block's last store and its successor's first load), and with
+// kHoldParams gamma and beta are unpacked once per lane instead of once per row.
+// Arithmetic and operation order per row are those of the warp tier: the same bits.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int kVecs, bool kHoldParams>
+__device__ __forceinline__ void layernorm_warp_persistent_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                               const T *gamma, const T *beta, int ddof) {
+    using Io = RowIo<T>;
+    using Raw = typename Io::Raw;
+    constexpr int kPairsPerVec = Io::kPerVec / 2;
+    static_assert(kVecs * Io::kPerVec <= 32, "rows that a lane holds unpacked");
+    const int lane = threadIdx.x & 31;
+    const int nvec = cols / Io::kPerVec;
+    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const Raw *in_v = reinterpret_cast<const Raw *>(in);
+    const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma), *beta_v = reinterpret_cast<const Raw *>(beta);
+    int my_vecs = 0;
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) my_vecs += (lane + 32 * j < nvec) ? 1 : 0;
+
+    Raw next[kVecs];
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) {
+        const int v = lane + 32 * j;
+        next[j] = (row < rows && v < nvec) ? ld_stream(in_v + row * nvec + v) : Raw{};
+    }
+    f32x2 held_g[kHoldParams ? kVecs * kPairsPerVec : 1], held_b[kHoldParams ? kVecs * kPairsPerVec : 1];
+    if constexpr (kHoldParams) {
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = lane + 32 * j;
+            Io::unpack_pairs((gamma_v && v < nvec) ? __ldg(gamma_v + v) : Raw{}, held_g + j * kPairsPerVec);
+            Io::unpack_pairs((beta_v && v < nvec) ? __ldg(beta_v + v) : Raw{}, held_b + j * kPairsPerVec);
+        }
+    }
+    for (; row < rows; row += stride) {
+        Raw cur[1][kVecs];
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) cur[0][j] = next[j];
+        const long long after = row + stride;
+        if (after < rows) {
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const int v = lane + 32 * j;
+                if (v < nvec) next[j] = ld_stream(in_v + after * nvec + v);
+            }
+        }
+        layernorm_rows_from_registers<T, kVecs, 1>(cur, my_vecs, nvec, lane, row, rows, reinterpret_cast<Raw *>(out), cols, eps,
+                                                   gamma_v, beta_v, ddof, (kHoldParams && gamma_v) ? held_g : nullptr,
+                                                   (kHoldParams && beta_v) ? held_b : nullptr);
     }
 }
 
@@ -688,6 +756,13 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const T *in, T *out
     grid_dependency_wait();    // nothing is read before the previous kernel's writes are visible
     layernorm_warp_tier<T, kVecs, kRows>(in, out, rows, cols, eps, gamma, beta, ddof);
 }
+template <typename T, int kVecs, bool kHoldParams>
+__global__ void __launch_bounds__(256) layernorm_warp_persistent_kernel(const T *in, T *out, long long rows, int cols, float eps,
+                                                                        const T *gamma, const T *beta, int ddof) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    layernorm_warp_persistent_tier<T, kVecs, kHoldParams>(in, out, rows, cols, eps, gamma, beta, ddof);
+}
 template <typename T, int kVecs, int kRows, int kConsumerWarps>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * 32)
 layernorm_staged_kernel(const T *in, T *out, long long rows, int cols, float eps, const T *gamma, const T *beta, int ddof,
@@ -758,6 +833,88 @@ struct WelfordMerge {
         count_a = count_ab;
     }
 };
+
+// One independent stream per vector slot (the reference's vector form, layernorm.h:25-34).
+template <typename T, int N>
+struct WelfordUpdate<AlignedArray<T, N>> {
+    __device__ __forceinline__ void operator()(AlignedArray<T, N> &count, AlignedArray<T, N> &mean, AlignedArray<T, N> &m2,
+                                               const AlignedArray<T, N> &new_value) const {
+#pragma unroll
+        for (int i = 0; i < N; ++i) WelfordUpdate<T>()(count[i], mean[i], m2[i], new_value[i]);
+    }
+};
+
+// The combiners below keep the reference's names, argument order and shared-memory footprint
+// (layernorm.h:52-62, :64-78, :80-91, :93-126, :128-143).  Unlike the reference's, they
+//   * return M2 as the SUM of squared deviations (divide by count - ddof once, after the last
+//     combine; the reference's merge divides at every level);
+//   * are correct for every block size that is a multiple of 32 (the reference's block forms fold
+//     stale lanes in unless blockDim.x == 1024);
+//   * leave the warp result in every lane and the block result in every thread, so the *Reduce
+//     forms satisfy their "valid in lane 0 / thread 0" contract with room to spare.
+
+// In-place combine of the 32 lanes' triples.
+template <typename T>
+__device__ __forceinline__ void WelfordWarpReduce(T &result_count, T &result_mean, T &result_m2) {
+#pragma unroll
+    for (int mask = 16; mask > 0; mask >>= 1) {
+        const T other_count = __shfl_xor_sync(0xffffffffu, result_count, mask);
+        const T other_mean = __shfl_xor_sync(0xffffffffu, result_mean, mask);
+        const T other_m2 = __shfl_xor_sync(0xffffffffu, result_m2, mask);
+        WelfordMerge<T>()(result_count, result_mean, result_m2, other_count, other_mean, other_m2);
+    }
+    // merge(a, b) and merge(b, a) may differ in the last bit: every lane takes lane 0's value
+    result_mean = __shfl_sync(0xffffffffu, result_mean, 0);
+    result_m2 = __shfl_sync(0xffffffffu, result_m2, 0);
+}
+
+// Folds a lane's N per-slot triples into one, then combines the lanes.
+template <typename T, int N>
+__device__ __forceinline__ void WelfordWarpReduce(const AlignedArray<T, N> &count, const AlignedArray<T, N> &mean,
+                                                  const AlignedArray<T, N> &m2, T &result_count, T &result_mean,
+                                                  T &result_m2) {
+    result_count = count[0];
+    result_mean = mean[0];
+    result_m2 = m2[0];
+#pragma unroll
+    for (int i = 1; i < N; ++i) WelfordMerge<T>()(result_count, result_mean, result_m2, count[i], mean[i], m2[i]);
+    WelfordWarpReduce<T>(result_count, result_mean, result_m2);
+}
+
+template <typename T, int N>
+__device__ __forceinline__ void WelfordWarpAllReduce(const AlignedArray<T, N> &count, const AlignedArray<T, N> &mean,
+                                                     const AlignedArray<T, N> &m2, T &result_count, T &result_mean,
+                                                     T &result_m2) {
+    WelfordWarpReduce<T, N>(count, mean, m2, result_count, result_mean, result_m2);  // already in every lane
+}
+
+// s_reduce_cache: 3 * 32 elements of T.  Every thread of the block must call it.
+template <typename T, int N>
+__device__ __forceinline__ void WelfordBlockAllReduce(const AlignedArray<T, N> &count, const AlignedArray<T, N> &mean,
+                                                      const AlignedArray<T, N> &m2, T &result_count, T &result_mean,
+                                                      T &result_m2, T *s_reduce_cache) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    WelfordWarpReduce<T, N>(count, mean, m2, result_count, result_mean, result_m2);
+    __syncthreads();  // the cache may still be read by a previous call
+    if (lane == 0) {
+        s_reduce_cache[warp] = result_count;
+        s_reduce_cache[32 + warp] = result_mean;
+        s_reduce_cache[64 + warp] = result_m2;
+    }
+    __syncthreads();
+    // every warp combines the per-warp triples; slots beyond the warp count are empty triples
+    result_count = lane < nwarps ? s_reduce_cache[lane] : T(0);
+    result_mean = lane < nwarps ? s_reduce_cache[32 + lane] : T(0);
+    result_m2 = lane < nwarps ? s_reduce_cache[64 + lane] : T(0);
+    WelfordWarpReduce<T>(result_count, result_mean, result_m2);
+}
+
+template <typename T, int N>
+__device__ __forceinline__ void WelfordBlockReduce(const AlignedArray<T, N> &count, const AlignedArray<T, N> &mean,
+                                                   const AlignedArray<T, N> &m2, T &result_count, T &result_mean,
+                                                   T &result_m2, T *s_reduce_cache) {
+    WelfordBlockAllReduce<T, N>(count, mean, m2, result_count, result_mean, result_m2, s_reduce_cache);
+}
 
 // ---------------------------------------------------------------------------------------------
 // source-level drop-in for the reference's launch syntax (compile-time shapes)

@@ -315,6 +315,45 @@ void ko_oracle_layernorm_f32(const float *in, float *out, int64_t rows, int32_t 
     }
 }
 
+/* Row statistics alone, as (count, mean, M2) with M2 the sum of squared deviations: what the
+ * Welford helpers of layernorm.h:13-143 are meant to deliver before the single division.
+ * stats_f32: FP32 in the warp kernel's order (per-slot streams :25-34, slot fold :64-75, tree :52-62,
+ * merge without the per-level division); stats_f64: two-pass float64. */
+void ko_oracle_welford_stats_f32(const float *in, float *out, int64_t rows, int32_t cols) {
+    const int vec = (cols % 4 == 0) ? 4 : 1;
+    const int nvec = cols / vec;
+    for (int64_t r = 0; r < rows; ++r) {
+        const float *x = in + r * (int64_t)cols;
+        welford_t lane[32];
+        for (int l = 0; l < 32; ++l) {
+            welford_t slot[4];
+            memset(slot, 0, sizeof slot);
+            for (int v = l; v < nvec; v += 32)
+                for (int s = 0; s < vec; ++s) welford_update(&slot[s], x[v * vec + s]);
+            lane[l] = slot[0];
+            for (int s = 1; s < vec; ++s) welford_merge(&lane[l], &slot[s], 0);
+        }
+        for (int off = 16; off > 0; off >>= 1)
+            for (int i = 0; i < off; ++i) welford_merge(&lane[i], &lane[i + off], 0);
+        out[r * 3 + 0] = lane[0].n;
+        out[r * 3 + 1] = lane[0].mean;
+        out[r * 3 + 2] = lane[0].m2;
+    }
+}
+
+void ko_oracle_welford_stats_f64(const float *in, double *out, int64_t rows, int32_t cols) {
+    for (int64_t r = 0; r < rows; ++r) {
+        const float *x = in + r * (int64_t)cols;
+        double sum = 0.0, m2 = 0.0;
+        for (int c = 0; c < cols; ++c) sum += (double)x[c];
+        const double mean = sum / (double)cols;
+        for (int c = 0; c < cols; ++c) m2 += ((double)x[c] - mean) * ((double)x[c] - mean);
+        out[r * 3 + 0] = (double)cols;
+        out[r * 3 + 1] = mean;
+        out[r * 3 + 2] = m2;
+    }
+}
+
 /* ------------------------------------------ GEMM ----------------------------------------- */
 /* Row-major SGEMM; every output accumulates a[i,k]*b[k,j] with one fused multiply-add per k in
  * ascending k, starting from zero (simt_gemm.h:202-222: `accum += a * b` compiles to FFMA),

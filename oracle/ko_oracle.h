@@ -67,6 +67,11 @@ void ko_oracle_layernorm_f32(const float *in, float *out, int64_t rows, int32_t 
                              const float *gamma, const float *beta, int ddof, int literal,
                              int threads);
 
+/* (count, mean, M2 = sum of squared deviations) per row, out[rows, 3]: FP32 in the warp kernel's
+ * update / merge order without the per-level division (layernorm.h:13-91), and two-pass float64 */
+void ko_oracle_welford_stats_f32(const float *in, float *out, int64_t rows, int32_t cols);
+void ko_oracle_welford_stats_f64(const float *in, double *out, int64_t rows, int32_t cols);
+
 /* ---- GEMM ---- */
 /* D[M,N] = A[M,K] B[K,N] (+ C), all row-major FP32; FP32 fused multiply-add in ascending k
  * (simt_gemm.h:202-222, epilogue :325-373; commented CPU loop gemm/main.cu:162-167) */

@@ -48,6 +48,8 @@ def _load() -> C.CDLL:
         "ko_oracle_softmax_f32": (None, [f32p, f32p, i64, i32, ci, ci]),
         "ko_oracle_layernorm_f64": (None, [f32p, f64p, i64, i32, f64, f32p, f32p, ci]),
         "ko_oracle_layernorm_f32": (None, [f32p, f32p, i64, i32, f32, f32p, f32p, ci, ci, ci]),
+        "ko_oracle_welford_stats_f32": (None, [f32p, f32p, i64, i32]),
+        "ko_oracle_welford_stats_f64": (None, [f32p, f64p, i64, i32]),
         "ko_oracle_sgemm_f32": (None, [i64, i64, i64, f32p, f32p, f32p, f32p, ci]),
         "ko_oracle_sgemm_f64": (None, [i64, i64, i64, f32p, f32p, f32p, f64p, ci]),
         "ko_oracle_gemm_tn_f32": (None, [i64, i64, i64, f32p, f32p, f32p, f32p, ci]),
@@ -175,6 +177,22 @@ def layernorm_f32(x, eps: float, gamma=None, beta=None, ddof: int = 0, literal: 
     out = np.empty(x.shape, dtype=np.float32)
     _lib.ko_oracle_layernorm_f32(_p(x, C.c_float), _p(out, C.c_float), rows, cols, eps,
                                  _p(g, C.c_float), _p(b, C.c_float), ddof, int(literal), threads)
+    return out
+
+
+def welford_stats_f32(x) -> np.ndarray:
+    """[rows, 3] = (count, mean, M2) in FP32, the reference warp kernel's update/merge order."""
+    x = _f32(x)
+    out = np.empty((x.shape[0], 3), dtype=np.float32)
+    _lib.ko_oracle_welford_stats_f32(_p(x, C.c_float), _p(out, C.c_float), x.shape[0], x.shape[1])
+    return out
+
+
+def welford_stats_f64(x) -> np.ndarray:
+    """[rows, 3] = (count, mean, M2) in float64, two passes."""
+    x = _f32(x)
+    out = np.empty((x.shape[0], 3), dtype=np.float64)
+    _lib.ko_oracle_welford_stats_f64(_p(x, C.c_float), _p(out, C.c_double), x.shape[0], x.shape[1])
     return out
 
 

@@ -85,6 +85,26 @@ def test_layernorm_constant_rows(oracle):
     assert np.array_equal(oracle.layernorm_f64(x, 1e-12), np.zeros_like(x, dtype=np.float64))
 
 
+@pytest.mark.parametrize("rows,cols", [(3, 4), (17, 128), (9, 768), (5, 1000), (2, 4099)])
+def test_welford_statistics_port_vs_float64(oracle, rows, cols):
+    """(count, mean, M2) of the reference-order FP32 restatement (update per vector slot, slot fold, shuffle tree,
+    merge without the per-level division) against the two-pass float64 statistics and numpy."""
+    x = oracle.fill_normal((rows, cols), 1, 5, 0.75, 2.0)
+    want = oracle.welford_stats_f64(x)
+    x64 = x.astype(np.float64)
+    assert np.array_equal(want[:, 0], np.full(rows, float(cols)))
+    assert np.allclose(want[:, 1], x64.mean(axis=1), rtol=0, atol=1e-13)
+    assert np.allclose(want[:, 2], ((x64 - x64.mean(axis=1, keepdims=True)) ** 2).sum(axis=1), rtol=1e-12)
+    port = oracle.welford_stats_f32(x)
+    assert np.array_equal(port[:, 0], want[:, 0].astype(np.float32))
+    assert np.abs(port[:, 1] - want[:, 1]).max() <= 1e-6
+    assert (np.abs(port[:, 2] - want[:, 2]) / want[:, 2]).max() <= 1e-5
+    # the same triple is what the port's LayerNorm divides once: var = M2 / cols
+    y = oracle.layernorm_f32(x, 0.0)
+    rstd = 1.0 / np.sqrt(port[:, 2].astype(np.float64) / cols)
+    assert np.abs(y - (x64 - port[:, 1:2]) * rstd[:, None]).max() <= 2e-6
+
+
 def test_sgemm_port_is_bit_identical_to_reference_kernel(oracle, golden):
     a, b = oracle.fill_uniform((64, 64), 2, 0), oracle.fill_uniform((64, 64), 2, 1)
     assert np.array_equal(oracle.sgemm_f32(a, b), golden["sgemm_64x64x64"])
