@@ -42,9 +42,16 @@ STEP_BYTES = SOFTMAX_BYTES + LN_BYTES
 METRIC, UNIT = "softmax+layernorm HBM throughput (BERT-Base row ops, FP32)", "GB/s"
 WORKLOAD = ("bert_base_row_ops: softmax f32 [196608,128] N(0,4) seed 0 + layernorm f32 [16384,768] affine eps 1e-12 "
             "seed 1, per GPU; rows sharded across GPUs, no collective")
-# DRAM bytes per launch of the softmax kernel on this workload from the ncu capture summarised in
-# profiles/softmax_warp_kernel_196608x128.txt (dram__bytes_read.sum + dram__bytes_write.sum)
-SOFTMAX_NCU_TRAFFIC_BYTES = 145_612_800
+DATA_NOTE = "synthetic (seeded Philox4x32-10 fills of the benchmark shapes and distributions; no dataset involved)"
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised in
+# profiles/softmax_warp_kernel_196608x128.txt and profiles/layernorm_warp_kernel_16384x768.txt.  "isolated": one
+# launch with the caches flushed before it, so the part of the output still dirty in the 126 MB L2 when the kernel ends
+# is missing from the write count; "steady": launches back to back over rotating buffer sets with the caches left
+# alone, where the write-back of the previous launch's output falls into this launch (None until captured).
+NCU_TRAFFIC = {
+    "softmax": {"isolated": 145_612_800, "steady": None},
+    "layernorm": {"isolated": 56_400_000, "steady": None},
+}
 
 
 def measured_peaks():
@@ -134,7 +141,8 @@ def cpu_sample(oracle, fraction: int):
     xl = oracle.fill_normal((rl, LN_COLS), 1, 0, 0.0, 1.0)
     g, b = oracle.fill_uniform((LN_COLS,), 1, 1, 0.5, 1.5), oracle.fill_normal((LN_COLS,), 1, 2, 0.0, 0.1)
     sample_bytes = 2 * rs * SOFTMAX_COLS * 4 + 2 * rl * LN_COLS * 4 + 2 * LN_COLS * 4
-    return (xs, xl, g, b), sample_bytes, f"first 1/{fraction} of the rows of both operators ({rs} + {rl} rows), FP32 ports, every step"
+    part = "all rows" if fraction == 1 else f"the first 1/{fraction} of the rows"
+    return (xs, xl, g, b), sample_bytes, f"{part} of both operators ({rs} + {rl} rows), FP32 ports, every step"
 
 
 def run_reference_arm(args):
@@ -144,7 +152,8 @@ def run_reference_arm(args):
     from oracle import ko_oracle as oracle
 
     cores = host_cores()
-    sample, sample_bytes, what = cpu_sample(oracle, 8)
+    sample, sample_bytes, what = cpu_sample(oracle, 1)  # every row of both operators: the GPU arm's per-GPU workload
+    assert sample_bytes == STEP_BYTES
     for _ in range(max(args.warmup, 1)):
         cpu_port_step(oracle, *sample, cores)
     t0 = time.perf_counter()
@@ -154,15 +163,15 @@ def run_reference_arm(args):
     gbs = sample_bytes * args.steps / elapsed / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3 * (STEP_BYTES / sample_bytes),
+        "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic (seeded Philox4x32-10 fills of the benchmark shapes)",
+        "data": DATA_NOTE,
         "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": what},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference project has no CPU implementation; this is the oracle's FP32 restatement of its kernels "
-                "(softmax.h:32-58, layernorm.h:13-50/:184-198 with the merge defect removed) on all host threads; "
-                "ms_per_step is scaled from the sample to the full per-GPU workload",
+                "(softmax.h:32-58, layernorm.h:13-50/:184-198 with the merge defect removed) on all host threads, "
+                "one GPU's worth of rows per step whatever --gpus says (rank 0 only)",
     }
     emit(line)
 
@@ -171,40 +180,124 @@ def run_reference_arm(args):
 # GPU arm
 # --------------------------------------------------------------------------------------------------
 E2E_CHUNKS = 8
+REPEAT_BATCHES = 10  # the timed batch of --steps steps is repeated this often; value = the median batch
+
+
+class Rig:
+    """One rank: its device, the process group and the timing rules (barrier + synchronize on both sides of a timed
+    region, CUDA events on the launch stream, max over ranks)."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        from kernel_optimization_b200 import native, sharding
+
+        self.torch, self.dist, self.sharding, self.native = torch, dist, sharding, native
+        self.lib = native.lib()  # raises when the CUDA library has not been built: there is no fallback
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus and self.world == 1 and args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE is 1)")
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.hbm_peak, self.tc_peak, self.peak_kind = measured_peaks()
+
+    def stream(self):
+        return self.torch.cuda.current_stream().cuda_stream
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, ms: float) -> float:
+        return self.sharding.max_over_ranks(ms, self.dev)
+
+    def timed(self, fn, iters, warm):
+        """ms per iteration of fn(i): `warm` untimed calls, then exactly `iters` calls between two events."""
+        torch = self.torch
+        for i in range(warm):
+            fn(i)
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i)
+        e1.record()
+        self.barrier()
+        return self.max_over_ranks(e0.elapsed_time(e1)) / iters
+
+    def per_launch(self, fn, iters, warm):
+        """(median, min) microseconds of single launches: an event between every two calls (which also keeps
+        consecutive launches from overlapping, unlike the back-to-back figure), max over ranks of each statistic."""
+        torch = self.torch
+        for i in range(warm):
+            fn(i)
+        self.barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+        ev[0].record()
+        for i in range(iters):
+            fn(i)
+            ev[i + 1].record()
+        self.barrier()
+        us = sorted(ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(iters))
+        return self.max_over_ranks(statistics.median(us)), self.max_over_ranks(us[0])
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def measure_link_ceiling(rig, bytes_each_way: int, iters: int):
+    """Plain pinned-memory copies of `bytes_each_way` host->device and device->host at the same time on two streams,
+    every rank at once; GB/s summed over both directions and all ranks (wall clock between barriers, max over ranks)."""
+    torch = rig.torch
+    n = bytes_each_way
+    h_in, h_out = torch.empty(n, dtype=torch.uint8).pin_memory(), torch.empty(n, dtype=torch.uint8).pin_memory()
+    d_in, d_out = torch.empty(n, dtype=torch.uint8, device=rig.dev), torch.empty(n, dtype=torch.uint8, device=rig.dev)
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def go(h2d: bool, d2h: bool):
+        def once():
+            if h2d:
+                with torch.cuda.stream(s_in):
+                    d_in.copy_(h_in, non_blocking=True)
+            if d2h:
+                with torch.cuda.stream(s_out):
+                    h_out.copy_(d_out, non_blocking=True)
+        once()
+        rig.barrier()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            once()
+        torch.cuda.synchronize()
+        dt = rig.max_over_ranks((time.perf_counter() - t0) * 1e3) / iters  # ms
+        rig.barrier()
+        return n * ((1 if h2d else 0) + (1 if d2h else 0)) * rig.world / (dt * 1e-3) / 1e9
+
+    out = {"h2d_gbs": go(True, False), "d2h_gbs": go(False, True), "both_directions_gbs": go(True, True),
+           "bytes_each_way_per_rank": n, "ranks": rig.world,
+           "how": "one pinned cudaMemcpyAsync per direction on its own stream, all ranks at once, no kernel"}
+    del h_in, h_out, d_in, d_out
+    return out
 
 
 def run_gpu_arm(args):
     import torch
-    import torch.distributed as dist
 
     import kernel_optimization_b200 as ko
     from kernel_optimization_b200 import native, sharding
 
-    lib = native.lib()  # raises when the CUDA library has not been built: there is no fallback
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE is 1)")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    def stream():
-        return torch.cuda.current_stream().cuda_stream
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(ms: float) -> float:
-        return sharding.max_over_ranks(ms, dev)
+    rig = Rig(args)
+    lib, world, rank, local_rank, dev = rig.lib, rig.world, rig.rank, rig.local_rank, rig.dev
+    stream, barrier, timed = rig.stream, rig.barrier, rig.timed
+    hbm_peak, tc_peak, peak_kind = rig.hbm_peak, rig.tc_peak, rig.peak_kind
 
     # ---- inputs: this rank's row shard of the global tensors, seeded by global element index
-    hbm_peak, tc_peak, peak_kind = measured_peaks()
     sm_off = sharding.weak_scaled_rows(SOFTMAX_ROWS, SOFTMAX_COLS, rank, world).elem_offset
     ln_off = sharding.weak_scaled_rows(LN_ROWS, LN_COLS, rank, world).elem_offset
     xs_host = ko.fill_normal((SOFTMAX_ROWS, SOFTMAX_COLS), 0, 0, 0.0, 2.0, elem_offset=sm_off)
@@ -232,28 +325,24 @@ def run_gpu_arm(args):
         softmax_launch(i)
         layernorm_launch(i)
 
-    def timed(fn, iters, warm):
-        """ms per iteration on the device: barrier + synchronize on both sides, events on the launch stream."""
-        for i in range(warm):
-            fn(i)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(iters):
-            fn(i)
-        e1.record()
-        barrier()
-        return max_over_ranks(e0.elapsed_time(e1)) / iters
-
-    # ---- headline: K steps of (softmax, layernorm)
+    # ---- headline: K steps of (softmax, layernorm), the batch repeated; the median batch is the reported one
     with ClockSampler(local_rank) as clocks:
-        ms_per_step = timed(step, args.steps, args.warmup)
+        batches = [timed(step, args.steps, args.warmup)]
+        batches += [timed(step, args.steps, 0) for _ in range(REPEAT_BATCHES - 1)]
         # per-kernel durations for the roofline, same buffers, same stream
-        ms_softmax = timed(softmax_launch, args.steps, args.warmup)
-        ms_layernorm = timed(layernorm_launch, args.steps, args.warmup)
+        sm_batches = [timed(softmax_launch, args.steps, args.warmup if b == 0 else 0) for b in range(5)]
+        ln_batches = [timed(layernorm_launch, args.steps, args.warmup if b == 0 else 0) for b in range(5)]
+        sm_med_us, sm_min_us = rig.per_launch(softmax_launch, max(args.steps, 20), 3)
+        ln_med_us, ln_min_us = rig.per_launch(layernorm_launch, max(args.steps, 20), 3)
+    ms_per_step = statistics.median(batches)
+    ms_softmax, ms_layernorm = statistics.median(sm_batches), statistics.median(ln_batches)
     value = STEP_BYTES * world / (ms_per_step * 1e-3) / 1e9
     softmax_gbs = SOFTMAX_BYTES / (ms_softmax * 1e-3) / 1e9
     layernorm_gbs = LN_BYTES / (ms_layernorm * 1e-3) / 1e9
+    repeat = {"batches": len(batches), "steps_per_batch": args.steps, "ms_per_step": batches, "median": ms_per_step,
+              "min": min(batches), "max": max(batches), "spread": (max(batches) - min(batches)) / ms_per_step,
+              "note": "every batch is exactly --steps steps between two events with a barrier + synchronize on both sides; "
+                      "value and ms_per_step are the median batch"}
 
     # ---- parity spot check of what was just timed (rank 0; the oracle is only the checker here)
     parity = None
@@ -285,6 +374,12 @@ def run_gpu_arm(args):
            "d2h_bytes_per_step": h2d, "ms_per_step": ms_e2e, "steps": e2e_steps,
            "path": f"ko_softmax_f32_host + ko_layernorm_f32_host, {args.e2e_chunks} chunks each: pinned host -> device -> kernel -> pinned host, "
                    "copies of neighbouring chunks overlap (PCIe is full duplex); every step ends with all results on the host"}
+    # the host link itself, all ranks at once: the step's bytes as one large pinned copy per direction on two
+    # streams, no kernel -- what any pipeline through this host's PCIe fabric could reach at this rank count
+    link = measure_link_ceiling(rig, h2d, 5)
+    e2e["link_ceiling_gbs"] = link["both_directions_gbs"]
+    e2e["of_link_ceiling"] = e2e["value"] / link["both_directions_gbs"]
+    e2e["link"] = link
     if rank == 0:
         from oracle import ko_oracle as oracle
 
@@ -369,27 +464,52 @@ def run_gpu_arm(args):
         cpu_baseline = {"value": sample_bytes / best / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
                         "sample": f"the full per-GPU workload (all rows of both operators), FP32 ports, best of {reps} passes"}
 
+    # ---- benchmark config 5 (the 1/2/4/8-GPU sweep's own shapes, strong scaling) under the same clock
+    scaled = None
+    if not args.skip_scaled:
+        torch.cuda.empty_cache()
+        c5_ops, c5_parity = scaled_ops(rig, max(3, min(args.steps, 10)), 3)
+        scaled = {"workload": SCALED_WORKLOAD, "scaling": "strong (totals fixed, every rank takes 1/N)", "ops": c5_ops,
+                  "parity_worst_over_ranks": c5_parity,
+                  "l2": "every per-GPU operand is larger than the 126 MB L2"}
+
     if rank == 0:
+        def roofline_of(kernel, gbs, ms, nbytes, traffic):
+            return {"bound": "hbm", "kernel": kernel, "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                    "traffic": traffic["steady"] if traffic["steady"] is not None else traffic["isolated"],
+                    "traffic_kind": ("steady state: back-to-back launches over rotating buffer sets, caches left alone"
+                                     if traffic["steady"] is not None else
+                                     "isolated launch, caches flushed before it: part of the output is still dirty in L2 when the "
+                                     "kernel ends, so this is below the algorithmic bytes; it shows that nothing is read twice"),
+                    "traffic_isolated_launch": traffic["isolated"], "peak_source": peak_kind,
+                    "algorithmic_bytes_per_launch": nbytes, "us_per_launch": ms * 1e3}
+
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic (seeded Philox4x32-10 fills of the benchmark shapes and distributions; no dataset involved)",
-            "config": {"workload": WORKLOAD, "rows_per_gpu": {"softmax": SOFTMAX_ROWS, "layernorm": LN_ROWS},
-                       "l2": f"inputs and outputs rotate over {n_sm_sets} (softmax) / {n_ln_sets} (layernorm) buffer sets "
-                             f"({n_sm_sets * SOFTMAX_BYTES / 1e6:.0f} / {n_ln_sets * LN_BYTES / 1e6:.0f} MB of distinct addresses "
-                             "against a 126 MB L2), so every launch reads from HBM",
-                       "parallelism": f"rows x{world}, no collective"},
-            "roofline": {"bound": "hbm", "kernel": "softmax_warp_kernel (softmax f32 [196608,128])", "achieved": softmax_gbs,
-                         "peak": hbm_peak, "unit": "GB/s", "frac": softmax_gbs / hbm_peak, "traffic": SOFTMAX_NCU_TRAFFIC_BYTES,
-                         "peak_source": peak_kind, "algorithmic_bytes_per_launch": SOFTMAX_BYTES, "us_per_launch": ms_softmax * 1e3},
-            "ops": {"softmax": {"gbs": softmax_gbs, "us": ms_softmax * 1e3, "of_peak": softmax_gbs / hbm_peak, "of_nominal_8TBs": softmax_gbs / 8000.0},
-                    "layernorm": {"gbs": layernorm_gbs, "us": ms_layernorm * 1e3, "of_peak": layernorm_gbs / hbm_peak, "of_nominal_8TBs": layernorm_gbs / 8000.0}},
+            "data": DATA_NOTE,
+            "config": {"workload": WORKLOAD},
+            "run": {"rows_per_gpu": {"softmax": SOFTMAX_ROWS, "layernorm": LN_ROWS},
+                    "l2": f"inputs and outputs rotate over {n_sm_sets} (softmax) / {n_ln_sets} (layernorm) buffer sets "
+                          f"({n_sm_sets * SOFTMAX_BYTES / 1e6:.0f} / {n_ln_sets * LN_BYTES / 1e6:.0f} MB of distinct addresses "
+                          "against a 126 MB L2), so every launch reads from HBM",
+                    "parallelism": f"rows x{world}, no collective"},
+            "repeat": repeat,
+            "roofline": roofline_of("softmax_warp_kernel (softmax f32 [196608,128])", softmax_gbs, ms_softmax, SOFTMAX_BYTES,
+                                    NCU_TRAFFIC["softmax"]),
+            "roofline_layernorm": roofline_of("layernorm_warp_kernel (layernorm f32 [16384,768])", layernorm_gbs, ms_layernorm,
+                                              LN_BYTES, NCU_TRAFFIC["layernorm"]),
+            "ops": {"softmax": {"gbs": softmax_gbs, "us": ms_softmax * 1e3, "of_peak": softmax_gbs / hbm_peak, "of_nominal_8TBs": softmax_gbs / 8000.0,
+                                "us_per_launch_median": sm_med_us, "us_per_launch_min": sm_min_us},
+                    "layernorm": {"gbs": layernorm_gbs, "us": ms_layernorm * 1e3, "of_peak": layernorm_gbs / hbm_peak, "of_nominal_8TBs": layernorm_gbs / 8000.0,
+                                  "us_per_launch_median": ln_med_us, "us_per_launch_min": ln_min_us},
+                    "note": "us / gbs: median of 5 batches of --steps launches back to back (consecutive launches overlap their "
+                            "ramps through programmatic dependent launch); us_per_launch_*: single launches with an event between them"},
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks.summary(),
-            "parity": parity, "gemm": gemm, "reference_kernels_on_b200": ref_rows,
+            "parity": parity, "gemm": gemm, "scaled": scaled, "reference_kernels_on_b200": ref_rows,
         }
         emit(line)
-    if world > 1:
-        dist.destroy_process_group()
+    rig.close()
 
 
 # --------------------------------------------------------------------------------------------------
@@ -400,44 +520,20 @@ C5_LN_ROWS, C5_LN_COLS = 262144, 4096
 C5_M, C5_N, C5_K = 65536, 8192, 8192
 
 
-def run_scaled(args):
-    """softmax FP32 [8x196608, 512] causal -1e4, LayerNorm BF16 [262144, 4096], BF16 GEMM 65536 x 8192 x 8192
-    (B replicated by one NCCL broadcast, untimed), seed 4; rows / M-blocks sharded over the ranks."""
-    import torch
-    import torch.distributed as dist
-
+def scaled_ops(rig, steps, warmup):
+    """Benchmark config 5 on this rank's shard: softmax FP32 [8x196608, 512] causal -1e4, LayerNorm BF16 [262144, 4096],
+    BF16 GEMM 65536 x 8192 x 8192 (B replicated by one NCCL broadcast, outside the timed region), seed 4; the totals
+    are fixed and rows / M-blocks are sharded over the ranks (strong scaling).  Every rank generates only its own shard.
+    Returns (per-operator results, parity worst over ranks)."""
     import kernel_optimization_b200 as ko
-    from kernel_optimization_b200 import native, sharding
 
-    lib = native.lib()
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    hbm_peak, tc_peak, peak_kind = measured_peaks()
-
-    def stream():
-        return torch.cuda.current_stream().cuda_stream
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    torch, dist, sharding, native, lib = rig.torch, rig.dist, rig.sharding, rig.native, rig.lib
+    world, rank, dev = rig.world, rig.rank, rig.dev
+    hbm_peak, tc_peak = rig.hbm_peak, rig.tc_peak
+    stream, barrier = rig.stream, rig.barrier
 
     def timed(fn, iters, warm):
-        for _ in range(warm):
-            fn()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        barrier()
-        return sharding.max_over_ranks(e0.elapsed_time(e1), dev) / iters
+        return rig.timed(lambda _i: fn(), iters, warm)
 
     from oracle import ko_oracle as oracle  # checker for the sampled rows below
 
@@ -451,7 +547,7 @@ def run_scaled(args):
     xd = torch.from_numpy(x).to(dev)
     yd = torch.empty_like(xd)
     ms = timed(lambda: native.check(lib.ko_softmax_f32(xd.data_ptr(), yd.data_ptr(), sh.rows, sh.cols, stream()), "softmax"),
-               args.steps, args.warmup)
+               steps, warmup)
     total = 2.0 * C5_SOFTMAX_ROWS * C5_SOFTMAX_COLS * 4
     out["softmax_f32_causal"] = {"gbs": total / (ms * 1e-3) / 1e9, "ms": ms, "of_peak_per_gpu": total / world / (ms * 1e-3) / 1e9 / hbm_peak,
                                  "bytes": total, "rows_per_gpu": sh.rows}
@@ -468,7 +564,7 @@ def run_scaled(args):
     xd, gd, bd = to_dev(xb), to_dev(gb), to_dev(bb)
     yd = torch.empty_like(xd)
     ms = timed(lambda: native.check(lib.ko_layernorm_bf16(xd.data_ptr(), yd.data_ptr(), sh.rows, sh.cols, LN_EPS, gd.data_ptr(),
-                                                          bd.data_ptr(), 0, stream()), "layernorm"), args.steps, args.warmup)
+                                                          bd.data_ptr(), 0, stream()), "layernorm"), steps, warmup)
     total = 2.0 * C5_LN_ROWS * C5_LN_COLS * 2
     out["layernorm_bf16"] = {"gbs": total / (ms * 1e-3) / 1e9, "ms": ms, "of_peak_per_gpu": total / world / (ms * 1e-3) / 1e9 / hbm_peak,
                              "bytes": total, "rows_per_gpu": sh.rows}
@@ -483,13 +579,16 @@ def run_scaled(args):
     ad = to_dev(ab)
     bh = ko.fill_uniform((C5_N, C5_K), 4, 5, dtype=2) if rank == 0 else None
     bd = to_dev(bh) if rank == 0 else torch.empty((C5_N, C5_K), dtype=torch.int16, device=dev)
+    sharding.replicate_from_rank0(bd)  # the first broadcast also brings the communicator's channels up: not timed
     barrier()
-    t0 = time.perf_counter()
-    sharding.replicate_from_rank0(bd)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    sharding.replicate_from_rank0(bd)  # same bytes again, warm: the NVLink figure
+    e1.record()
     barrier()
-    bcast_ms = (time.perf_counter() - t0) * 1e3
+    bcast_ms = rig.max_over_ranks(e0.elapsed_time(e1)) if world > 1 else 0.0
     dd = torch.empty((sh.rows, C5_N), device=dev)
-    gsteps = max(2, min(args.steps, 5))
+    gsteps = max(2, min(steps, 5))
     ms = timed(lambda: native.check(lib.ko_gemm_bf16_f32(sh.rows, C5_N, C5_K, ad.data_ptr(), bd.data_ptr(), None, dd.data_ptr(), stream()),
                                     "gemm"), gsteps, 1)
     flops = 2.0 * C5_M * C5_N * C5_K
@@ -497,31 +596,45 @@ def run_scaled(args):
     ms_c = timed(lambda: torch.mm(a_t, b_t.t(), out_dtype=torch.float32), gsteps, 1)
     out["gemm_bf16_f32"] = {"tflops": flops / (ms * 1e-3) / 1e12, "ms": ms, "cublas_tflops": flops / (ms_c * 1e-3) / 1e12, "vs_cublas": ms_c / ms,
                             "of_measured_bf16_peak_per_gpu": flops / world / (ms * 1e-3) / 1e12 / tc_peak, "flops": flops,
-                            "b_broadcast_ms": bcast_ms, "b_bytes": C5_N * C5_K * 2, "m_per_gpu": sh.rows}
+                            "b_broadcast_ms": bcast_ms, "b_bytes": C5_N * C5_K * 2, "m_per_gpu": sh.rows,
+                            "b_broadcast_gbs": (C5_N * C5_K * 2 / (bcast_ms * 1e-3) / 1e9) if bcast_ms > 0 else None,
+                            "b_broadcast_note": "second (warm) NCCL broadcast of B from rank 0, device-timed, max over ranks; "
+                                                "outside the steady-state timing"}
     native.check(lib.ko_poll_device_status(), "ko_poll_device_status")
     rows = np.unique(np.r_[0:8, sh.rows - 8:sh.rows, rng.integers(0, sh.rows, 16)])
     bfull = oracle.from_bf16_bits(bd.cpu().numpy().view(np.uint16))
     want = oracle.gemm_tn_f64(oracle.from_bf16_bits(ab[rows]), bfull)
     parity["gemm_rel_fro_sampled_rows"] = oracle.rel_frobenius(dd[torch.from_numpy(rows).to(dev)].cpu().numpy(), want)
+    del ab, ad, bd, dd, a_t, b_t
+    torch.cuda.empty_cache()
     gathered = [None] * world
     if world > 1:
         dist.all_gather_object(gathered, parity)
     else:
         gathered = [parity]
-    if rank == 0:
-        worst = {k: max(g[k] for g in gathered) for k in parity}
+    worst = {k: max(g[k] for g in gathered) for k in parity}
+    return out, worst
+
+
+SCALED_WORKLOAD = ("config5_scaled: softmax f32 [1572864,512] causal -1e4 + layernorm bf16 [262144,4096] + bf16 gemm 65536x8192x8192, "
+                   "rows / M-blocks sharded, B replicated by one untimed NCCL broadcast")
+
+
+def run_scaled(args):
+    """`--workload scaled`: benchmark config 5 alone, one JSON line."""
+    rig = Rig(args)
+    out, worst = scaled_ops(rig, args.steps, args.warmup)
+    if rig.rank == 0:
         row_bytes = out["softmax_f32_causal"]["bytes"] + out["layernorm_bf16"]["bytes"]
         row_ms = out["softmax_f32_causal"]["ms"] + out["layernorm_bf16"]["ms"]
         emit({"metric": "scaled sweep (benchmark config 5): softmax+layernorm HBM throughput", "value": row_bytes / (row_ms * 1e-3) / 1e9,
-              "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": row_ms, "higher_is_better": True,
+              "unit": UNIT, "n_gpus": rig.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": row_ms, "higher_is_better": True,
               "scaling": "strong", "vs_baseline": None, "dtype": "f32 softmax / bf16 layernorm (f32 statistics) / bf16 gemm (f32 accumulate)",
               "data": "synthetic (seeded Philox4x32-10, seed 4)",
-              "config": {"workload": "config5_scaled: softmax f32 [1572864,512] causal -1e4 + layernorm bf16 [262144,4096] + bf16 gemm 65536x8192x8192, "
-                                     "rows / M-blocks sharded, B replicated by one untimed NCCL broadcast",
-                         "l2": "every per-GPU operand is larger than the 126 MB L2", "parallelism": f"rows and M-blocks x{world}, no data-path collective"},
-              "ops": out, "parity_worst_over_ranks": worst, "peak_source": peak_kind})
-    if world > 1:
-        dist.destroy_process_group()
+              "config": {"workload": SCALED_WORKLOAD,
+                         "l2": "every per-GPU operand is larger than the 126 MB L2", "parallelism": f"rows and M-blocks x{rig.world}, no data-path collective"},
+              "ops": out, "parity_worst_over_ranks": worst, "peak_source": rig.peak_kind})
+    rig.close()
 
 
 CASES = {
@@ -722,6 +835,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--skip-gemm", action="store_true", help="row operators only")
     ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    ap.add_argument("--skip-scaled", action="store_true", help="leave benchmark config 5 (the scaled shapes) out of the default run")
     ap.add_argument("--row-sets", type=int, default=0,
                     help="buffer sets to rotate over (0 = default 4/8); 1 keeps a profiler capture small")
     ap.add_argument("--workload", choices=["bert_base", "scaled"], default="bert_base",

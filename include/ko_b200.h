@@ -10,9 +10,21 @@
  * Conventions
  *   - every function returns a ko_status_t (0 = success); nothing prints, exits or aborts;
  *     ko_last_error_string() gives the calling thread's most recent failure in words;
- *   - operator entry points take DEVICE pointers valid on the CURRENT device, enqueue on
- *     `stream` (a cudaStream_t passed as void*, NULL = default stream) and return without
- *     synchronising; they allocate nothing;
+ *   - operator entry points take DEVICE pointers valid on the CURRENT device and enqueue on
+ *     `stream` (a cudaStream_t passed as void*, NULL = default stream);
+ *   - a WARMED operator call enqueues and returns: it does not synchronise, allocate or change
+ *     host-side state, and may therefore be captured into a CUDA graph.  The first call of a kind
+ *     does set-up that must not happen inside a capture, so make it eagerly beforehand:
+ *       every operator   the first launch of a kernel needing more than 48 KB of shared memory
+ *                        raises that kernel's limit (once per kernel and device);
+ *       ko_sgemm_f32     the first call on a (context, stream) that splits K allocates that stream's
+ *                        scratch lane with cudaMalloc (see ko_context_create below); later calls on
+ *                        that stream reuse it;
+ *       ko_gemm_*        a combination of (pointer, shape, type) not seen before encodes its TMA
+ *                        descriptors (host work only, no device call);
+ *       ko_*_f32_host    the first call on a device creates two copy streams and their events;
+ *                        these calls also take one process-wide lock while they enqueue;
+ *       ko_sgemm_f32_no_alloc  looks up its scratch address on first use per device (see there);
  *   - matrices are dense (leading dimension = logical width);
  *   - there is no CPU fallback: without a usable CUDA device the operator calls fail.
  */
@@ -43,7 +55,9 @@ int ko_version(void);
 /* Kernels built on mbarrier / tcgen05 pipelines bound every device-side wait; one that runs out
  * records a code in a device status word instead of hanging.  This call waits for the device's
  * outstanding work, returns KO_ERR_TIMEOUT (and clears the words) if any kernel gave up since the
- * last poll, KO_OK otherwise.  No counterpart in the reference, whose kernels never wait. */
+ * last poll, KO_OK otherwise.  "Waits" is a cudaDeviceSynchronize(): every stream of the current
+ * device, blocking or not, has drained when the words are read, so a code written by any kernel
+ * enqueued before the call is seen by it.  No counterpart in the reference, whose kernels never wait. */
 int ko_poll_device_status(void);
 /* Exercises that path without any fault: launches a one-warp kernel that waits at most `polls`
  * (1 .. 2^20) polls on an mbarrier nothing arrives at, lets the wait run out and records a code;
@@ -126,9 +140,14 @@ int ko_softmax_bf16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t col
  * Stands in for layer_normalization<LayerNormWarpImpl|LayerNormBlockImpl|
  * LayerNormBlockNoCacheImpl<E, vec, rows, cols, affine>><<<...>>>(in, out, eps, gamma, beta):
  * nn_operators/layernorm/layernorm.h:145-201, :204-252, :254-300, :302-312.
- * y = (x - mean) * rsqrt(var + eps) [* gamma] [+ beta]; statistics in FP32 by Welford/Chan
- * merging; var = M2 / (cols - ddof), ddof in {0, 1}.  gamma and beta may each be NULL and have
- * the I/O element type.  `out` may equal `in`.
+ * y = (x - mean) * rsqrt(var + eps) [* gamma] [+ beta]; var = M2 / (cols - ddof), ddof in {0, 1};
+ * statistics in FP32.  Which form of them runs depends on the row length only: rows a warp holds
+ * unpacked in registers (FP32 up to 1024 columns, 16-bit up to 1024) and the rows of the resident
+ * tier (to 16384 / 32768 columns) use the exact two-pass form over registers -- the mean from the
+ * row sum, then M2 as the sum of squared deviations from that mean, i.e. the value the merge of
+ * Welford triples converges to; longer rows (block, cluster and scalar tiers) form per-thread
+ * (count, mean, M2) triples and merge them pairwise (Chan et al.) across lanes, warps and blocks.
+ * gamma and beta may each be NULL and have the I/O element type.  `out` may equal `in`.
  * ---------------------------------------------------------------------------------------- */
 int ko_layernorm_f32(const float *in, float *out, int64_t rows, int32_t cols, float eps,
                      const float *gamma, const float *beta, int ddof, void *stream);
@@ -141,7 +160,9 @@ int ko_layernorm_f16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t co
 
 /* ------------------------------------------------------------------------------------------
  * The same operators for a caller whose rows live in HOST memory: `in` is copied to the device,
- * the operator runs and `out` is copied back, cut into `chunks` row ranges (0 = 8, at most 64) that
+ * the operator runs and `out` is copied back, cut into `chunks` nominal row ranges (0 = 8, at most 60;
+ * from 4 on, the first and last range are each cut further into a quarter, a quarter and a half, so that
+ * the stretches in which only one direction of the link is busy are short) that
  * flow through three streams, so that the copy in, the kernel and the copy out of neighbouring
  * chunks overlap and a call costs about one direction of the PCIe link.  Ordered like any other
  * work on `stream` (it starts after what `stream` holds and `stream` continues after the last
@@ -163,21 +184,51 @@ int ko_layernorm_f32_host(ko_tensor_t *in, ko_tensor_t *out, int64_t rows, int32
  * Every output is a chain of FP32 FMAs in ascending k, as in the reference; depending on the shape the
  * K range of a tile may be cut into parts that are accumulated that way and then added in K order
  * (deterministic: the same call gives the same bits; relative Frobenius error <= 1e-6 either way).
- * The first call on a (device, stream) that needs partial-tile scratch allocates it with cudaMalloc.
+ * Partial tiles of a split K live in a scratch lane owned by a context (below), one lane per stream:
+ * the first call on a stream that splits K allocates the lane with cudaMalloc, at the largest size
+ * the shape rules can ask for (4 x SMs partial tiles of 64 KB, about 39 MB on a B200), and nothing
+ * is freed or moved until the context is destroyed -- a graph captured after that first call keeps
+ * valid pointers.  A captured launch and an eager launch on the SAME stream use the same lane:
+ * replaying such a graph on another stream while that stream is busy races on it.
  * ---------------------------------------------------------------------------------------- */
 int ko_sgemm_f32(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C,
                  float *D, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Context: the owner of what the launchers keep between calls -- the SGEMM's split-K scratch lanes
+ * and the cache of encoded TMA descriptors of the tensor-core GEMM.  The plain entry points use a
+ * default context per device (created on first use, kept until the process exits); a caller that
+ * wants to bound or release that memory creates its own and calls the *_ctx forms.  No counterpart
+ * in the reference, whose kernels need neither scratch nor descriptors.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct ko_context ko_context_t;
+/* device < 0 = the current device.  Creating a context allocates nothing on the device. */
+int ko_context_create(int device, ko_context_t **out);
+/* Waits for the context's device to drain (cudaDeviceSynchronize), then frees every scratch block
+ * and forgets the cached descriptors.  Graphs captured from calls on this context must not be
+ * replayed afterwards.  NULL is a no-op. */
+int ko_context_destroy(ko_context_t *ctx);
+/* Bytes of device memory the context holds, cached descriptors, cache hits and misses; ctx = NULL
+ * reports the current device's default context; any out pointer may be NULL. */
+int ko_context_stats(ko_context_t *ctx, size_t *device_bytes, size_t *tensor_maps, size_t *map_hits,
+                     size_t *map_misses);
+/* ko_sgemm_f32 / ko_gemm_tc on an explicit context (ctx = NULL: the default one).  The context's
+ * device must be the current device. */
+int ko_sgemm_f32_ctx(ko_context_t *ctx, int64_t M, int64_t N, int64_t K, const float *A,
+                     const float *B, const float *C, float *D, void *stream);
+int ko_gemm_tc_ctx(ko_context_t *ctx, int in_fmt, int out_fmt, int b_row_major, int64_t M, int64_t N,
+                   int64_t K, const void *A, const void *B, const void *C, void *D, void *stream);
 
 /* Same operation and kernel as ko_sgemm_f32 for hosts that must not allocate device memory (a process
  * whose own pool owns the whole GPU, a loop that cannot afford an allocation's implicit
  * synchronisation, code running where the allocation calls are forbidden).  It has no counterpart
  * in the reference.  The split-K partial tiles and arrival counters live in a fixed array inside the
- * library image -- 2 Mi floats (8 MiB) and 4096 counters per GPU, held until the process exits --
- * and no cudaMalloc / cudaFree or allocating library routine is called.
+ * library image -- 2 Mi floats (8 MiB: 128 partial tiles of 128 x 128) and 128 counters per GPU, held
+ * until the process exits -- and no cudaMalloc / cudaFree or allocating library routine is called.
  *   split_k  0 = choose (never more slices than the fixed scratch holds), 1 = no split (needs no
- *            scratch, any size), n > 1 = exactly n K-slices; a request that needs more than the
- *            scratch holds (tiles * split_k * 16384 floats, tiles = ceil(M/128) * ceil(N/128), at most
- *            4096 tiles) returns KO_ERR_SHAPE and launches nothing.
+ *            scratch, any size), n > 1 = exactly n K-slices.  A split needs tiles * split_k partial
+ *            tiles, tiles = ceil(M/128) * ceil(N/128): at most 128 in all (64 tiles in 2 slices, 32 in
+ *            4, ...); a request beyond that returns KO_ERR_SHAPE and launches nothing.
  * The first call on each device looks up the array's device address and configures the kernel; make
  * that call during set-up, before any stream capture.  Every call on a device uses the same array,
  * which keeps the previous call's contents (counters are cleared on `stream` before each launch):

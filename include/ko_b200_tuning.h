@@ -1,7 +1,12 @@
-// Launch-geometry overrides of the operator entry points (same semantics as the public calls of
-// ko_b200.h; a zero knob selects the library's default).  Used by the sweep tooling and by the tests
-// that pin every instantiated variant; applications call the plain entry points.
-#pragma once
+/*
+ * ko_b200_tuning.h -- launch-geometry overrides of the operator entry points of ko_b200.h (same
+ * semantics; a zero knob selects the library's default).  For sweeps and for tests that pin every
+ * instantiated kernel variant; applications call the plain entry points.  The reference fixes these
+ * choices as template arguments and <<<grid, block>>> literals in its drivers
+ * (nn_operators/softmax/main.cu:77, nn_operators/layernorm/main.cu:75-76, nn_operators/gemm/main.cu:343).
+ */
+#ifndef KO_B200_TUNING_H
+#define KO_B200_TUNING_H
 
 #include <stdint.h>
 
@@ -15,10 +20,7 @@ typedef struct ko_row_knobs {
                             5 = resident (LayerNorm only: persistent blocks, packed FP32 math),
                             6 = cluster (one row per thread-block cluster, partials through DSMEM; softmax: stages = 1
                                 turns the shared-memory prefetch of the next row's slice off),
-                            7 = prefetching block (softmax only: row in registers, next row bulk-copied to shared memory),
-                            8 = persistent warp (LayerNorm only, rows of at most 1024 columns: one resident grid, each warp
-                                walks its rows with the next row's loads in flight; stages = 1 re-reads gamma / beta per
-                                row instead of holding them in registers) */
+                            7 = prefetching block (softmax only: row in registers, next row bulk-copied to shared memory) */
     int rows_per_warp;   /* warp / staged tier: independent row slots a warp processes together (a slot is
                             one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows) */
     int block;           /* warp tier: threads per block (<= 256); block / resident tier: threads per row (128..1024) */
@@ -40,14 +42,16 @@ int ko_layernorm_bf16_tuned(const uint16_t *in, uint16_t *out, int64_t rows, int
                             const uint16_t *gamma, const uint16_t *beta, int ddof, const ko_row_knobs_t *knobs,
                             void *stream);
 /* variant: 0 = choose, 1..3 = scalar-FFMA tilings (128x128, 128x64, 64x64), 4 = packed-FFMA 128x128 kernel;
- * 5 = 128x64 scalar-FFMA cp.async kernel; 6 / 7 / 8 = variant 4 pinned to 128x128 tiles with 128-thread
+ * 6 / 7 / 8 = variant 4 pinned to 128x128 tiles with 128-thread
  * blocks / 128x128 tiles with two warp groups that halve the block's K range / 64x128 tiles with four
  * warp groups that quarter it; split_k (variants 4, 6, 7, 8): 0 = choose the block count (stream-K),
  * 1 = one block per tile, n > 1 = n K-slices per tile */
 int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
                        int variant, int split_k, void *stream);
 /* fmt: 0 = F16, 1 = BF16 (A, B); out_fmt: 0 = FP32, 1 = F16, 2 = BF16 (D, C); b_row_major: 0 / 1; bn: 0 = choose,
- * 64 / 128 / 256 = columns of D per 128-row tile, 512 = the 256 x 256 tile (two 128-row halves per CTA share each B tile);
+ * 64 / 128 / 256 = columns of D per 128-row tile, 512 = the 256 x 256 tile (two 128-row halves per CTA share each B tile),
+ * all with equal column tiles; 1024 / 1280 = the 128- / 256-row tile with N cut into uneven column tiles of at most 256
+ * columns that fill the last round of CTAs (KO_ERR_SHAPE when that gains nothing; 0 uses them when they gain);
  * store_mode: 0 = choose, 1 = TMA-store epilogue (KO_ERR_SHAPE when not possible), 2 = direct stores */
 int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
                      const void *C, void *D, int bn, int store_mode, void *stream);
@@ -55,3 +59,4 @@ int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N
 #ifdef __cplusplus
 }
 #endif
+#endif /* KO_B200_TUNING_H */

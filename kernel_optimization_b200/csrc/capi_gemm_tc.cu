@@ -1,7 +1,8 @@
 // C-ABI launchers of the tcgen05 tensor-core GEMM: build the TMA descriptors, pick the tile width,
 // launch one persistent CTA per SM.
+#include "ko_context.h"
 #include "ko_internal.h"
-#include "ko_tuning.h"
+#include "../../include/ko_b200_tuning.h"
 #include "row_launch.h"
 
 #include <mutex>
@@ -9,6 +10,7 @@
 #include <cudaTypedefs.h>
 
 #include "../nn_operators/gemm/tensor_core_gemm.h"
+#include "../nn_operators/gemm/tensor_core_gemm_pair.h"
 
 namespace {
 
@@ -61,15 +63,99 @@ int make_map_b_row_major(EncodeTiledFn encode, CUtensorMap *map, int fmt, const 
     return KO_OK;
 }
 
-template <int BN, bool kTmaStore, int MT = 1>
-int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &md, const ko::tc::GemmParams &p, int sm_count,
-           cudaStream_t s) {
-    using Cfg = ko::tc::TileConfig<BN, MT>;
-    auto kernel = ko::tc::gemm_tcgen05_kernel<BN, kTmaStore, MT>;
+template <int BN, bool kTmaStore, int MT = 1, int kBoxes = 2>
+int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mb_narrow, const CUtensorMap &md,
+           const ko::tc::GemmParams &p, int sm_count, cudaStream_t s) {
+    using Cfg = ko::tc::TileConfig<BN, MT, kBoxes>;
+    auto kernel = ko::tc::gemm_tcgen05_kernel<BN, kTmaStore, MT, kBoxes>;
     if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), Cfg::kSmemBytes)) return st;
-    const long long tiles = (long long)((p.M + MT * ko::tc::kBM - 1) / (MT * ko::tc::kBM)) * ((p.N + BN - 1) / BN);
+    const long long tiles_n = p.tiles_n ? p.tiles_n : (p.N + BN - 1) / BN;
+    const long long tiles = (long long)((p.M + MT * ko::tc::kBM - 1) / (MT * ko::tc::kBM)) * tiles_n;
     const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
-    return ko::launch_overlapped(kernel, grid, (unsigned)ko::tc::kThreads, (size_t)Cfg::kSmemBytes, s, ma, mb, md, p);
+    return ko::launch_overlapped(kernel, grid, (unsigned)ko::tc::kThreads, (size_t)Cfg::kSmemBytes, s, ma, mb, mb_narrow, md, p);
+}
+
+// The two-SM kernel: clusters of two CTAs, one 256 x BN tile per cluster at a time, as many clusters as the device
+// holds at once (a cluster lives inside one GPC, so that can be fewer than SMs / 2).
+template <bool kTmaStore>
+int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mb_narrow, const CUtensorMap &md,
+                const ko::tc::GemmParams &p, int resident_pairs, cudaStream_t s) {
+    using Cfg = ko::tc::PairConfig;
+    auto kernel = ko::tc::gemm_tcgen05_pair_kernel<kTmaStore>;
+    const long long tiles_n = p.tiles_n ? p.tiles_n : (p.N + Cfg::kBN - 1) / Cfg::kBN;
+    const long long tiles = (long long)((p.M + 2 * ko::tc::kBM - 1) / (2 * ko::tc::kBM)) * tiles_n;
+    const unsigned pairs = (unsigned)(tiles < resident_pairs ? tiles : resident_pairs);
+    return ko::launch_clustered_overlapped(kernel, 2 * pairs, (unsigned)ko::tc::kThreads, 2, (size_t)Cfg::kSmemBytes, s, ma, mb,
+                                           mb_narrow, md, p);
+}
+
+// clusters of two CTAs of the pair kernel the current device holds at once (cached per device)
+int resident_pairs(int *out) {
+    static std::mutex mu;
+    static int cached[64] = {};
+    int dev = 0;
+    KO_CUDA(cudaGetDevice(&dev));
+    KO_REQUIRE(dev >= 0 && dev < 64, KO_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == 0) {
+        using Cfg = ko::tc::PairConfig;
+        for (const void *k : {reinterpret_cast<const void *>(ko::tc::gemm_tcgen05_pair_kernel<true>),
+                              reinterpret_cast<const void *>(ko::tc::gemm_tcgen05_pair_kernel<false>)})
+            if (int st = ko::ensure_dynamic_smem(k, Cfg::kSmemBytes)) return st;
+        int n = 0;
+        if (int st = ko::max_resident_clusters(reinterpret_cast<const void *>(ko::tc::gemm_tcgen05_pair_kernel<true>), ko::tc::kThreads, 2,
+                                               Cfg::kSmemBytes, &n))
+            return st;
+        cached[dev] = n;
+    }
+    *out = cached[dev];
+    return KO_OK;
+}
+
+// Uneven column tiles.  With every tile bn_max columns wide, tiles_m * ceil(N / bn_max) tiles run as whole rounds of
+// `slots` CTAs and the last round may be mostly empty (4096^3 with 256 x 256 tiles: 256 tiles on 148 CTAs, the second
+// round 73 % full).  Cutting N into a few more, slightly narrower tiles (widths multiples of 32, the first
+// `wide_tiles_n` one step wider than the rest) fills the rounds: 17 column tiles (9 of 256, 8 of 224) make 272 tiles
+// whose second round holds only 224-wide ones -- 480 tile-columns per CTA instead of 512 (measured 98.9 against
+// 102.3 us).  Cost model: a round takes as long as its widest tile (wide tiles are dealt first, ko::tc::tile_of); a
+// tile takes the longer of its MMAs (rows x width) and of bringing its operands into shared memory (rows + width,
+// scaled so that the 128 x 256 tile is operand-bound at 0.87 of the MMA rate, as measured on long K) -- narrower
+// tiles move more operand bytes per MMA, which is why the FFN shape keeps its 12 equal column tiles (15 uneven
+// ones measured 85.2 against 78.8 us).
+struct ColumnPlan {
+    int tiles_n = 0, wide_tiles_n = 0, bn_wide = 0, bn_narrow = 0;  // tiles_n == 0: uniform
+};
+// pair: the tile is computed by two CTAs, each with half the rows and half the B columns to load
+double tile_cost(int rows, int width, bool pair) {
+    const double mma = (double)(pair ? rows / 2 : rows) * width;
+    const double operands = (128.0 * 256.0 / 0.87 / 384.0) * (pair ? rows / 2 + width / 2 : rows + width);
+    return mma > operands ? mma : operands;
+}
+ColumnPlan plan_columns(long long M, long long N, int tile_m, int bn_max, int slots, bool pair) {
+    ColumnPlan best;
+    const long long tiles_m = (M + tile_m - 1) / tile_m;
+    const long long uniform_n = (N + bn_max - 1) / bn_max;
+    const long long uniform_rounds = (tiles_m * uniform_n + slots - 1) / slots;
+    double best_cost = (double)uniform_rounds * tile_cost(tile_m, bn_max, pair);
+    if (tiles_m * uniform_n <= slots) return best;  // a single, partly filled round: nothing to even out
+    const long long units = (N + 31) / 32;
+    for (long long tn = uniform_n + 1; tn <= 2 * uniform_n; ++tn) {
+        const long long narrow_u = units / tn, extra = units % tn;
+        if (narrow_u * 32 < bn_max / 2) break;
+        const int narrow = (int)narrow_u * 32, wide = extra ? narrow + 32 : narrow;
+        if (wide > bn_max) continue;
+        const long long total = tiles_m * tn, wide_total = tiles_m * extra;
+        double cost = 0.0;
+        for (long long r = 0; r * slots < total; ++r) cost += tile_cost(tile_m, (r * slots < wide_total) ? wide : narrow, pair);
+        if (cost < 0.97 * best_cost) {  // worth a new shape only for a clear gain
+            best_cost = cost;
+            best.tiles_n = (int)tn;
+            best.wide_tiles_n = (int)extra;
+            best.bn_wide = wide;
+            best.bn_narrow = narrow;
+        }
+    }
+    return best;
 }
 
 // [M, N] row-major output, boxes of 32 rows x 32 columns: FP32 rows of 128 bytes with the 128-byte swizzle,
@@ -95,16 +181,16 @@ double wave_efficiency(long long M, long long N, int bn, int sm_count, int bm = 
     return (double)(M * N) / (double)(waves * sm_count * (long long)bm * bn);
 }
 
-}  // namespace
-
-extern "C" {
-
 // fmt: A and B, 0 = F16, 1 = BF16; out_fmt: D and C, 0 = FP32, 1 = F16, 2 = BF16; b_row_major: 0 = B[K,N]
-// column-major (K contiguous), 1 = row-major (N contiguous); bn: 0 = choose, else 64 / 128 / 256 columns per tile;
-// store_mode: 0 = choose, 1 = TMA-store epilogue (error if not possible), 2 = direct stores;
-// bn = 512 selects the 256 x 256 tile (two 128-row halves per CTA share every B tile)
-int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
-                     const void *C, void *D, int bn, int store_mode, void *stream) {
+// column-major (K contiguous), 1 = row-major (N contiguous);
+// bn: 0 = choose; 64 / 128 / 256 = columns per 128-row tile; 512 = the 256 x 256 tile of one CTA (two 128-row halves
+// share every B tile); 1024 / 1280 = the 128- / 256-row tile with uneven column tiles forced; 2048 / 2304 = the
+// two-SM kernel (256 x 256 tile per pair of CTAs) with equal / uneven column tiles;
+// store_mode: 0 = choose, 1 = TMA-store epilogue (error if not possible), 2 = direct stores.
+// The TMA descriptors of a call are looked up in the context's cache by (base, shape, box, type) and encoded only
+// when that combination is new.
+int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A,
+                     const void *B, const void *C, void *D, int bn, int store_mode, void *stream) {
     KO_REQUIRE(fmt == 0 || fmt == 1, KO_ERR_INVALID_ARG, "gemm: fmt must be 0 (f16) or 1 (bf16)");
     KO_REQUIRE(out_fmt >= 0 && out_fmt <= 2, KO_ERR_INVALID_ARG, "gemm: out_fmt must be 0 (f32), 1 (f16) or 2 (bf16)");
     KO_REQUIRE(b_row_major == 0 || b_row_major == 1, KO_ERR_INVALID_ARG, "gemm: b_row_major must be 0 or 1");
@@ -123,7 +209,15 @@ int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N
     if (int st = ko::current_device_info(&info)) return st;
     EncodeTiledFn encode = nullptr;
     if (int st = get_encode_fn(&encode)) return st;
+    ko::Context *ctx = nullptr;
+    if (int st = ko::resolve_context(handle, &ctx)) return st;
 
+    const int bn_request = bn;
+    const bool pair = bn == 2048 || bn == 2304;
+    KO_REQUIRE(!pair || !b_row_major, KO_ERR_SHAPE, "gemm: the two-SM kernel takes column-major B");
+    if (bn == 1024) bn = 256;  // 128 x 256 tiles, uneven column tiles forced
+    if (bn == 1280) bn = 512;  // 256 x 256 tiles, uneven column tiles forced
+    if (pair) bn = 256;
     if (bn == 0) {
         const double e256 = wave_efficiency(M, N, 256, info.sm_count);
         const double e128 = 0.80 * wave_efficiency(M, N, 128, info.sm_count);
@@ -139,20 +233,51 @@ int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N
             if (tall > 0.87 * e256) bn = 512;
         }
     }
-    KO_REQUIRE(bn == 64 || bn == 128 || bn == 256 || bn == 512, KO_ERR_INVALID_ARG, "gemm: tile width %d not in {64,128,256,512}", bn);
+    KO_REQUIRE(bn == 64 || bn == 128 || bn == 256 || bn == 512, KO_ERR_INVALID_ARG,
+               "gemm: tile code %d not in {64,128,256,512,1024,1280,2048,2304}", bn_request);
     const int mt = bn == 512 ? 2 : 1;
     if (bn == 512) bn = 256;
 
-    alignas(64) CUtensorMap map_a, map_b, map_d;
-    if (int st = make_map(encode, &map_a, fmt, A, M, K, mt * ko::tc::kBM)) return st;
-    if (int st = b_row_major ? make_map_b_row_major(encode, &map_b, fmt, B, K, N) : make_map(encode, &map_b, fmt, B, N, K, bn))
-        return st;
+    int pair_slots = 0;
+    if (pair)
+        if (int st = resident_pairs(&pair_slots)) return st;
+
+    // uneven column tiles for the wide tile shapes (column-major B)
+    ColumnPlan cols;
+    const bool may_split = !b_row_major && bn == 256 && N > 256 &&
+                           (bn_request == 0 || bn_request == 1024 || bn_request == 1280 || bn_request == 2304);
+    if (may_split) cols = pair ? plan_columns(M, N, 256, 256, pair_slots, true) : plan_columns(M, N, mt * ko::tc::kBM, 256, info.sm_count, false);
+    KO_REQUIRE((bn_request != 1024 && bn_request != 1280 && bn_request != 2304) || cols.tiles_n != 0, KO_ERR_SHAPE,
+               "gemm: uneven column tiles bring nothing for this shape");
+
+    alignas(64) CUtensorMap map_a, map_b, map_b_narrow, map_d;
+    // key.kind: bits 0-1 input / output type, bits 4-7 which of the map layouts
+    const int a_box_rows = pair ? ko::tc::kBM : mt * ko::tc::kBM;  // a CTA of a pair loads its own 128 rows
+    const ko::TensorMapKey key_a{A, (uint64_t)K, (uint64_t)M, (uint32_t)ko::tc::kBK, (uint32_t)a_box_rows, (uint32_t)fmt | 0x10u};
+    if (int st = ctx->tensor_map(key_a, &map_a, [&](CUtensorMap *m) { return make_map(encode, m, fmt, A, M, K, a_box_rows); })) return st;
+    if (b_row_major) {
+        const ko::TensorMapKey key_b{B, (uint64_t)N, (uint64_t)K, 64u, (uint32_t)ko::tc::kBK, (uint32_t)fmt | 0x20u};
+        if (int st = ctx->tensor_map(key_b, &map_b, [&](CUtensorMap *m) { return make_map_b_row_major(encode, m, fmt, B, K, N); })) return st;
+    } else {
+        // a CTA of a pair loads half of the tile's columns
+        const int box_rows = (cols.tiles_n ? cols.bn_wide : bn) / (pair ? 2 : 1);
+        const ko::TensorMapKey key_b{B, (uint64_t)K, (uint64_t)N, (uint32_t)ko::tc::kBK, (uint32_t)box_rows, (uint32_t)fmt | 0x10u};
+        if (int st = ctx->tensor_map(key_b, &map_b, [&](CUtensorMap *m) { return make_map(encode, m, fmt, B, N, K, box_rows); })) return st;
+    }
+    map_b_narrow = map_b;
+    if (cols.tiles_n && cols.bn_narrow != cols.bn_wide) {
+        const int box_rows = cols.bn_narrow / (pair ? 2 : 1);
+        const ko::TensorMapKey key_n{B, (uint64_t)K, (uint64_t)N, (uint32_t)ko::tc::kBK, (uint32_t)box_rows, (uint32_t)fmt | 0x10u};
+        if (int st = ctx->tensor_map(key_n, &map_b_narrow, [&](CUtensorMap *m) { return make_map(encode, m, fmt, B, N, K, box_rows); }))
+            return st;
+    }
     // TMA-store epilogue when D has a 16-byte pitch and nothing is added to it
     const bool tma_store = store_mode != 2 && C == nullptr && N % (out_fmt == 0 ? 4 : 8) == 0 && ko::aligned16(D);
     KO_REQUIRE(store_mode != 1 || tma_store, KO_ERR_SHAPE,
                "gemm: the TMA-store epilogue needs C == NULL and a 16-byte row pitch and base for D");
     if (tma_store) {
-        if (int st = make_store_map(encode, &map_d, out_fmt, D, M, N)) return st;
+        const ko::TensorMapKey key_d{D, (uint64_t)N, (uint64_t)M, 32u, 32u, (uint32_t)out_fmt | 0x40u};
+        if (int st = ctx->tensor_map(key_d, &map_d, [&](CUtensorMap *m) { return make_store_map(encode, m, out_fmt, D, M, N); })) return st;
     } else {
         map_d = map_a;  // unused by the direct-store epilogue
     }
@@ -160,21 +285,39 @@ int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N
     ko::tc::GemmParams p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.C = C; p.D = D; p.fmt = fmt; p.out_fmt = out_fmt; p.b_row_major = b_row_major;
+    p.tiles_n = cols.tiles_n; p.wide_tiles_n = cols.wide_tiles_n; p.bn_wide = cols.bn_wide; p.bn_narrow = cols.bn_narrow;
     if (int st = ko::device_status_word(0, &p.status)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (pair)
+        return tma_store ? launch_pair<true>(map_a, map_b, map_b_narrow, map_d, p, pair_slots, s)
+                         : launch_pair<false>(map_a, map_b, map_b_narrow, map_d, p, pair_slots, s);
     if (mt == 2)
-        return tma_store ? launch<256, true, 2>(map_a, map_b, map_d, p, info.sm_count, s)
-                         : launch<256, false, 2>(map_a, map_b, map_d, p, info.sm_count, s);
+        return tma_store ? launch<256, true, 2>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s)
+                         : launch<256, false, 2>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s);
     switch (bn) {
-        case 64: return tma_store ? launch<64, true>(map_a, map_b, map_d, p, info.sm_count, s) : launch<64, false>(map_a, map_b, map_d, p, info.sm_count, s);
-        case 128: return tma_store ? launch<128, true>(map_a, map_b, map_d, p, info.sm_count, s) : launch<128, false>(map_a, map_b, map_d, p, info.sm_count, s);
-        default: return tma_store ? launch<256, true>(map_a, map_b, map_d, p, info.sm_count, s) : launch<256, false>(map_a, map_b, map_d, p, info.sm_count, s);
+        case 64: return tma_store ? launch<64, true>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s) : launch<64, false>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s);
+        case 128: return tma_store ? launch<128, true>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s) : launch<128, false>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s);
+        default: return tma_store ? launch<256, true>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s) : launch<256, false>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s);
     }
+}
+
+}  // namespace
+
+extern "C" {
+
+int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
+                     const void *C, void *D, int bn, int store_mode, void *stream) {
+    return gemm_tc_dispatch(nullptr, fmt, out_fmt, b_row_major, M, N, K, A, B, C, D, bn, store_mode, stream);
 }
 
 int ko_gemm_tc(int in_fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
                const void *C, void *D, void *stream) {
-    return ko_gemm_tc_tuned(in_fmt, out_fmt, b_row_major, M, N, K, A, B, C, D, 0, 0, stream);
+    return gemm_tc_dispatch(nullptr, in_fmt, out_fmt, b_row_major, M, N, K, A, B, C, D, 0, 0, stream);
+}
+
+int ko_gemm_tc_ctx(ko_context_t *ctx, int in_fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A,
+                   const void *B, const void *C, void *D, void *stream) {
+    return gemm_tc_dispatch(ctx, in_fmt, out_fmt, b_row_major, M, N, K, A, B, C, D, 0, 0, stream);
 }
 
 int ko_gemm_f16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B, const float *C, float *D,

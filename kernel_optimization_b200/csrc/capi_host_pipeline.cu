@@ -65,8 +65,31 @@ int run_pipeline(ko_tensor_t *in, ko_tensor_t *out, int64_t rows, int32_t cols, 
                ko_tensor_device(in));
     if (bytes == 0) return KO_OK;
     if (chunks <= 0) chunks = 8;
-    if (chunks > kMaxChunks) chunks = kMaxChunks;
+    if (chunks > kMaxChunks - 4) chunks = kMaxChunks - 4;
     if (chunks > rows) chunks = (int)rows;
+    // Row ranges.  The first chunk's copy in and the last chunk's copy out overlap with nothing (the other direction of
+    // the link is idle meanwhile), so the ends of the sequence are cut finer: with n >= 4 nominal chunks the pieces weigh
+    // 1/4, 1/4, 1/2, 1 x (n - 2), 1/2, 1/4, 1/4 of a nominal chunk (n + 4 pieces), which shrinks both idle stretches
+    // four-fold for a handful of extra copies.
+    int64_t bounds[kMaxChunks + 1];
+    int pieces = 0;
+    if (chunks >= 4 && rows >= 64LL * chunks) {
+        const int quarter_units[3] = {1, 1, 2};  // in quarters of a nominal chunk
+        int64_t done_q = 0;
+        const int64_t total_q = 4LL * chunks;
+        bounds[0] = 0;
+        auto push = [&](int q) {
+            done_q += q;
+            bounds[++pieces] = rows * done_q / total_q;
+        };
+        for (int q : quarter_units) push(q);
+        for (int c = 0; c < chunks - 2; ++c) push(4);
+        for (int i = 2; i >= 0; --i) push(quarter_units[i]);
+    } else {
+        for (int c = 0; c <= chunks; ++c) bounds[c] = rows * c / chunks;
+        pieces = chunks;
+    }
+    chunks = pieces;
 
     std::lock_guard<std::mutex> lock(g_mutex);
     Lanes *l = nullptr;
@@ -79,8 +102,10 @@ int run_pipeline(ko_tensor_t *in, ko_tensor_t *out, int64_t rows, int32_t cols, 
     KO_CUDA(cudaEventRecord(l->start, stream));
     KO_CUDA(cudaStreamWaitEvent(l->copy_in, l->start, 0));
     KO_CUDA(cudaStreamWaitEvent(l->copy_out, l->start, 0));
-    for (int c = 0; c < chunks; ++c) {
-        const int64_t r0 = rows * c / chunks, r1 = rows * (c + 1) / chunks;
+    // one chunk: copy in, wait, launch, copy out; the first failing step ends the call
+    auto enqueue_chunk = [&](int c) -> int {
+        const int64_t r0 = bounds[c], r1 = bounds[c + 1];
+        if (r1 == r0) return KO_OK;
         const size_t off = (size_t)r0 * row_bytes, len = (size_t)(r1 - r0) * row_bytes;
         KO_CUDA(cudaMemcpyAsync(d_in + off, h_in + off, len, cudaMemcpyHostToDevice, l->copy_in));
         KO_CUDA(cudaEventRecord(l->landed[c], l->copy_in));
@@ -89,9 +114,19 @@ int run_pipeline(ko_tensor_t *in, ko_tensor_t *out, int64_t rows, int32_t cols, 
         KO_CUDA(cudaEventRecord(l->computed[c], stream));
         KO_CUDA(cudaStreamWaitEvent(l->copy_out, l->computed[c], 0));
         KO_CUDA(cudaMemcpyAsync(h_out + off, d_out + off, len, cudaMemcpyDeviceToHost, l->copy_out));
-    }
-    KO_CUDA(cudaEventRecord(l->done, l->copy_out));
-    KO_CUDA(cudaStreamWaitEvent(stream, l->done, 0));
+        return KO_OK;
+    };
+    int status = KO_OK;
+    for (int c = 0; c < chunks && status == KO_OK; ++c) status = enqueue_chunk(c);
+    // Success or not, the caller's stream continues only after everything that was enqueued on the two copy
+    // streams: a call that failed half way leaves no copy running behind the caller's back.
+    const cudaError_t join_in = cudaEventRecord(l->start, l->copy_in);
+    const cudaError_t wait_in = join_in == cudaSuccess ? cudaStreamWaitEvent(stream, l->start, 0) : join_in;
+    const cudaError_t join_out = cudaEventRecord(l->done, l->copy_out);
+    const cudaError_t wait_out = join_out == cudaSuccess ? cudaStreamWaitEvent(stream, l->done, 0) : join_out;
+    if (status != KO_OK) return status;
+    if (wait_in != cudaSuccess) return ko::fail_cuda(wait_in, "host pipeline: joining the copy-in stream");
+    if (wait_out != cudaSuccess) return ko::fail_cuda(wait_out, "host pipeline: joining the copy-out stream");
     return KO_OK;
 }
 

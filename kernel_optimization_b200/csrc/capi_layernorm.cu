@@ -27,37 +27,6 @@ int launch_warp(const Args<T> &a, const ko_row_knobs_t &k, cudaStream_t s) {
                                  (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
 }
 
-// persistent warp tier: as many blocks as the device holds at once, trimmed so that every warp gets the same
-// number of rows (or one fewer); hold = gamma / beta kept unpacked in registers across rows
-template <typename T, int kVecs>
-int launch_warp_persistent(const Args<T> &a, const ko_row_knobs_t &k, int sm_count, cudaStream_t s) {
-    const int block = (k.block > 0 && k.block <= 256) ? k.block : 128;
-    const bool hold = k.stages != 1 && (a.gamma || a.beta);
-    auto kernel = hold ? ko::layernorm_warp_persistent_kernel<T, kVecs, true> : ko::layernorm_warp_persistent_kernel<T, kVecs, false>;
-    int per_sm = 0;
-    KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, 0));
-    const int wpb = block / 32;
-    long long max_blocks = k.grid_cap > 0 ? k.grid_cap : (long long)sm_count * (per_sm > 0 ? per_sm : 1);
-    const long long rows_per_warp = (a.rows + max_blocks * wpb - 1) / (max_blocks * wpb);
-    const long long warps = (a.rows + rows_per_warp - 1) / rows_per_warp;
-    const unsigned grid = ko::clamp_grid((warps + wpb - 1) / wpb, max_blocks);
-    return ko::launch_overlapped(kernel, grid, (unsigned)block, 0, s, a.in, a.out, (long long)a.rows, a.cols, a.eps, a.gamma,
-                                 a.beta, a.ddof);
-}
-
-template <typename T>
-int dispatch_warp_persistent(int vecs, const Args<T> &a, const ko_row_knobs_t &k, int sm_count, cudaStream_t s) {
-    constexpr int kMax = 32 / ko::RowIo<T>::kPerVec;  // vectors a lane keeps unpacked
-    if (vecs <= 1) return launch_warp_persistent<T, 1>(a, k, sm_count, s);
-    if (vecs <= 2) return launch_warp_persistent<T, 2>(a, k, sm_count, s);
-    if (vecs <= 4) return launch_warp_persistent<T, 4>(a, k, sm_count, s);
-    if constexpr (kMax >= 8) {
-        if (vecs <= 6) return launch_warp_persistent<T, 6>(a, k, sm_count, s);
-        if (vecs <= 8) return launch_warp_persistent<T, 8>(a, k, sm_count, s);
-    }
-    return ko::fail(KO_ERR_SHAPE, "layernorm: the persistent warp tier holds rows of at most 1024 columns");
-}
-
 template <typename T, int kVecs, int kRows>
 int launch_staged(const Args<T> &a, const ko_row_knobs_t &k, const DeviceInfo &info, cudaStream_t s, bool *used) {
     constexpr int W = ko::kStagedConsumerWarps;
@@ -166,7 +135,7 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
     if (a.rows == 0 || a.cols == 0) return KO_OK;
     KO_REQUIRE(a.in != nullptr && a.out != nullptr, KO_ERR_INVALID_ARG, "layernorm: NULL pointer");
     const ko_row_knobs_t k = knobs ? *knobs : ko_row_knobs_t{};
-    KO_REQUIRE((k.tier >= 0 && k.tier <= 6) || k.tier == 8, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
+    KO_REQUIRE(k.tier >= 0 && k.tier <= 6, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
     KO_REQUIRE(k.cluster == 0 || k.cluster == 2 || k.cluster == 4 || k.cluster == 8, KO_ERR_INVALID_ARG,
                "layernorm: cluster size %d not in {2,4,8}", k.cluster);
     KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
@@ -194,11 +163,6 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
                                                                 // gamma and beta, re-read from L2 for every row, set the pace)
         else if (nvec <= 8 * 1024 * kMaxVecsPerThread) tier = 6;  // beyond one block's registers: a cluster holds the row
         else tier = 3;
-    }
-    if (tier == 8) {
-        KO_REQUIRE(vec_ok && nvec * kPer <= 1024, KO_ERR_SHAPE,
-                   "layernorm: the persistent warp tier needs 16-byte aligned rows of at most 1024 columns");
-        return dispatch_warp_persistent<T>(vecs, a, k, info.sm_count, s);
     }
     if (tier == 6) {
         KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "layernorm: the cluster tier needs 16-byte aligned rows");

@@ -32,7 +32,8 @@ namespace x2 = ko::sgemm2;
 using Wide = x2::Shape<2, 2>;  // 128 x 128 tiles, one group of 4 warps per block
 
 constexpr size_t kMaxPartialFloats = (size_t)2 << 20;  // 2 Mi floats = 8 MiB, e.g. 1024 x 1024 outputs in 2 K-slices
-constexpr size_t kMaxTiles = 4096;                     // arrival counters (one per 128 x 128 output tile)
+constexpr size_t kMaxTiles = 128;                      // arrival counters (one per 128 x 128 output tile; a split needs
+                                                       // tiles * split_k <= 128 partial tiles, so at most 64 tiles ever split)
 constexpr size_t kCounterOffset = kMaxPartialFloats * sizeof(float);
 constexpr size_t kScratchBytes = kCounterOffset + kMaxTiles * sizeof(unsigned);
 

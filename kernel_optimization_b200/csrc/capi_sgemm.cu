@@ -1,14 +1,10 @@
 // C-ABI launcher of the FFMA SGEMM: picks the tile configuration from the problem shape.
+#include "ko_context.h"
 #include "ko_internal.h"
-#include "ko_tuning.h"
-
-#include <map>
-#include <mutex>
-#include <utility>
+#include "../../include/ko_b200_tuning.h"
 
 #include "../nn_operators/gemm/simt_gemm.h"
 #include "../nn_operators/gemm/simt_gemm_x2.h"
-#include "../nn_operators/gemm/simt_gemm_a8.h"
 #include "row_launch.h"
 
 namespace {
@@ -31,49 +27,15 @@ int launch(int M, int N, int K, const float *A, const float *B, const float *C, 
     return KO_OK;
 }
 
-// Split-K scratch: partial tiles plus one arrival counter per tile.  One buffer per (device, stream),
-// grown on demand and kept for the life of the process, so that launches on different streams never
-// share partials.  Counters are zero whenever no launch is in flight (the last block resets them).
-struct Scratch {
-    float *partials = nullptr;
-    size_t partial_floats = 0;
-    unsigned *counters = nullptr;
-    size_t counter_count = 0;
-};
-
-int get_scratch(cudaStream_t s, size_t partial_floats, size_t counter_count, Scratch *out) {
-    static std::mutex mu;
-    static std::map<std::pair<int, cudaStream_t>, Scratch> cache;
-    int dev = 0;
-    KO_CUDA(cudaGetDevice(&dev));
-    std::lock_guard<std::mutex> lock(mu);
-    Scratch &sc = cache[{dev, s}];
-    if (sc.partial_floats < partial_floats) {
-        // earlier launches on this stream may still read the old buffer
-        KO_CUDA(cudaStreamSynchronize(s));
-        if (sc.partials) KO_CUDA(cudaFree(sc.partials));
-        sc.partials = nullptr;
-        sc.partial_floats = 0;
-        KO_CUDA(cudaMalloc(&sc.partials, partial_floats * sizeof(float)));
-        sc.partial_floats = partial_floats;
-    }
-    if (sc.counter_count < counter_count) {
-        KO_CUDA(cudaStreamSynchronize(s));
-        if (sc.counters) KO_CUDA(cudaFree(sc.counters));
-        sc.counters = nullptr;
-        sc.counter_count = 0;
-        KO_CUDA(cudaMalloc(&sc.counters, counter_count * sizeof(unsigned)));
-        KO_CUDA(cudaMemset(sc.counters, 0, counter_count * sizeof(unsigned)));
-        sc.counter_count = counter_count;
-    }
-    *out = sc;
-    return KO_OK;
-}
-
+// Split-K scratch (partial tiles plus one arrival counter per tile) comes from the context: one lane per
+// stream, so that launches on different streams never share partials; allocated the first time a stream needs
+// one, at the largest size the shape rules below can ask for (ranges: 2 partial tiles for each of 2 x SMs blocks,
+// tiles < 4 x SMs), never freed or moved before the context dies.  Counters are zero whenever no launch is in
+// flight (the last block of a tile resets its counter).
 // One launch of sgemm_x2_kernel<kVecB, kWarpsM, kWarpsN, kGroups>.
 // split_k: 0 = choose the block count, 1 = one block per tile, n > 1 = n K-slices per tile.
 template <int kWarpsM, int kWarpsN, int kGroups>
-int launch_x2_shape(int M, int N, int K, const float *A, const float *B, const float *C, float *D, int split_k,
+int launch_x2_shape(ko::Context *ctx, int M, int N, int K, const float *A, const float *B, const float *C, float *D, int split_k,
                     int sm_count, cudaStream_t s) {
     namespace x2 = ko::sgemm2;
     using S = x2::Shape<kWarpsM, kWarpsN>;
@@ -115,9 +77,10 @@ int launch_x2_shape(int M, int N, int K, const float *A, const float *B, const f
             const long long most = (ktiles + per_block - 1) / per_block + 1;
             p.max_contrib = (int)(most > ctas ? ctas : most);
         }
-        Scratch sc;
+        ko::SgemmScratch sc;
         const size_t partials = ranges ? (size_t)ctas * 2 : (size_t)tiles * max_contrib;
-        if (int st = get_scratch(s, partials * S::kTileFloats, (size_t)tiles, &sc)) return st;
+        const size_t floor_tiles = (size_t)4 * sm_count;
+        if (int st = ctx->sgemm_scratch(s, partials * S::kTileFloats, (size_t)tiles, floor_tiles * 128 * 128, floor_tiles, &sc)) return st;
         p.workspace = sc.partials;
         p.counters = sc.counters;
     }
@@ -133,7 +96,7 @@ int launch_x2_shape(int M, int N, int K, const float *A, const float *B, const f
 
 // shape: 0 = choose; 1 = 128 x 128 tiles, 128-thread blocks (two per SM); 2 = 128 x 128 tiles, two groups of
 // 4 warps halve the block's K range; 3 = 64 x 128 tiles, four groups of 2 warps quarter it.
-int launch_x2(int M, int N, int K, const float *A, const float *B, const float *C, float *D, int split_k, int shape,
+int launch_x2(ko::Context *ctx, int M, int N, int K, const float *A, const float *B, const float *C, float *D, int split_k, int shape,
               int sm_count, cudaStream_t s) {
     if (shape == 0) {
         // The grouped shapes add K parts like K-slices, so they are chosen only when the caller left the
@@ -155,36 +118,21 @@ int launch_x2(int M, int N, int K, const float *A, const float *B, const float *
             shape = (M > 64 && ktiles >= 16) ? 3 : 2;
     }
     switch (shape) {
-        case 1: return launch_x2_shape<2, 2, 1>(M, N, K, A, B, C, D, split_k, sm_count, s);
-        case 2: return launch_x2_shape<2, 2, 2>(M, N, K, A, B, C, D, split_k, sm_count, s);
-        default: return launch_x2_shape<1, 2, 4>(M, N, K, A, B, C, D, split_k, sm_count, s);
+        case 1: return launch_x2_shape<2, 2, 1>(ctx, M, N, K, A, B, C, D, split_k, sm_count, s);
+        case 2: return launch_x2_shape<2, 2, 2>(ctx, M, N, K, A, B, C, D, split_k, sm_count, s);
+        default: return launch_x2_shape<1, 2, 4>(ctx, M, N, K, A, B, C, D, split_k, sm_count, s);
     }
-}
-
-int launch_a8(int M, int N, int K, const float *A, const float *B, const float *C, float *D, cudaStream_t s) {
-    namespace a8 = ko::sgemm8;
-    const long long tiles = (long long)((M + a8::BM - 1) / a8::BM) * ((N + a8::BN - 1) / a8::BN);
-    KO_REQUIRE(tiles <= 0x7fffffffLL, KO_ERR_SHAPE, "sgemm: %lld blocks exceed the grid limit", tiles);
-    const a8::Params p{M, N, K, A, B, C, D};
-    const bool vec_b = N % 4 == 0 && ko::aligned16(B);
-    const void *kernel = vec_b ? reinterpret_cast<const void *>(a8::sgemm_a8_kernel<true>)
-                               : reinterpret_cast<const void *>(a8::sgemm_a8_kernel<false>);
-    if (int st = ko::ensure_dynamic_smem(kernel, a8::kSmemBytes)) return st;
-    if (vec_b) a8::sgemm_a8_kernel<true><<<(unsigned)tiles, a8::kThreads, a8::kSmemBytes, s>>>(p);
-    else a8::sgemm_a8_kernel<false><<<(unsigned)tiles, a8::kThreads, a8::kSmemBytes, s>>>(p);
-    KO_CHECK_LAUNCH("sgemm_a8_kernel");
-    return KO_OK;
 }
 
 }  // namespace
 
-extern "C" {
+namespace {
 
 // variant: 0 = choose; 1 = 128x128 tiles with 8x8 per thread; 2 = 128x64; 3 = 64x64 (scalar FFMA,
 // register-staged); 4 = 128x128 with 16x8 per thread, packed FFMA, cp.async ring, split_k slices
-// (split_k 0 = choose, ignored by variants 1-3)
-int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
-                       int variant, int split_k, void *stream) {
+// (split_k 0 = choose, ignored by variants 1-3); 6 / 7 / 8 = variant 4 pinned to one block shape
+int sgemm_dispatch(ko_context_t *handle, int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
+                   int variant, int split_k, void *stream) {
     KO_REQUIRE(M >= 0 && N >= 0 && K >= 0, KO_ERR_INVALID_ARG, "sgemm: negative shape {%lld,%lld,%lld}",
                (long long)M, (long long)N, (long long)K);
     if (M == 0 || N == 0) return KO_OK;
@@ -193,6 +141,8 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
     KO_REQUIRE(D != A && D != B, KO_ERR_INVALID_ARG, "sgemm: D must not alias A or B");
     ko::DeviceInfo info;
     if (int st = ko::current_device_info(&info)) return st;
+    ko::Context *ctx = nullptr;
+    if (int st = ko::resolve_context(handle, &ctx)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool aligned = K % 4 == 0 && N % 4 == 0 && ko::aligned16(A) && ko::aligned16(B);
 
@@ -201,11 +151,10 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
     if (K == 0 && variant >= 4) variant = 3;  // an empty sum: D = C (or 0), nothing to pipeline
     const int m = (int)M, n = (int)N, k = (int)K;
     switch (variant) {
-        case 4: return launch_x2(m, n, k, A, B, C, D, split_k, 0, info.sm_count, s);
-        case 6: return launch_x2(m, n, k, A, B, C, D, split_k, 1, info.sm_count, s);  // 128 x 128, 128-thread blocks
-        case 7: return launch_x2(m, n, k, A, B, C, D, split_k, 2, info.sm_count, s);  // 128 x 128, two warp groups
-        case 8: return launch_x2(m, n, k, A, B, C, D, split_k, 3, info.sm_count, s);  // 64 x 128, four warp groups
-        case 5: return launch_a8(m, n, k, A, B, C, D, s);
+        case 4: return launch_x2(ctx, m, n, k, A, B, C, D, split_k, 0, info.sm_count, s);
+        case 6: return launch_x2(ctx, m, n, k, A, B, C, D, split_k, 1, info.sm_count, s);  // 128 x 128, 128-thread blocks
+        case 7: return launch_x2(ctx, m, n, k, A, B, C, D, split_k, 2, info.sm_count, s);  // 128 x 128, two warp groups
+        case 8: return launch_x2(ctx, m, n, k, A, B, C, D, split_k, 3, info.sm_count, s);  // 64 x 128, four warp groups
         case 1: return launch<CfgBig>(m, n, k, A, B, C, D, aligned, s);
         case 2: return launch<CfgWide>(m, n, k, A, B, C, D, aligned, s);
         case 3: return launch<CfgSmall>(m, n, k, A, B, C, D, aligned, s);
@@ -213,9 +162,23 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
     }
 }
 
+}  // namespace
+
+extern "C" {
+
+int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
+                       int variant, int split_k, void *stream) {
+    return sgemm_dispatch(nullptr, M, N, K, A, B, C, D, variant, split_k, stream);
+}
+
 int ko_sgemm_f32(int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C, float *D,
                  void *stream) {
-    return ko_sgemm_f32_tuned(M, N, K, A, B, C, D, 0, 0, stream);
+    return sgemm_dispatch(nullptr, M, N, K, A, B, C, D, 0, 0, stream);
+}
+
+int ko_sgemm_f32_ctx(ko_context_t *ctx, int64_t M, int64_t N, int64_t K, const float *A, const float *B, const float *C,
+                     float *D, void *stream) {
+    return sgemm_dispatch(ctx, M, N, K, A, B, C, D, 0, 0, stream);
 }
 
 }  // extern "C"

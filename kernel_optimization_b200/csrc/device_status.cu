@@ -20,7 +20,10 @@ int device_status_word(int which, unsigned int **out) {
 
 extern "C" int ko_poll_device_status(void) {
     unsigned int words[ko::kStatusWordCount] = {};
-    KO_CUDA(cudaMemcpyFromSymbol(words, g_status_words, sizeof words));  // synchronises with prior work
+    // every stream of the device, non-blocking ones included (a copy on the legacy default stream alone would
+    // not wait for those), has drained before the words are read: nothing can write between the read and the clear
+    KO_CUDA(cudaDeviceSynchronize());
+    KO_CUDA(cudaMemcpyFromSymbol(words, g_status_words, sizeof words));
     for (int i = 0; i < ko::kStatusWordCount; ++i) {
         if (words[i] != 0) {
             const unsigned int zeros[ko::kStatusWordCount] = {};

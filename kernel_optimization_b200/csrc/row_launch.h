@@ -2,7 +2,7 @@
 #pragma once
 
 #include "ko_internal.h"
-#include "ko_tuning.h"
+#include "../../include/ko_b200_tuning.h"
 
 #include "../common/row_pipeline.h"
 
@@ -86,6 +86,28 @@ int launch_overlapped(void (*kernel)(KernelArgs...), unsigned grid, unsigned blo
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    KO_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...));
+    return KO_OK;
+}
+
+// Both of the above: clusters of `cluster` blocks along x, launched with programmatic stream serialization.
+template <typename... KernelArgs, typename... Args>
+int launch_clustered_overlapped(void (*kernel)(KernelArgs...), unsigned grid, unsigned block, unsigned cluster, size_t smem,
+                                cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
     KO_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...));
     return KO_OK;
 }

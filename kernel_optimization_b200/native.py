@@ -63,6 +63,11 @@ PROTOTYPES = {
     "ko_gemm_f16_f16": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ko_gemm_bf16_bf16": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ko_gemm_tc": (_int, [_int, _int, _int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "ko_context_create": (_int, [_int, C.POINTER(_vp)]),
+    "ko_context_destroy": (_int, [_vp]),
+    "ko_context_stats": (_int, [_vp, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]),
+    "ko_sgemm_f32_ctx": (_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "ko_gemm_tc_ctx": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ko_probe_functor": (_int, [_int, _int, _int, _vp, _vp, _vp, _vp, _i64, _vp]),
     "ko_probe_reduce": (_int, [_int, _int, _vp, _vp, _i64, _int, _vp]),
     "ko_probe_limits": (_int, [_vp, _vp, _vp, _vp, _vp]),
@@ -71,7 +76,7 @@ PROTOTYPES = {
 }
 
 class RowKnobs(C.Structure):
-    """ko_row_knobs_t of csrc/ko_tuning.h: launch-geometry overrides of the row operators (0 = default)."""
+    """ko_row_knobs_t of include/ko_b200_tuning.h: launch-geometry overrides of the row operators (0 = default)."""
 
     _fields_ = [("tier", _int), ("rows_per_warp", _int), ("block", _int), ("grid_cap", _i64), ("stage_rows", _int),
                 ("stages", _int), ("ctas_per_sm", _int), ("cluster", _int)]
@@ -79,7 +84,7 @@ class RowKnobs(C.Structure):
 
 _knobs_p = C.POINTER(RowKnobs)
 
-# launch-geometry overrides (csrc/ko_tuning.h); bound when exported
+# launch-geometry overrides (include/ko_b200_tuning.h)
 TUNING_PROTOTYPES = {
     "ko_softmax_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _knobs_p, _vp]),
     "ko_layernorm_f32_tuned": (_int, [_vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _knobs_p, _vp]),

@@ -57,23 +57,31 @@ enum : unsigned { kStatusOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeout
 // operand bytes brought into shared memory per MMA drop by a third (A 32 KB + B 32 KB per 8 MMAs instead of
 // A 16 KB + B 32 KB per 4), which is what limits the 128-row tile on long K; the two halves then fill tensor
 // memory (2 x BN columns), so the epilogue of a tile no longer overlaps the next tile's MMAs.
-template <int BN, int MT = 1>
+// kBoxes: staging boxes per epilogue warp for the TMA stores of D (a store keeps its box until it has been read out
+// of shared memory).  Two are in use; four, paid for with one stage of the operand ring, measured slower at every
+// shape (FFN 16384 x 3072 x 768: 80.4 against 78.8 us), so the stores in flight are not what limits the epilogue.
+template <int BN, int MT = 1, int kBoxes = 2>
 struct TileConfig {
     static constexpr int kBN = BN;
     static constexpr int kBytesA = MT * kBM * kBK * 2;
     static constexpr int kBytesB = BN * kBK * 2;
     static constexpr int kStageBytes = kBytesA + kBytesB;
-    static constexpr int kStages = MT == 2 ? 3 : (BN >= 256 ? 4 : 6);
     static constexpr int kTmemCols = 2 * BN;  // MT = 1: double-buffered FP32 accumulator; MT = 2: one per half (power of two >= 32)
     static constexpr int kBarrierBytes = 256;
-    // epilogue staging for TMA stores: per epilogue warp two 32-row x 32-column FP32 boxes (4 KB each)
+    // epilogue staging for TMA stores: per epilogue warp kBoxes 32-row x 32-column FP32 boxes (4 KB each)
+    static constexpr int kStoreBoxes = kBoxes;
     static constexpr int kStoreBoxBytes = 32 * 32 * 4;
-    static constexpr int kStoreBytes = 4 * 2 * kStoreBoxBytes;
-    // + 1024 so the stage ring can be aligned to the 1024-byte swizzle period
+    static constexpr int kStoreBytes = 4 * kBoxes * kStoreBoxBytes;
+    static constexpr int kSmemLimit = 232448;  // 227 KB: the most one CTA may use
+    // + 1024 so the stage ring can be aligned to the 1024-byte swizzle period; as many stages as fit, at most 6
+    static constexpr int kFit = (kSmemLimit - 1024 - kBarrierBytes - kStoreBytes) / kStageBytes;
+    static constexpr int kStages = kFit > 6 ? 6 : kFit;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBarrierBytes + 1024;
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN must keep 2*BN a power of two <= 512");
     static_assert(MT == 1 || MT == 2, "one or two 128-row halves");
-    static_assert(kSmemBytes <= 232448, "stage ring exceeds the shared memory of an SM");
+    static_assert(kBoxes >= 2 && kBoxes <= 8, "staging boxes per epilogue warp");
+    static_assert(kStages >= 2, "the operand ring needs at least two stages");
+    static_assert(kSmemBytes <= kSmemLimit, "stage ring exceeds the shared memory of an SM");
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -183,7 +191,45 @@ struct GemmParams {
     int fmt;          // A and B: 0 = F16, 1 = BF16
     int out_fmt;      // D and C: 0 = FP32, 1 = F16, 2 = BF16
     int b_row_major;  // 0: B[K,N] column-major (K contiguous); 1: row-major (N contiguous)
+    // Column tiles.  tiles_n == 0: every tile is BN columns wide (tiles_n = ceil(N / BN)).  Otherwise N is cut into
+    // tiles_n tiles of which the first wide_tiles_n are bn_wide columns and the rest bn_narrow (both multiples of 32,
+    // bn_narrow <= bn_wide <= BN; column-major B only): a tile count that fills the last wave of CTAs instead of
+    // leaving part of it idle.  map_b then has a box of bn_wide rows and map_b_narrow one of bn_narrow rows.
+    int tiles_n, wide_tiles_n, bn_wide, bn_narrow;
 };
+
+// where column tile tn starts and how wide it is
+template <int BN>
+__device__ __forceinline__ void column_tile(const GemmParams &p, int tn, int &col0, int &bn) {
+    if (p.tiles_n == 0) {
+        col0 = tn * BN;
+        bn = BN;
+    } else if (tn < p.wide_tiles_n) {
+        col0 = tn * p.bn_wide;
+        bn = p.bn_wide;
+    } else {
+        col0 = p.wide_tiles_n * p.bn_wide + (tn - p.wide_tiles_n) * p.bn_narrow;
+        bn = p.bn_narrow;
+    }
+}
+
+// Tile t of a CTA's round-robin sequence -> (tile row, column tile).  With uneven column tiles all wide tiles come
+// first (then the narrow ones), so that a CTA whose first tile is wide gets narrow ones afterwards; inside each of
+// the two regions the order is tile_coords' (groups of kGroupM tile-rows, for L2 reuse).
+__device__ __forceinline__ void tile_of(const GemmParams &p, long long t, int tiles_m, int tiles_n, int &tm, int &tn) {
+    if (p.tiles_n == 0) {
+        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        return;
+    }
+    const long long wide = (long long)tiles_m * p.wide_tiles_n;
+    if (t < wide) {
+        tile_coords(t, tiles_m, p.wide_tiles_n, tm, tn);
+    } else {
+        tile_coords(t - wide, tiles_m, tiles_n - p.wide_tiles_n, tm, tn);
+        tn += p.wide_tiles_n;
+    }
+}
+
 
 // MN-major operand tile made of 64-column blocks of 64 K-rows x 128 bytes (128-byte swizzle): 8-K-row
 // atoms are 1024 bytes apart (stride offset), 64-column blocks 8192 bytes apart (leading offset).
@@ -248,13 +294,79 @@ __device__ __forceinline__ void store_row_segment(const float (&v)[32], const Ge
     }
 }
 
+// One epilogue warp's share of one 128-row block of a tile: its 32 accumulator rows (TMEM lanes of its quadrant),
+// columns [0, bn) of the accumulator that starts at TMEM address t_row, written to D rows row_base .. row_base + 31,
+// columns col0 .. col0 + bn - 1.  kTmaStore: registers -> swizzled shared box -> TMA store (box n % kBoxes of this
+// warp's kBoxes staging boxes of box_bytes each, store_seq counts the warp's stores across tiles); otherwise direct
+// 16-byte stores (and + C).  Warp-collective: all 32 lanes call it.
+template <bool kTmaStore, int kBoxes>
+__device__ __forceinline__ void epilogue_block(const CUtensorMap *map_d, const GemmParams &p, uint32_t t_row, int row_base,
+                                               int col0, int bn, int lane, uint32_t warp_boxes, uint32_t box_bytes,
+                                               uint32_t &store_seq) {
+    if constexpr (kTmaStore) {
+        // row = lane, 8 chunks of 16 B, chunk j stored at j ^ (row & 7): conflict-free, and exactly the 128-byte
+        // swizzle the store's tensor map undoes
+#pragma unroll 1
+        for (int c0 = 0; c0 < bn; c0 += 32, ++store_seq) {
+            float v[32];
+            tmem_ld_32x32(t_row + c0, v);
+            const uint32_t box = warp_boxes + (store_seq % kBoxes) * box_bytes;
+            if (lane == 0) bulk_wait_group_read<kBoxes - 1>();  // the store issued from this box kBoxes chunks ago has read it
+            __syncwarp();
+            if (p.out_fmt == 0) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t dst = box + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                                 "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                                 : "memory");
+                }
+            } else {
+                // 16-bit D: rows of 64 bytes, 4 chunks of 16 B, chunk j stored at j ^ ((row >> 1) & 3): the
+                // 64-byte swizzle of the store's tensor map, conflict-free for 8 consecutive rows
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t dst = box + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                 "r"(pack16(v[8 * j], v[8 * j + 1], p.out_fmt)), "r"(pack16(v[8 * j + 2], v[8 * j + 3], p.out_fmt)),
+                                 "r"(pack16(v[8 * j + 4], v[8 * j + 5], p.out_fmt)), "r"(pack16(v[8 * j + 6], v[8 * j + 7], p.out_fmt))
+                                 : "memory");
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            const int col = col0 + c0;
+            if (lane == 0) {
+                // rows / columns beyond M / N are clipped by the map; a box that lies entirely outside is
+                // skipped, but still closes a (then empty) group so that the box rotation holds
+                if (row_base < p.M && col < p.N) tma_store_2d(map_d, col, row_base, box);
+                bulk_commit_group();
+            }
+        }
+    } else {
+        const int row = row_base + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < bn; c0 += 32) {
+            float v[32];
+            tmem_ld_32x32(t_row + c0, v);  // warp-collective: every lane takes part
+            const int col = col0 + c0;
+            if (row < p.M && col < p.N) {
+                if (p.out_fmt == 0) store_row_segment<float>(v, p, row, col);
+                else if (p.out_fmt == 1) store_row_segment<__half>(v, p, row, col);
+                else store_row_segment<__nv_bfloat16>(v, p, row, col);
+            }
+        }
+    }
+}
+
 // kTmaStore: D is written by TMA stores staged through shared memory (needs a 16-byte row pitch and base for D
 // and no C operand); otherwise every thread stores its row segment directly (and adds C when given)
-template <int BN, bool kTmaStore, int MT = 1>
+template <int BN, bool kTmaStore, int MT = 1, int kBoxes = 2>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
-    using Cfg = TileConfig<BN, MT>;
+                    const __grid_constant__ CUtensorMap map_b_narrow, const __grid_constant__ CUtensorMap map_d,
+                    const GemmParams p) {
+    using Cfg = TileConfig<BN, MT, kBoxes>;
     constexpr int kTileM = MT * kBM;
     extern __shared__ uint8_t ko_tc_smem_raw[];
     // stage ring on a 1024-byte boundary (swizzle period), barriers behind it
@@ -273,7 +385,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + BN - 1) / BN;
+    const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = p.tiles_n ? p.tiles_n : (p.N + BN - 1) / BN;
     const long long num_tiles = (long long)tiles_m * tiles_n;
     const int k_blocks = (p.K + kBK - 1) / kBK;
 
@@ -292,6 +404,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         fence_proxy_async();
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
+        if (p.tiles_n) prefetch_tensormap(&map_b_narrow);
         if (kTmaStore) prefetch_tensormap(&map_d);
     }
     grid_launch_dependents();  // the stream's next kernel may set up while this one drains
@@ -310,8 +423,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t it = 0;
             bool ok = true;
             for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                int tm, tn;
-                tile_coords(t, tiles_m, tiles_n, tm, tn);
+                int tm, tn, col0, bn;
+                tile_of(p, t, tiles_m, tiles_n, tm, tn);
+                column_tile<BN>(p, tn, col0, bn);
+                const CUtensorMap *b_map = (p.tiles_n && bn != p.bn_wide) ? &map_b_narrow : &map_b;  // box of bn rows
+                const uint32_t stage_bytes = (uint32_t)Cfg::kBytesA + (uint32_t)bn * (kBK * 2);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % Cfg::kStages;
                     const uint32_t phase = (it / Cfg::kStages) & 1u;
@@ -321,11 +437,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
+                    mbar_expect_tx(full_bar(s), stage_bytes);
                     const uint32_t dst = ring + s * Cfg::kStageBytes;
                     tma_load_2d(dst, &map_a, kb * kBK, tm * kTileM, full_bar(s));  // one box of kTileM rows
                     if (!p.b_row_major) {
-                        tma_load_2d(dst + Cfg::kBytesA, &map_b, kb * kBK, tn * BN, full_bar(s));
+                        tma_load_2d(dst + Cfg::kBytesA, b_map, kb * kBK, col0, full_bar(s));
                     } else {
 #pragma unroll
                         for (int nb = 0; nb < BN / 64; ++nb)
@@ -347,10 +463,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(p.fmt, kBM, BN) | (p.b_row_major ? 1u << 16 : 0u);  // bit 16: B is MN-major
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
             for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
+                int tm, tn, col0, bn;
+                tile_of(p, t, tiles_m, tiles_n, tm, tn);
+                column_tile<BN>(p, tn, col0, bn);
+                const uint32_t idesc = make_idesc(p.fmt, kBM, bn) | (p.b_row_major ? 1u << 16 : 0u);  // bit 16: B is MN-major
                 // MT = 1: two accumulators used in turn; MT = 2: one accumulator per half, both busy with every tile
                 const uint32_t acc = MT == 1 ? (local_tile & 1u) : 0u, acc_phase = (MT == 1 ? (local_tile >> 1) : local_tile) & 1u;
                 if (!mbar_wait(acc_free_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -394,10 +513,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
         uint32_t local_tile = 0;
+        uint32_t store_seq = 0;  // TMA stores issued by this warp so far: store n uses staging box n % kBoxes
         bool ok = true;
         for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
-            int tm, tn;
-            tile_coords(t, tiles_m, tiles_n, tm, tn);
+            int tm, tn, col0, bn;
+            tile_of(p, t, tiles_m, tiles_n, tm, tn);
+            column_tile<BN>(p, tn, col0, bn);
             const uint32_t acc = MT == 1 ? (local_tile & 1u) : 0u, acc_phase = (MT == 1 ? (local_tile >> 1) : local_tile) & 1u;
             if (!mbar_wait(acc_ready_bar(acc), acc_phase, abort_flag)) {
                 if (lane == 0 && !*abort_flag) atomicCAS(p.status, kStatusOk, kTimeoutEpilogue);
@@ -408,63 +529,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_after();
 #pragma unroll 1
             for (int half = 0; half < MT; ++half) {
-            const int row = tm * kTileM + half * kBM + quad * 32 + lane;
-            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (MT == 1 ? acc * BN : half * BN);
-            if constexpr (kTmaStore) {
-                // registers -> swizzled shared box (row = lane, 8 chunks of 16 B, chunk j stored at j ^ (row & 7):
-                // conflict-free, and exactly the 128-byte swizzle the store's tensor map undoes) -> TMA store
-                const int ep_warp = warp - 2;
-                const int row_base = tm * kTileM + half * kBM + quad * 32;
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    float v[32];
-                    tmem_ld_32x32(t_row + c0, v);
-                    const uint32_t box = store_base + (uint32_t)(ep_warp * 2 + ((c0 >> 5) & 1)) * Cfg::kStoreBoxBytes;
-                    if (lane == 0) bulk_wait_group_read<1>();  // the store issued from this box two chunks ago has read it
-                    __syncwarp();
-                    if (p.out_fmt == 0) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const uint32_t dst = box + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
-                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]),
-                                         "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
-                                         : "memory");
-                        }
-                    } else {
-                        // 16-bit D: rows of 64 bytes, 4 chunks of 16 B, chunk j stored at j ^ ((row >> 1) & 3): the
-                        // 64-byte swizzle of the store's tensor map, conflict-free for 8 consecutive rows
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t dst = box + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4);
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
-                                         "r"(pack16(v[8 * j], v[8 * j + 1], p.out_fmt)), "r"(pack16(v[8 * j + 2], v[8 * j + 3], p.out_fmt)),
-                                         "r"(pack16(v[8 * j + 4], v[8 * j + 5], p.out_fmt)), "r"(pack16(v[8 * j + 6], v[8 * j + 7], p.out_fmt))
-                                         : "memory");
-                        }
-                    }
-                    fence_proxy_async();
-                    __syncwarp();
-                    const int col = tn * BN + c0;
-                    if (lane == 0) {
-                        // rows / columns beyond M / N are clipped by the map; a box that lies entirely outside is
-                        // skipped, but still closes a (then empty) group so that the two-deep box rotation holds
-                        if (row_base < p.M && col < p.N) tma_store_2d(&map_d, col, row_base, box);
-                        bulk_commit_group();
-                    }
-                }
-            } else {
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                float v[32];
-                tmem_ld_32x32(t_row + c0, v);  // warp-collective: every lane takes part
-                const int col = tn * BN + c0;
-                if (row < p.M && col < p.N) {
-                    if (p.out_fmt == 0) store_row_segment<float>(v, p, row, col);
-                    else if (p.out_fmt == 1) store_row_segment<__half>(v, p, row, col);
-                    else store_row_segment<__nv_bfloat16>(v, p, row, col);
-                }
-            }
-            }
+                const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (MT == 1 ? acc * BN : half * BN);
+                epilogue_block<kTmaStore, kBoxes>(&map_d, p, t_row, tm * kTileM + half * kBM + quad * 32, col0, bn, lane,
+                                                  store_base + (uint32_t)((warp - 2) * kBoxes) * Cfg::kStoreBoxBytes,
+                                                  (uint32_t)Cfg::kStoreBoxBytes, store_seq);
             }  // halves
             // the accumulator buffer may be overwritten once all four warps have read it
             tc_fence_before();

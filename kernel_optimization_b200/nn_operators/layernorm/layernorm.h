@@ -189,11 +189,7 @@ __device__ __forceinline__ void layernorm_rows_from_registers(const typename Row
                                                               int nvec, int lane, long long row0, long long row_limit,
                                                               typename RowIo<T>::Raw *out_v, int cols, float eps,
                                                               const typename RowIo<T>::Raw *gamma_v,
-                                                              const typename RowIo<T>::Raw *beta_v, int ddof,
-                                                              const f32x2 *held_gamma = nullptr,
-                                                              const f32x2 *held_beta = nullptr) {
-    // held_gamma / held_beta (short rows only): this lane's gamma / beta already unpacked to FP32 pairs by a
-    // caller that loops over rows, kVecs * kPer / 2 pairs each; the values are the ones __ldg would fetch
+                                                              const typename RowIo<T>::Raw *beta_v, int ddof) {
     using Io = RowIo<T>;
     constexpr int kPer = Io::kPerVec, kPairsPerVec = kPer / 2;
     if constexpr (kVecs * kPer <= 32) {  // depends on the row length only, so a row's bits do not depend on kRows
@@ -246,14 +242,8 @@ __device__ __forceinline__ void layernorm_rows_from_registers(const typename Row
             const int v = lane + 32 * j;
             if (v >= nvec) continue;
             f32x2 g2[kPairsPerVec], b2[kPairsPerVec];
-            if (held_gamma) {
-#pragma unroll
-                for (int q = 0; q < kPairsPerVec; ++q) g2[q] = held_gamma[j * kPairsPerVec + q];
-            } else if (gamma_v) Io::unpack_pairs(__ldg(gamma_v + v), g2);
-            if (held_beta) {
-#pragma unroll
-                for (int q = 0; q < kPairsPerVec; ++q) b2[q] = held_beta[j * kPairsPerVec + q];
-            } else if (beta_v) Io::unpack_pairs(__ldg(beta_v + v), b2);
+            if (gamma_v) Io::unpack_pairs(__ldg(gamma_v + v), g2);
+            if (beta_v) Io::unpack_pairs(__ldg(beta_v + v), b2);
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
                 if (row0 + r >= row_limit) continue;
@@ -325,64 +315,6 @@ __device__ __forceinline__ void layernorm_warp_tier(const T *in, T *out, long lo
         layernorm_rows_from_registers<T, kVecs, kRows>(raw, my_vecs, nvec, lane, row0, rows, reinterpret_cast<Raw *>(out),
                                                        cols, eps, reinterpret_cast<const Raw *>(gamma),
                                                        reinterpret_cast<const Raw *>(beta), ddof);
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// persistent warp tier (short rows): the grid is sized to what the device holds at once and every
-// warp walks rows warp, warp + W, warp + 2W, ...  The next row's loads are issued before the current
-// row is reduced, so a warp always has a row in flight (a one-row-per-warp grid has nothing in flight
-// for a block slot between one block's last store and its successor's first load), and with
-// kHoldParams gamma and beta are unpacked once per lane instead of once per row.
-// Arithmetic and operation order per row are those of the warp tier: the same bits.
-// ---------------------------------------------------------------------------------------------
-template <typename T, int kVecs, bool kHoldParams>
-__device__ __forceinline__ void layernorm_warp_persistent_tier(const T *in, T *out, long long rows, int cols, float eps,
-                                                               const T *gamma, const T *beta, int ddof) {
-    using Io = RowIo<T>;
-    using Raw = typename Io::Raw;
-    constexpr int kPairsPerVec = Io::kPerVec / 2;
-    static_assert(kVecs * Io::kPerVec <= 32, "rows that a lane holds unpacked");
-    const int lane = threadIdx.x & 31;
-    const int nvec = cols / Io::kPerVec;
-    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
-    long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const Raw *in_v = reinterpret_cast<const Raw *>(in);
-    const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma), *beta_v = reinterpret_cast<const Raw *>(beta);
-    int my_vecs = 0;
-#pragma unroll
-    for (int j = 0; j < kVecs; ++j) my_vecs += (lane + 32 * j < nvec) ? 1 : 0;
-
-    Raw next[kVecs];
-#pragma unroll
-    for (int j = 0; j < kVecs; ++j) {
-        const int v = lane + 32 * j;
-        next[j] = (row < rows && v < nvec) ? ld_stream(in_v + row * nvec + v) : Raw{};
-    }
-    f32x2 held_g[kHoldParams ? kVecs * kPairsPerVec : 1], held_b[kHoldParams ? kVecs * kPairsPerVec : 1];
-    if constexpr (kHoldParams) {
-#pragma unroll
-        for (int j = 0; j < kVecs; ++j) {
-            const int v = lane + 32 * j;
-            Io::unpack_pairs((gamma_v && v < nvec) ? __ldg(gamma_v + v) : Raw{}, held_g + j * kPairsPerVec);
-            Io::unpack_pairs((beta_v && v < nvec) ? __ldg(beta_v + v) : Raw{}, held_b + j * kPairsPerVec);
-        }
-    }
-    for (; row < rows; row += stride) {
-        Raw cur[1][kVecs];
-#pragma unroll
-        for (int j = 0; j < kVecs; ++j) cur[0][j] = next[j];
-        const long long after = row + stride;
-        if (after < rows) {
-#pragma unroll
-            for (int j = 0; j < kVecs; ++j) {
-                const int v = lane + 32 * j;
-                if (v < nvec) next[j] = ld_stream(in_v + after * nvec + v);
-            }
-        }
-        layernorm_rows_from_registers<T, kVecs, 1>(cur, my_vecs, nvec, lane, row, rows, reinterpret_cast<Raw *>(out), cols, eps,
-                                                   gamma_v, beta_v, ddof, (kHoldParams && gamma_v) ? held_g : nullptr,
-                                                   (kHoldParams && beta_v) ? held_b : nullptr);
     }
 }
 
@@ -755,13 +687,6 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const T *in, T *out
     grid_launch_dependents();  // the next kernel of the stream may take SMs as this one's blocks retire
     grid_dependency_wait();    // nothing is read before the previous kernel's writes are visible
     layernorm_warp_tier<T, kVecs, kRows>(in, out, rows, cols, eps, gamma, beta, ddof);
-}
-template <typename T, int kVecs, bool kHoldParams>
-__global__ void __launch_bounds__(256) layernorm_warp_persistent_kernel(const T *in, T *out, long long rows, int cols, float eps,
-                                                                        const T *gamma, const T *beta, int ddof) {
-    grid_launch_dependents();
-    grid_dependency_wait();
-    layernorm_warp_persistent_tier<T, kVecs, kHoldParams>(in, out, rows, cols, eps, gamma, beta, ddof);
 }
 template <typename T, int kVecs, int kRows, int kConsumerWarps>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * 32)

@@ -301,15 +301,17 @@ __device__ __forceinline__ void softmax_block_prefetch_tier(const float *in, flo
 // For rows beyond one block's registers (more than 32768 columns) or few very long rows: each of the
 // cluster's blocks holds a contiguous slice of the row, block-level (max, sum) partials are exchanged
 // through distributed shared memory (every block reads its peers' partials with plain loads from
-// their shared memory), so the row is still read from HBM exactly once.  Two cluster barriers per row;
-// the exchange slots are double buffered by row parity so no third barrier is needed.
+// their shared memory), so the row is still read from HBM exactly once.  One exchange per row: each block
+// reduces its slice against its own maximum (online softmax) and the blocks trade (max, sum) pairs; the
+// exchange slots are double buffered by row parity so no second synchronisation is needed.
 // kPrefetch: the block's slice of the cluster's NEXT row is brought into a shared-memory buffer by a bulk copy while
 // the current row is reduced, exchanged and stored (see the prefetching block tier); row_buf / bar_word / status are
 // used only then.
 // Partial (max, sum) exchange without cluster-wide barriers: every block pushes its value into each peer's mailbox
 // (a plain store into the peer's shared memory) and arrives on that peer's mbarrier; a block waits only for its own
-// mailbox to fill.  value[parity][kind][rank], one mbarrier per (parity, kind) expecting one arrival per block; row
-// parity double-buffers the slots -- a peer can be at most one exchange ahead, because every exchange needs
+// mailbox to fill.  value[parity][kind][rank] (kind 0 = block maximum, 1 = block sum against that maximum), one
+// mbarrier per parity expecting one arrival per block (bar[parity][0]; bar[parity][1] is unused); row parity
+// double-buffers the slots -- a peer can be at most one exchange ahead, because every exchange needs
 // everybody's arrival.  A cluster barrier costs about 1.3 us per row and use here, this about a third of it.
 struct ClusterMailbox {
     uint64_t bar[2][2];
@@ -349,25 +351,28 @@ __device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out
         }
         cluster.sync();  // every mailbox is ready before anybody pushes into it
     }
-    // all blocks call this with their block-wide value; returns once every block's value has arrived here
-    auto exchange = [&](int par, int kind, float v, uint32_t phase) -> bool {
+    // Every block pushes its (max, sum) pair into each peer's mailbox and arrives once on that peer's mbarrier;
+    // returns once every block's pair has arrived here.  The result is made block-uniform (one thread of a block
+    // could otherwise see the last poll succeed and another see it fail).
+    auto exchange = [&](int par, float m_block, float s_block, uint32_t phase) -> bool {
         if (threadIdx.x < nblocks) {
             const uint32_t peer = threadIdx.x;
-            st_cluster_f32(map_to_cluster_rank(smem_u32(&mail->value[par][kind][rank]), peer), v);
-            mbar_arrive_cluster(map_to_cluster_rank(smem_u32(&mail->bar[par][kind]), peer));
+            st_cluster_f32(map_to_cluster_rank(smem_u32(&mail->value[par][0][rank]), peer), m_block);
+            st_cluster_f32(map_to_cluster_rank(smem_u32(&mail->value[par][1][rank]), peer), s_block);
+            mbar_arrive_cluster(map_to_cluster_rank(smem_u32(&mail->bar[par][0]), peer));
         }
-        return mbar_wait_cluster(smem_u32(&mail->bar[par][kind]), phase);
+        return __syncthreads_and(mbar_wait_cluster(smem_u32(&mail->bar[par][0]), phase)) != 0;
     };
     volatile int never_aborted = 0;
     uint32_t landed_parity = 0;
-    bool gave_up = false;
+    bool gave_up = false;  // block-uniform by construction
     int parity = 0;
     uint32_t use = 0;  // rows done by this cluster: the mailbox of a parity is on its (use / 2)-th phase
     for (long long row = first; row < rows; row += clusters, parity ^= 1, ++use) {
         float4 x[kVecs];
         float m = kNegInf;
         if (kPrefetch) {
-            // a block that gives up still takes part in every cluster barrier below (its peers must not hang):
+            // a block that gives up still takes part in every exchange below (its peers must not hang):
             // it works on padding from here on and the status word reports the call as failed
             if (slice_bytes && !gave_up) {
                 const bool landed = mbar_wait(bar, landed_parity, &never_aborted);
@@ -395,42 +400,41 @@ __device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out
                 m = fmaxf(m, max4(x[j]));
             }
         }
+        // Online form: the block normalises its slice against its OWN maximum first, so that a single exchange of
+        // (max, sum) pairs is enough; the row's sum is sum_r s_r * 2^((m_r - m) log2 e), added in rank order.
         m = block_allreduce<true>(m, s_exchange);
-        const uint32_t mail_phase = (use >> 1) & 1u;
+        const float neg_block = m == kNegInf ? 0.f : -m * kLog2e;  // an empty or fully masked slice contributes 2^(-inf) = 0
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) s += exp_shifted4(x[j], neg_block);
+        s = block_allreduce<false>(s, s_exchange);
+        float row_max = kNegInf, total = 0.f;
         if (mail) {
-            if (!exchange(parity, 0, m, mail_phase) && !gave_up) {
+            if (!exchange(parity, m, s, (use >> 1) & 1u) && !gave_up) {
                 if (threadIdx.x == 0) atomicCAS(status, 0u, kRowPrefetchTimeout);
                 gave_up = true;  // keeps pushing (the peers wait for it) but writes nothing
             }
-            for (unsigned r = 0; r < nblocks; ++r) m = fmaxf(m, mail->value[parity][0][r]);
+            for (unsigned r = 0; r < nblocks; ++r) row_max = fmaxf(row_max, mail->value[parity][0][r]);
+            for (unsigned r = 0; r < nblocks; ++r)
+                total = fmaf(mail->value[parity][1][r], exp2_approx((mail->value[parity][0][r] - row_max) * kLog2e), total);
         } else {
-            if (threadIdx.x == 0) s_part[parity][0] = m;
-            cluster.sync();
-            for (unsigned r = 0; r < nblocks; ++r) m = fmaxf(m, cluster.map_shared_rank(&s_part[parity][0], r)[0]);
-        }
-        const float neg = -m * kLog2e;
-        float s = 0.f;
-#pragma unroll
-        for (int j = 0; j < kVecs; ++j) s += exp_shifted4(x[j], neg);  // padding: 2^(-inf) = 0
-        s = block_allreduce<false>(s, s_exchange);
-        float total = 0.f;
-        if (mail) {
-            if (!exchange(parity, 1, s, mail_phase) && !gave_up) {
-                if (threadIdx.x == 0) atomicCAS(status, 0u, kRowPrefetchTimeout);
-                gave_up = true;
+            if (threadIdx.x == 0) {
+                s_part[parity][0] = m;
+                s_part[parity][1] = s;
             }
-            for (unsigned r = 0; r < nblocks; ++r) total += mail->value[parity][1][r];  // rank order
-        } else {
-            if (threadIdx.x == 0) s_part[parity][1] = s;
             cluster.sync();
-            for (unsigned r = 0; r < nblocks; ++r) total += cluster.map_shared_rank(&s_part[parity][1], r)[0];  // rank order
+            for (unsigned r = 0; r < nblocks; ++r) row_max = fmaxf(row_max, cluster.map_shared_rank(&s_part[parity][0], r)[0]);
+            for (unsigned r = 0; r < nblocks; ++r) {
+                const float *peer = cluster.map_shared_rank(&s_part[parity][0], r);
+                total = fmaf(peer[1], exp2_approx((peer[0] - row_max) * kLog2e), total);
+            }
         }
-        const float inv = rcp_approx(total);
+        const float scale = exp2_approx((m - row_max) * kLog2e) * rcp_approx(total);
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
             const int v = v_begin + (int)threadIdx.x + (int)blockDim.x * j;
             if (v < v_end && !gave_up) {
-                scale4(x[j], inv);
+                scale4(x[j], scale);
                 st_stream(out4 + row * nvec + v, x[j]);
             }
         }

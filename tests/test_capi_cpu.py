@@ -70,3 +70,14 @@ def test_product_does_not_reach_into_the_oracle():
             if f.endswith((".py", ".h", ".cu", ".cc", ".cuh")):
                 text = open(os.path.join(base, f), errors="replace").read()
                 assert "oracle" not in text.lower(), f"{os.path.join(base, f)} refers to the oracle"
+
+
+def test_every_tuning_symbol_is_exported_and_bound(ko, lib):
+    """include/ko_b200_tuning.h: the launch-geometry overrides are part of the library and of the ctypes binding."""
+    text = open(os.path.join(ROOT, "include", "ko_b200_tuning.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = sorted(set(re.findall(r"\b(ko_[a-z0-9_]+)\s*\(", text)))
+    assert len(names) >= 6
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/ko_b200_tuning.h but not exported"
+    assert set(names) == set(ko.native.TUNING_PROTOTYPES)

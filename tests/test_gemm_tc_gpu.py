@@ -248,3 +248,95 @@ def test_general_entry_point_validates_its_arguments(cuda, lib):
     assert lib.ko_gemm_tc(1, 0, 0, 128, 64, 64, a.data_ptr() + 2, b.data_ptr(), None, d.data_ptr(), s) == 2  # unaligned A
     cuda.cuda.synchronize()
     assert lib.ko_poll_device_status() == 0
+
+
+# ---------------------------------------------------------------------------------------------------
+# uneven column tiles (bn = 1024 / 1280), and cuBLAS as a second oracle
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 128), (2048, 8192, 64), (5000, 1000, 72), (38000, 520, 64), (19000, 1032, 64)])
+def test_uneven_column_tiles_give_the_bits_of_equal_tiles(cuda, lib, oracle, kind, M, N, K):
+    """N cut into a few more, narrower column tiles (widths multiples of 32, wide tiles dealt first) so that the last
+    round of CTAs is full: every output is still one chain of the same MMAs, so the bits are those of the 256-column
+    tiling.  Shapes with more tiles than CTAs; some have a clipped last tile; both tile heights, both epilogues, with C."""
+    to_bits, from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 3, 0)), to_bits(oracle.fill_uniform((N, K), 3, 1))
+    base = _run(cuda, lib, kind, ab, bb, bn=256)
+    s = cuda.cuda.current_stream().cuda_stream
+    ran = 0
+    for bn in (1024, 1280):
+        ad, bd = _dev16(cuda, ab, kind), _dev16(cuda, bb, kind)
+        probe = cuda.empty((M, N), dtype=cuda.float32, device="cuda")
+        rc = lib.ko_gemm_tc_tuned(0 if kind == "f16" else 1, 0, 0, M, N, K, ad.data_ptr(), bd.data_ptr(), None, probe.data_ptr(), bn, 0, s)
+        cuda.cuda.synchronize()
+        if rc == 3:
+            continue  # this tile height gains nothing from uneven tiles at this shape: refused, nothing launched
+        assert rc == 0, lib.ko_last_error_string()
+        ran += 1
+        assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=bn), base)
+        assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=bn, store_mode=2), base)
+        if M <= 5000:
+            c = oracle.fill_uniform((M, N), 3, 2)
+            assert np.array_equal(_run(cuda, lib, kind, ab, bb, c, bn=bn), _run(cuda, lib, kind, ab, bb, c, bn=256))
+            assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=bn, out16=True), _run(cuda, lib, kind, ab, bb, bn=256, out16=True))
+    assert ran >= 1, "no tile height used uneven column tiles at this shape"
+    assert np.array_equal(_run(cuda, lib, kind, ab, bb), base)  # whatever the default picks
+    if M * N <= 5000 * 4096:
+        err = oracle.rel_frobenius(base, oracle.gemm_tn_f64(from_bits(ab), from_bits(bb)))
+        assert err <= TOL_FRO and err <= tight(K)
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 4096), (16384, 3072, 768)])
+def test_benchmark_shapes_against_cublas(cuda, lib, kind, M, N, K):
+    """The whole output of both benchmark shapes against cuBLAS (torch.mm with FP32 output) on the same device operands:
+    the second oracle for this kernel, whose reference counterpart is disabled.  Both accumulate exact products in
+    FP32, in different orders: relative Frobenius difference within tight(K)."""
+    tdt = cuda.float16 if kind == "f16" else cuda.bfloat16
+    gen = cuda.Generator(device="cuda")
+    gen.manual_seed(3)
+    a = (cuda.rand((M, K), device="cuda", generator=gen) * 2 - 1).to(tdt)
+    b = (cuda.rand((N, K), device="cuda", generator=gen) * 2 - 1).to(tdt)
+    d = cuda.full((M, N), float("nan"), dtype=cuda.float32, device="cuda")
+    fn = lib.ko_gemm_f16_f32 if kind == "f16" else lib.ko_gemm_bf16_f32
+    assert fn(M, N, K, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), cuda.cuda.current_stream().cuda_stream) == 0, lib.ko_last_error_string()
+    cuda.cuda.synchronize()
+    assert lib.ko_poll_device_status() == 0
+    want = cuda.mm(a, b.t(), out_dtype=cuda.float32)
+    rel = ((d.double() - want.double()).norm() / want.double().norm()).item()
+    assert rel <= tight(K), rel
+    assert bool(cuda.isfinite(d).all())
+
+
+# ---------------------------------------------------------------------------------------------------
+# the two-SM kernel (tcgen05 cta_group::2): bn = 2048 (equal column tiles) / 2304 (uneven)
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (128, 64, 64), (1, 4, 8), (100, 36, 56), (129, 264, 136), (1000, 520, 200),
+                                   (2048, 1024, 512), (5000, 300, 320), (38000, 256, 64), (20000, 1032, 72)])
+def test_two_sm_kernel_gives_the_bits_of_the_one_sm_kernel(cuda, lib, oracle, kind, M, N, K):
+    """A pair of CTAs computes a 256 x 256 tile with tcgen05.mma.cta_group::2, each CTA loading its own rows of A and its
+    own half of the B tile: every output is the same chain of MMAs in the same K order, so the bits equal the single-CTA
+    kernel's.  Tails in M, N and K; fewer tiles than pairs and many more (both accumulator buffers, ring wrap-around);
+    TMA-store and direct epilogues; + C; 16-bit D."""
+    to_bits, from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 3, 0)), to_bits(oracle.fill_uniform((N, K), 3, 1))
+    base = _run(cuda, lib, kind, ab, bb, bn=256)
+    assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=2048), base)
+    assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=2048, store_mode=2), base)
+    if M <= 5000:
+        c = oracle.fill_uniform((M, N), 3, 2)
+        assert np.array_equal(_run(cuda, lib, kind, ab, bb, c, bn=2048), _run(cuda, lib, kind, ab, bb, c, bn=256))
+        assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=2048, out16=True), _run(cuda, lib, kind, ab, bb, bn=256, out16=True))
+        err = oracle.rel_frobenius(base, oracle.gemm_tn_f64(from_bits(ab), from_bits(bb)))
+        assert err <= TOL_FRO and err <= tight(K)
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 128), (19000, 1032, 64), (38000, 520, 64)])
+def test_two_sm_kernel_with_uneven_column_tiles(cuda, lib, oracle, kind, M, N, K):
+    to_bits, _from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 3, 0)), to_bits(oracle.fill_uniform((N, K), 3, 1))
+    base = _run(cuda, lib, kind, ab, bb, bn=256)
+    assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=2304), base)
+    assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=2304, store_mode=2), base)

@@ -72,7 +72,7 @@ def test_subtract_subtracts_and_multiply_add_rounds_to_nearest(cuda, lib):
     ad, bd, cd = (cuda.from_numpy(v).cuda() for v in (a, b, c))
     out = cuda.empty(4, device="cuda")
     _ok(lib, lib.ko_probe_functor(SUBTRACT, SCALAR, F32, ad.data_ptr(), bd.data_ptr(), None, out.data_ptr(), 4, _stream(cuda)))
-    assert out.cpu().numpy().tolist() == [2.0, 1.0, 0.0, -10.0]
+    assert out.cpu().numpy().tolist() == [2.0, 1.0 - 2.0**-24, 0.0, -10.0]  # (the reference's a + b would give 8, 1 + 2^-24 -> 1, 2, -5)
     _ok(lib, lib.ko_probe_functor(MULTIPLY_ADD, VEC_VEC, F32, ad.data_ptr(), bd.data_ptr(), cd.data_ptr(), out.data_ptr(), 4,
                                   _stream(cuda)))
     got = out.cpu().numpy()
@@ -81,8 +81,9 @@ def test_subtract_subtracts_and_multiply_add_rounds_to_nearest(cuda, lib):
     assert got.tolist() == [15.0, 1.0, 1.0, -18.75]
     a2 = np.array([1.0, 1.0, 1.0, 1.0], dtype=np.float32)
     c2 = np.array([-(2.0**-30)] * 4, dtype=np.float32)
-    _ok(lib, lib.ko_probe_functor(MULTIPLY_ADD, SCALAR, F32, cuda.from_numpy(a2).cuda().data_ptr(), cuda.from_numpy(a2).cuda().data_ptr(),
-                                  cuda.from_numpy(c2).cuda().data_ptr(), out.data_ptr(), 4, _stream(cuda)))
+    a2d, c2d = cuda.from_numpy(a2).cuda(), cuda.from_numpy(c2).cuda()
+    _ok(lib, lib.ko_probe_functor(MULTIPLY_ADD, SCALAR, F32, a2d.data_ptr(), a2d.data_ptr(), c2d.data_ptr(), out.data_ptr(), 4,
+                                  _stream(cuda)))
     assert out.cpu().numpy().tolist() == [1.0] * 4  # round-toward-minus-infinity would give 1 - 2^-24
 
 

@@ -26,7 +26,7 @@ SHAPES = [(1, 1, 1), (64, 64, 8), (100, 36, 52), (129, 65, 17), (256, 256, 256),
           (128, 128, 1), (640, 384, 72)]
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4, 6])
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_unsplit_kernels_are_bit_identical_to_the_reference_order(cuda, lib, oracle, M, N, K, variant):
     a, b, c = oracle.fill_uniform((M, K), 2, 0), oracle.fill_uniform((K, N), 2, 1), oracle.fill_uniform((M, N), 2, 2)

@@ -62,3 +62,48 @@ def test_defaults_and_the_size_limit(cuda, lib, oracle):
     cuda.cuda.synchronize()
     assert rc == 3 and b"scratch" in lib.ko_last_error_string()
     assert bool((out == 7.0).all()), "a refused call must not launch anything"
+
+
+def test_the_limit_is_128_partial_tiles(cuda, lib):
+    """tiles * split_k <= 128: 64 output tiles in 2 slices are accepted, 65 tiles in 2 slices are refused before
+    anything is launched (the limit the header states)."""
+    s = cuda.cuda.current_stream().cuda_stream
+    K = 256
+    for (M, N), accepted in (((1024, 1024), True), ((1024 + 1, 1024), False), ((128 * 5, 128 * 13), False)):
+        a = cuda.zeros((M, K), dtype=cuda.float32, device="cuda")
+        b = cuda.zeros((K, N), dtype=cuda.float32, device="cuda")
+        out = cuda.full((M, N), 7.0, dtype=cuda.float32, device="cuda")
+        rc = lib.ko_sgemm_f32_no_alloc(M, N, K, a.data_ptr(), b.data_ptr(), None, out.data_ptr(), 2, s)
+        cuda.cuda.synchronize()
+        if accepted:
+            assert rc == 0, lib.ko_last_error_string()
+            assert bool((out == 0.0).all())
+        else:
+            assert rc == 3 and b"scratch" in lib.ko_last_error_string()
+            assert bool((out == 7.0).all())
+
+
+def test_a_warmed_call_leaves_device_memory_untouched(cuda, lib, oracle):
+    """What the entry point exists for: once its one-time set-up has run, a call allocates nothing -- the free-memory
+    figure the driver reports is the same before and after, and so is the caching allocator's reservation."""
+    M, N, K = 512, 512, 2048
+    a, b = oracle.fill_uniform((M, K), 2, 0), oracle.fill_uniform((K, N), 2, 1)
+    ad, bd = cuda.from_numpy(a).cuda(), cuda.from_numpy(b).cuda()
+    dd = cuda.empty((M, N), dtype=cuda.float32, device="cuda")
+    s = cuda.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = lib.ko_sgemm_f32_no_alloc(M, N, K, ad.data_ptr(), bd.data_ptr(), None, dd.data_ptr(), 4, s)
+        assert rc == 0, lib.ko_last_error_string()
+
+    call()  # set-up (symbol address, shared-memory limit) happens here at the latest
+    cuda.cuda.synchronize()
+    free_before, _total = cuda.cuda.mem_get_info()
+    reserved_before = cuda.cuda.memory_reserved()
+    for _ in range(3):
+        call()
+    cuda.cuda.synchronize()
+    free_after, _total = cuda.cuda.mem_get_info()
+    assert free_after == free_before, f"device memory changed by {free_before - free_after} bytes across warmed calls"
+    assert cuda.cuda.memory_reserved() == reserved_before
+    assert oracle.rel_frobenius(dd.cpu().numpy(), oracle.sgemm_f64(a, b)) <= TOL_FRO
