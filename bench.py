@@ -179,7 +179,7 @@ def run_reference_arm(args):
 # --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
-E2E_CHUNKS = 8
+E2E_CHUNKS = 6
 REPEAT_BATCHES = 10  # the timed batch of --steps steps is repeated this often; value = the median batch
 
 
@@ -362,18 +362,30 @@ def run_gpu_arm(args):
     t_sm_in.host_ref(np.float32)[:] = xs_host.reshape(-1)
     t_ln_in.host_ref(np.float32)[:] = xl_host.reshape(-1)
 
+    # The two operators of a step are independent, so a caller gives each its own stream: the second call's copies then
+    # queue right behind the first call's on the library's copy lanes instead of waiting for its last copy out.
+    e2e_streams = (torch.cuda.Stream(), torch.cuda.Stream())
+    e2e_joined = (torch.cuda.Event(), torch.cuda.Event())
+
     def e2e_step(_i):
         # the public host-tensor calls: rows flow through copy-in / kernel / copy-out streams in chunks
-        ko.softmax_host(t_sm_in, t_sm_out, SOFTMAX_ROWS, SOFTMAX_COLS, args.e2e_chunks)
-        ko.layernorm_host(t_ln_in, t_ln_out, LN_ROWS, LN_COLS, LN_EPS, gamma, beta, 0, args.e2e_chunks)
+        main = torch.cuda.current_stream()
+        for st in e2e_streams:
+            st.wait_stream(main)
+        ko.softmax_host(t_sm_in, t_sm_out, SOFTMAX_ROWS, SOFTMAX_COLS, args.e2e_chunks, stream=e2e_streams[0].cuda_stream)
+        ko.layernorm_host(t_ln_in, t_ln_out, LN_ROWS, LN_COLS, LN_EPS, gamma, beta, 0, args.e2e_chunks, stream=e2e_streams[1].cuda_stream)
+        for st, ev in zip(e2e_streams, e2e_joined):
+            ev.record(st)
+            main.wait_event(ev)  # the step ends (and the timing events follow) once both results are on the host
 
     e2e_steps = max(3, min(args.steps, 20))
     ms_e2e = timed(e2e_step, e2e_steps, 3)
     h2d = SOFTMAX_BYTES // 2 + LN_ROWS * LN_COLS * 4
     e2e = {"value": STEP_BYTES * world / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": h2d, "ms_per_step": ms_e2e, "steps": e2e_steps,
-           "path": f"ko_softmax_f32_host + ko_layernorm_f32_host, {args.e2e_chunks} chunks each: pinned host -> device -> kernel -> pinned host, "
-                   "copies of neighbouring chunks overlap (PCIe is full duplex); every step ends with all results on the host"}
+           "path": f"ko_softmax_f32_host + ko_layernorm_f32_host on one stream each, {args.e2e_chunks} nominal chunks per call: pinned host -> "
+                   "device -> kernel -> pinned host, copies of neighbouring chunks overlap (PCIe is full duplex); every step ends with "
+                   "all results on the host"}
     # the host link itself, all ranks at once: the step's bytes as one large pinned copy per direction on two
     # streams, no kernel -- what any pipeline through this host's PCIe fabric could reach at this rank count
     link = measure_link_ceiling(rig, h2d, 5)
@@ -645,6 +657,12 @@ CASES = {
     "softmax_c5_shard": "softmax FP32 [196608,512] with the causal -1e4 pattern (1/8 of benchmark config 5)",
     "layernorm_bf16_c5_shard": "LayerNorm BF16 [32768,4096] (1/8 of benchmark config 5)",
     "softmax_long_rows": "softmax FP32 [2048,32768]: one row per block in registers, the next row prefetched by a bulk copy",
+    "softmax_cluster_rows": "softmax FP32 [256,131072]: one row per cluster of 4 blocks, (max, sum) pairs exchanged through DSMEM mailboxes",
+    "layernorm_cluster_rows": "LayerNorm FP32 [256,131072] affine: one row per cluster of 4 blocks, Welford triples exchanged through DSMEM mailboxes",
+    "layernorm_c2": "LayerNorm FP32 [16384,768] affine (benchmark config 2), 8 rotating buffer sets",
+    "softmax_c1": "softmax FP32 [196608,128] (benchmark config 1), 4 rotating buffer sets",
+    "gemm_bf16_ffn_pair": "BF16 GEMM 16384x3072x768 on the two-SM kernel (tcgen05 cta_group::2)",
+    "gemm_bf16_4096_pair": "BF16 GEMM 4096^3 on the two-SM kernel (tcgen05 cta_group::2)",
 }
 
 
@@ -668,12 +686,33 @@ def run_case(args):
         launch = lambda: native.check(lib.ko_sgemm_f32(n, n, n, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s()), name)  # noqa: E731
         work, unit = 2.0 * n ** 3, "TFLOP/s"
     elif name.startswith("gemm_bf16"):
-        M, N, K = (4096, 4096, 4096) if name.endswith("4096") else (16384, 3072, 768)
+        M, N, K = (4096, 4096, 4096) if "4096" in name else (16384, 3072, 768)
         a = torch.from_numpy(ko.fill_uniform((M, K), 3, 0, dtype=2).view(np.int16)).to(dev)
         b = torch.from_numpy(ko.fill_uniform((N, K), 3, 1, dtype=2).view(np.int16)).to(dev)
         d = torch.empty((M, N), device=dev)
-        launch = lambda: native.check(lib.ko_gemm_bf16_f32(M, N, K, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s()), name)  # noqa: E731
+        if name.endswith("_pair"):
+            launch = lambda: native.check(lib.ko_gemm_tc_tuned(1, 0, 0, M, N, K, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), 2048, 0, s()), name)  # noqa: E731
+        else:
+            launch = lambda: native.check(lib.ko_gemm_bf16_f32(M, N, K, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s()), name)  # noqa: E731
         work, unit = 2.0 * M * N * K, "TFLOP/s"
+    elif name in ("softmax_cluster_rows", "layernorm_cluster_rows", "layernorm_c2", "softmax_c1"):
+        rows, cols, nsets = {"softmax_cluster_rows": (256, 131072, 3), "layernorm_cluster_rows": (256, 131072, 3),
+                             "layernorm_c2": (LN_ROWS, LN_COLS, 8), "softmax_c1": (SOFTMAX_ROWS, SOFTMAX_COLS, 4)}[name]
+        host = ko.fill_normal((rows, cols), 1, 0, 0.0, 1.0)
+        xs = [torch.from_numpy(host).to(dev) for _ in range(nsets)]
+        ys = [torch.empty_like(xs[0]) for _ in range(nsets)]
+        g = torch.from_numpy(ko.fill_uniform((cols,), 1, 1, 0.5, 1.5)).to(dev)
+        b = torch.from_numpy(ko.fill_normal((cols,), 1, 2, 0.0, 0.1)).to(dev)
+        turn = [0]
+
+        def launch():
+            j = turn[0] % nsets
+            turn[0] += 1
+            if name.startswith("softmax"):
+                native.check(lib.ko_softmax_f32(xs[j].data_ptr(), ys[j].data_ptr(), rows, cols, s()), name)
+            else:
+                native.check(lib.ko_layernorm_f32(xs[j].data_ptr(), ys[j].data_ptr(), rows, cols, LN_EPS, g.data_ptr(), b.data_ptr(), 0, s()), name)
+        work, unit = 2.0 * rows * cols * 4, "GB/s"
     elif name == "softmax_long_rows":
         rows, cols = 2048, 32768
         xd = torch.from_numpy(ko.fill_normal((rows, cols), 0, 0, 0.0, 2.0)).to(dev)
@@ -709,7 +748,8 @@ def run_case(args):
     ms = e0.elapsed_time(e1) / args.steps
     scale = 1e12 if unit == "TFLOP/s" else 1e9
     emit({"case": name, "what": CASES[name], "us_per_launch": ms * 1e3, "value": work / (ms * 1e-3) / scale,
-          "unit": unit, "steps": args.steps, "note": "same buffers every launch (L2-warm for small cases)"})
+          "unit": unit, "steps": args.steps,
+          "note": "row-operator cases named *_rows / *_c1 / *_c2 rotate over buffer sets larger than the L2; the others use the same buffers every launch"})
 
 
 # --------------------------------------------------------------------------------------------------

@@ -309,6 +309,12 @@ int ko_probe_welford(int kind, const float *in, int64_t rows, int32_t cols, floa
 int ko_probe_composed_rowop(int op, const float *in, float *out, int64_t rows, int32_t cols,
                             float eps, const float *gamma, const float *beta, int block, void *stream);
 
+/* gemm<GemmKernelTensorCore<half, half, half, GemmShape<128,128,32>, GemmShape<64,64,32>, GemmShape<16,8,8>, 8,8,8>>
+ * launched as the reference's driver would launch it (nn_operators/gemm/main.cu:179-339, call disabled at :344):
+ * half A [M,K], B [K,N], optional C and D [M,N], all row-major; D = A * B (+ C) with FP32 accumulation. */
+int ko_probe_gemm_tensor_core_template(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
+                                       const uint16_t *C, uint16_t *D, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

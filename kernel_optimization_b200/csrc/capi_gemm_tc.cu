@@ -213,7 +213,12 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     if (int st = ko::resolve_context(handle, &ctx)) return st;
 
     const int bn_request = bn;
-    const bool pair = bn == 2048 || bn == 2304;
+    // The two-SM kernel when the caller asks for it, and by default where it measured fastest: medium K, where the
+    // single-CTA tiles are limited by bringing operands in (128 x 256) or by their exposed epilogue (256 x 256) --
+    // 16384 x 3072 x 768: 72.7 against 77.6 us; 16384 x 768 x 3072: 65.8 / 70.8; 4096 x 4096 x 1024: 35.1 / 36.7.
+    // Longer K goes to the single-CTA 256 x 256 tile with uneven columns (4096^3: 97.6 against 101.9 us), K <= 512 and
+    // small problems to the 128-row tile (8192 x 8192 x 512: 79.5 / 82.4; 32768 x 1024 x 256: 31.8 / 37.6).
+    const bool pair = bn == 2048 || bn == 2304 || (bn == 0 && !b_row_major && K > 512 && K <= 3072 && M >= 4096 && N >= 512);
     KO_REQUIRE(!pair || !b_row_major, KO_ERR_SHAPE, "gemm: the two-SM kernel takes column-major B");
     if (bn == 1024) bn = 256;  // 128 x 256 tiles, uneven column tiles forced
     if (bn == 1280) bn = 512;  // 256 x 256 tiles, uneven column tiles forced
@@ -245,7 +250,7 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     // uneven column tiles for the wide tile shapes (column-major B)
     ColumnPlan cols;
     const bool may_split = !b_row_major && bn == 256 && N > 256 &&
-                           (bn_request == 0 || bn_request == 1024 || bn_request == 1280 || bn_request == 2304);
+                           ((bn_request == 0 && !pair) || bn_request == 1024 || bn_request == 1280 || bn_request == 2304);
     if (may_split) cols = pair ? plan_columns(M, N, 256, 256, pair_slots, true) : plan_columns(M, N, mt * ko::tc::kBM, 256, info.sm_count, false);
     KO_REQUIRE((bn_request != 1024 && bn_request != 1280 && bn_request != 2304) || cols.tiles_n != 0, KO_ERR_SHAPE,
                "gemm: uneven column tiles bring nothing for this shape");

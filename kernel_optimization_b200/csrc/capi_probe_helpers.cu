@@ -420,3 +420,30 @@ extern "C" int ko_probe_composed_rowop(int op, const float *in, float *out, int6
     KO_CHECK_LAUNCH("composed row operator probe");
     return KO_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The reference's tensor-core kernel template, launched the way its driver would
+// (nn_operators/gemm/main.cu:179-339, call disabled at :344): half A [M,K], B [K,N], C / D [M,N],
+// all row-major, gemm<GemmKernelTensorCore<...>><<<grid, thread_per_block, smem_total_size_in_bytes>>>.
+// ---------------------------------------------------------------------------------------------
+#include "../nn_operators/gemm/gemm.h"
+
+extern "C" int ko_probe_gemm_tensor_core_template(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
+                                                  const uint16_t *C, uint16_t *D, void *stream) {
+    using Kernel = GemmKernelTensorCore<half, half, half, shape::GemmShape<128, 128, 32>, shape::GemmShape<64, 64, 32>,
+                                        shape::GemmShape<16, 8, 8>, 8, 8, 8>;
+    KO_REQUIRE(M >= 1 && N >= 1 && K >= 0 && M <= 0x7fffffff && N <= 0x7fffffff && K <= 0x7fffffff, KO_ERR_INVALID_ARG,
+               "probe: bad GEMM shape");
+    KO_REQUIRE(A && B && D, KO_ERR_INVALID_ARG, "probe: NULL operand");
+    const long long tiles = ((M + 127) / 128) * ((N + 127) / 128);
+    const unsigned grid = (unsigned)(tiles < 4096 ? tiles : 4096);
+    const shape::GemmCoord problem((size_t)M, (size_t)N, (size_t)K);
+    // what the reference's driver does before every launch (nn_operators/gemm/main.cu:75-82)
+    if (Kernel::smem_total_size_in_bytes >= (48 << 10))
+        KO_CUDA(cudaFuncSetAttribute(gemm<Kernel>, cudaFuncAttributeMaxDynamicSharedMemorySize, Kernel::smem_total_size_in_bytes));
+    gemm<Kernel><<<grid, Kernel::thread_per_block, Kernel::smem_total_size_in_bytes, static_cast<cudaStream_t>(stream)>>>(
+        problem, reinterpret_cast<half *>(const_cast<uint16_t *>(A)), reinterpret_cast<half *>(const_cast<uint16_t *>(B)),
+        reinterpret_cast<half *>(const_cast<uint16_t *>(C)), reinterpret_cast<half *>(D));
+    KO_CHECK_LAUNCH("gemm<GemmKernelTensorCore>");
+    return KO_OK;
+}

@@ -11,10 +11,12 @@
 // Synchronisation (all mbarriers; every wait is bounded and reports through the device status word):
 //   full[s]      leader only.  The leader's producer posts the byte count of BOTH CTAs' loads of stage s; both CTAs'
 //                TMA loads complete on it (the peer passes the leader's barrier, cp.async.bulk.tensor ... cta_group::2).
-//   empty[s]     one per CTA.  The leader commits (tcgen05.commit.cta_group::2) to its own and to the peer's barrier,
-//                two plain commits with shared::cluster addresses; each producer waits on its own.
-//   acc_ready[a] one per CTA, committed the same way once a tile's MMAs are issued; each CTA's epilogue warps wait on
-//                their own.
+//   empty[s]     one per CTA.  The leader's MMA thread commits (tcgen05.commit.cta_group::2, which tracks both SMs) to
+//                the leader's barrier only -- a commit costs the MMA issue stream about 50 ns, a second one per stage
+//                measured 14 % -- and the leader's producer, once it has seen that release, passes it on to the
+//                peer's barrier with a relaxed remote arrive; each producer waits on its own barrier.
+//   acc_ready[a] one per CTA, two plain commits (shared::cluster addresses) once a tile's MMAs are issued; each CTA's
+//                epilogue warps wait on their own.
 //   acc_free[a]  leader only, 8 arrivals: the four epilogue warps of both CTAs (the peer's arrive remotely).
 // Before tensor memory is released and before either CTA exits, the leader drains its MMAs and the pair meets at a
 // cluster barrier: the leader's MMAs read the peer's shared memory and write its tensor memory until then.
@@ -82,6 +84,12 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar)
         : "memory");
+}
+// Arrive on an mbarrier of another CTA of the cluster as a pure token (no data of this thread is handed over, so no
+// release: a releasing arrive from the producer thread measured twice the kernel time, it waits for the thread's
+// copies in flight).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
 // bounded wait with cluster-scope acquire (for barriers another CTA arrives on)
 __device__ __forceinline__ bool mbar_wait_remote(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
@@ -171,7 +179,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         ok = false;
                         break;
                     }
-                    if (leader) mbar_expect_tx(full_bar(s), 2u * cta_bytes);  // both CTAs' loads land on this barrier
+                    if (leader) {
+                        // the MMAs that read this stage -- in both CTAs -- have completed: tell the peer's producer (a plain
+                        // remote arrive; a second tcgen05.commit per stage would cost the MMA issue stream ~50 ns each)
+                        if (it >= (uint32_t)Cfg::kStages) mbar_arrive_cluster_relaxed(map_to_cluster_rank(empty_bar(s), 1));
+                        mbar_expect_tx(full_bar(s), 2u * cta_bytes);  // both CTAs' loads land on this barrier
+                    }
                     const uint32_t leader_full = map_to_cluster_rank(full_bar(s), 0);
                     const uint32_t dst = ring + s * Cfg::kStageBytes;
                     tma_load_2d_pair(dst, &map_a, kb * kBK, tm * kTileM + (int)rank * kBM, leader_full);
@@ -185,7 +198,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (lane == 0 && leader) {
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
-            const uint32_t peer_empty0 = map_to_cluster_rank(empty_bar(0), 1), own_empty0 = map_to_cluster_rank(empty_bar(0), 0);
+            const uint32_t own_empty0 = map_to_cluster_rank(empty_bar(0), 0);
             const uint32_t peer_ready0 = map_to_cluster_rank(acc_ready_bar(0), 1), own_ready0 = map_to_cluster_rank(acc_ready_bar(0), 0);
             for (long long t = pair; t < num_tiles && ok; t += pairs, ++local_tile) {
                 int tm, tn, col0, bn;
@@ -208,9 +221,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         const uint64_t db = smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
                         umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
-                    // the stage is reusable in both CTAs once these MMAs have read it
+                    // the stage is reusable once these MMAs have read it (in both CTAs: the commit tracks both SMs); the
+                    // leader's producer passes the release on to the peer
                     umma_commit_pair(own_empty0 + 8u * s);
-                    umma_commit_pair(peer_empty0 + 8u * s);
                 }
                 if (ok) {
                     umma_commit_pair(own_ready0 + 8u * acc);

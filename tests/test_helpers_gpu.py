@@ -291,3 +291,29 @@ def test_composed_layernorm_matches_the_oracle(cuda, lib, oracle, block, affine)
                                          gd.data_ptr() if affine else None, bd.data_ptr() if affine else None, block,
                                          _stream(cuda)))
     assert oracle.max_rel_err(out.cpu().numpy(), oracle.layernorm_f64(x, 1e-12, g, b)) <= 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (256, 384, 64), (100, 36, 52), (129, 65, 17), (300, 200, 1000), (128, 128, 64),
+                                   (1000, 520, 200), (2048, 1024, 4096), (131, 4104, 72), (20000, 128, 256)])
+@pytest.mark.parametrize("with_c", [False, True])
+def test_reference_tensor_core_template_through_its_launch_syntax(cuda, lib, oracle, M, N, K, with_c):
+    """gemm<GemmKernelTensorCore<half, ...>><<<grid, thread_per_block, smem>>>: half operands, row-major B, FP32 accumulation,
+    D rounded once to half; against the float64 product of the rounded inputs.  K and N multiples of 8 run on tcgen05 (operand
+    tiles copied into the swizzled layouts by cp.async, descriptors built in the kernel), other shapes on the FP32 pipe; tails in
+    M, N and K, one to 64 K-blocks, more tiles than blocks."""
+    ab = oracle.to_f16_bits(oracle.fill_uniform((M, K), 3, 0))
+    bb = oracle.to_f16_bits(oracle.fill_uniform((K, N), 3, 1))
+    cb = oracle.to_f16_bits(oracle.fill_uniform((M, N), 3, 2)) if with_c else None
+    dev = lambda bits: cuda.from_numpy(bits.view(np.int16)).cuda()  # noqa: E731
+    ad, bd = dev(ab), dev(bb)
+    cd = dev(cb) if with_c else None
+    dd = cuda.full((M, N), 0x7E00, dtype=cuda.int16, device="cuda")  # NaN
+    _ok(lib, lib.ko_probe_gemm_tensor_core_template(M, N, K, ad.data_ptr(), bd.data_ptr(), cd.data_ptr() if with_c else None, dd.data_ptr(),
+                                                    _stream(cuda)))
+    cuda.cuda.synchronize()
+    got = oracle.from_f16_bits(dd.cpu().numpy().view(np.uint16)).astype(np.float64)
+    want = oracle.from_f16_bits(ab).astype(np.float64) @ oracle.from_f16_bits(bb).astype(np.float64)
+    if with_c:
+        want = want + oracle.from_f16_bits(cb).astype(np.float64)
+    assert np.isfinite(got).all()
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
