@@ -47,10 +47,11 @@ DATA_NOTE = "synthetic (seeded Philox4x32-10 fills of the benchmark shapes and d
 # profiles/softmax_warp_kernel_196608x128.txt and profiles/layernorm_warp_kernel_16384x768.txt.  "isolated": one
 # launch with the caches flushed before it, so the part of the output still dirty in the 126 MB L2 when the kernel ends
 # is missing from the write count; "steady": launches back to back over rotating buffer sets with the caches left
-# alone, where the write-back of the previous launch's output falls into this launch (None until captured).
+# alone, where the write-back of the previous launch's output falls into this launch (mean of three consecutive
+# launches of `bench.py --case softmax_c1` / `--case layernorm_c2` under ncu --cache-control none).
 NCU_TRAFFIC = {
-    "softmax": {"isolated": 145_612_800, "steady": None},
-    "layernorm": {"isolated": 56_400_000, "steady": None},
+    "softmax": {"isolated": 145_612_800, "steady": 198_488_900},
+    "layernorm": {"isolated": 56_400_000, "steady": 98_592_800},
 }
 
 

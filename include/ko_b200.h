@@ -145,8 +145,9 @@ int ko_softmax_bf16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t col
  * unpacked in registers (FP32 up to 1024 columns, 16-bit up to 1024) and the rows of the resident
  * tier (to 16384 / 32768 columns) use the exact two-pass form over registers -- the mean from the
  * row sum, then M2 as the sum of squared deviations from that mean, i.e. the value the merge of
- * Welford triples converges to; longer rows (block, cluster and scalar tiers) form per-thread
- * (count, mean, M2) triples and merge them pairwise (Chan et al.) across lanes, warps and blocks.
+ * Welford triples converges to; longer rows (block, cluster, two-pass and scalar tiers) form
+ * per-thread (count, mean, M2) triples and merge them pairwise (Chan et al.) across lanes, warps
+ * and blocks.  Rows too long for one block's registers are read twice, the second time from the L2.
  * gamma and beta may each be NULL and have the I/O element type.  `out` may equal `in`.
  * ---------------------------------------------------------------------------------------- */
 int ko_layernorm_f32(const float *in, float *out, int64_t rows, int32_t cols, float eps,

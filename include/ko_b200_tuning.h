@@ -20,9 +20,13 @@ typedef struct ko_row_knobs {
                             5 = resident (LayerNorm only: persistent blocks, packed FP32 math),
                             6 = cluster (one row per thread-block cluster, partials through DSMEM; softmax: stages = 1
                                 turns the shared-memory prefetch of the next row's slice off),
-                            7 = prefetching block (softmax only: row in registers, next row bulk-copied to shared memory) */
+                            7 = prefetching block (softmax only: row in registers, next row bulk-copied to shared memory),
+                            8 = reread (FP32 softmax and every LayerNorm: one row per block in two passes, the second served
+                                by the L2; block = 256 / 512 / 1024 threads, grid_cap = rows in flight) */
     int rows_per_warp;   /* warp / staged tier: independent row slots a warp processes together (a slot is
-                            one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows) */
+                            one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows); LayerNorm reread tier:
+                            1 = one row per block at a time, 2 = two (gamma / beta loaded once for both),
+                            0 = two from 512 KB per row */
     int block;           /* warp tier: threads per block (<= 256); block / resident tier: threads per row (128..1024) */
     int64_t grid_cap;    /* warp / block / stream tier: upper bound on the grid (0 = one pass per warp) */
     int stage_rows;      /* staged tier: rows per bulk copy (0 = about 16-32 KB) */

@@ -192,6 +192,30 @@ __device__ __forceinline__ uint4 ld_stream(const uint4 *p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
 __device__ __forceinline__ void st_stream(uint4 *p, uint4 v) { __stcs(p, v); }
 
+// Loads whose lines should stay in the L2 because the same block reads them a second time soon (the two-pass tiers
+// for rows too long for registers): L1 is bypassed, the L2 line is marked evict-last.  The second read uses
+// ld_stream, which marks it evict-first again.
+__device__ __forceinline__ uint64_t l2_keep_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ float4 ld_keep(const float4 *p, uint64_t policy) {
+    float4 v;
+    asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p), "l"(policy));
+    return v;
+}
+
+__device__ __forceinline__ uint4 ld_keep(const uint4 *p, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(policy));
+    return v;
+}
+
 // Running (count, mean, M2) triple; M2 is the sum of squared deviations from the mean.
 struct Welford {
     float n, mean, m2;

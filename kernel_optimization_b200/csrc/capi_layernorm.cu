@@ -1,6 +1,8 @@
 // C-ABI launchers of the LayerNorm forward: tier and launch geometry from the runtime shape.
 #include "row_launch.h"
 
+#include <algorithm>
+
 #include "../nn_operators/layernorm/layernorm.h"
 
 namespace {
@@ -128,6 +130,27 @@ int dispatch_rows(int vecs, int rpw, const Args<T> &a, const ko_row_knobs_t &k, 
 #undef KO_GO
 }
 
+// one row per block, read twice (the second time from the L2); blocks per SM: as many as fit, fewer when the rows in
+// flight would not fit in `l2_budget` bytes
+template <typename T, int kThreads, bool kPair>
+int launch_reread(const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
+    // registers: 16-bit vectors unpack to 8 floats each, and a pair of rows doubles what the second pass holds
+    constexpr int kStatUnroll = (sizeof(T) == 2 && kThreads == 1024) ? 2 : 4;
+    constexpr int kUnroll = ((sizeof(T) == 2 || kPair) && kThreads == 1024) ? 2 : 4;
+    auto kernel = ko::layernorm_reread_kernel<T, kStatUnroll, kUnroll, kThreads, kPair>;
+    long long cap = grid_cap;
+    if (cap <= 0) {
+        int per_sm = 0;
+        KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+        const long long l2_budget = 80ll << 20;
+        const long long fit = l2_budget / ((long long)a.cols * (long long)sizeof(T) * sm_count * (kPair ? 2 : 1));
+        cap = (long long)sm_count * std::max(1ll, std::min<long long>(per_sm, fit));
+    }
+    const long long units = kPair ? (a.rows + 1) / 2 : a.rows;
+    return ko::launch_overlapped(kernel, ko::clamp_grid(units, cap), (unsigned)kThreads, 0, s, a.in, a.out, a.rows, a.cols, a.eps,
+                                 a.gamma, a.beta, a.ddof);
+}
+
 template <typename T>
 int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream_t s) {
     KO_REQUIRE(a.rows >= 0 && a.cols >= 0, KO_ERR_INVALID_ARG, "layernorm: negative shape [%lld, %d]", a.rows, a.cols);
@@ -135,7 +158,7 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
     if (a.rows == 0 || a.cols == 0) return KO_OK;
     KO_REQUIRE(a.in != nullptr && a.out != nullptr, KO_ERR_INVALID_ARG, "layernorm: NULL pointer");
     const ko_row_knobs_t k = knobs ? *knobs : ko_row_knobs_t{};
-    KO_REQUIRE(k.tier >= 0 && k.tier <= 6, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
+    KO_REQUIRE((k.tier >= 0 && k.tier <= 6) || k.tier == 8, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
     KO_REQUIRE(k.cluster == 0 || k.cluster == 2 || k.cluster == 4 || k.cluster == 8, KO_ERR_INVALID_ARG,
                "layernorm: cluster size %d not in {2,4,8}", k.cluster);
     KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
@@ -159,10 +182,24 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         // (BF16 [32768,2048]: resident tier with 128-thread blocks 46.0 us, warp tier 51.8 us; at 1024 columns they tie)
         else if (warp_ok && (sizeof(T) == 4 || nvec <= 128)) tier = 1;
         else if (nvec <= 1024 * 4) tier = 5;
-        else if (nvec <= 1024 * kMaxVecsPerThread) tier = 2;  // (prefetching the next row, as softmax does, measured no gain here:
-                                                                // gamma and beta, re-read from L2 for every row, set the pace)
-        else if (nvec <= 8 * 1024 * kMaxVecsPerThread) tier = 6;  // beyond one block's registers: a cluster holds the row
-        else tier = 3;
+        // FP32 rows of more than 16384 columns: two passes per row, the second from the L2, measured faster than the
+        // row in registers (5.1 against 4.4 TB/s at [4096,20480], 5.1 against 4.8 at [8192,32768]); 16-bit rows stay in
+        // registers up to 65536 columns (3.9 TB/s either way at [4096,65536])
+        else if (nvec <= 1024 * kMaxVecsPerThread && sizeof(T) == 2) tier = 2;
+        // beyond one block's registers: with fewer rows than SMs a cluster spreads each row over several SMs
+        else if (nvec > 1024 * kMaxVecsPerThread && a.rows < info.sm_count && nvec <= 8 * 1024 * kMaxVecsPerThread) tier = 6;
+        else tier = 8;
+    }
+    if (tier == 8) {
+        KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "layernorm: the reread tier needs 16-byte aligned rows");
+        // two rows per block at a time, gamma / beta loaded once for both: measured faster from 512 KB per row
+        // (FP32 [512,131072]: 4.1 against 3.6 TB/s; [1024,65536]: 4.2 against 4.5)
+        const bool pair = k.rows_per_warp == 2 || (k.rows_per_warp == 0 && (long long)a.cols * (long long)sizeof(T) >= (512ll << 10));
+        int block = k.block;
+        if (block == 0) block = nvec <= 1024 * 5 ? 256 : (nvec <= 1024 * kMaxVecsPerThread ? 512 : 1024);
+        if (block == 256) return pair ? launch_reread<T, 256, true>(a, k.grid_cap, info.sm_count, s) : launch_reread<T, 256, false>(a, k.grid_cap, info.sm_count, s);
+        if (block == 512) return pair ? launch_reread<T, 512, true>(a, k.grid_cap, info.sm_count, s) : launch_reread<T, 512, false>(a, k.grid_cap, info.sm_count, s);
+        return pair ? launch_reread<T, 1024, true>(a, k.grid_cap, info.sm_count, s) : launch_reread<T, 1024, false>(a, k.grid_cap, info.sm_count, s);
     }
     if (tier == 6) {
         KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "layernorm: the cluster tier needs 16-byte aligned rows");

@@ -1,6 +1,8 @@
 // C-ABI launcher of the row softmax: picks the tier and the launch geometry from the runtime shape.
 #include "row_launch.h"
 
+#include <algorithm>
+
 #include "../nn_operators/softmax/softmax.h"
 #include "../nn_operators/softmax/softmax_16bit.h"
 
@@ -50,6 +52,22 @@ int launch_block_prefetch(const float *in, float *out, long long rows, int cols,
     const int per_sm = smem <= 100 * 1024 && kThreads <= 512 ? 2 : 1;
     const long long cap = grid_cap > 0 ? grid_cap : (long long)sm_count * per_sm;
     return ko::launch_overlapped(kernel, ko::clamp_grid(rows, cap), (unsigned)kThreads, smem, s, in, out, rows, cols, status);
+}
+
+// one row per block, read twice (the second time from the L2); blocks per SM: as many as fit, fewer when the rows in
+// flight would not fit in `l2_budget` bytes
+template <int kThreads>
+int launch_reread(const float *in, float *out, long long rows, int cols, long long grid_cap, int sm_count, cudaStream_t s) {
+    auto kernel = ko::softmax_reread_kernel<4, kThreads>;
+    long long cap = grid_cap;
+    if (cap <= 0) {
+        int per_sm = 0;
+        KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+        const long long l2_budget = 80ll << 20;
+        const long long fit = l2_budget / ((long long)cols * 4 * sm_count);
+        cap = (long long)sm_count * std::max(1ll, std::min<long long>(per_sm, fit));
+    }
+    return ko::launch_overlapped(kernel, ko::clamp_grid(rows, cap), (unsigned)kThreads, 0, s, in, out, rows, cols);
 }
 
 // one row per cluster of `c` blocks; a block holds up to 8 vectors per thread.  256-thread blocks when the slice
@@ -124,7 +142,8 @@ int dispatch_rows(int nvec, int slots, const float *in, float *out, long long ro
 #undef KO_GO
 }
 
-// FP16 / BF16 rows: warp tier up to 2048 columns, block tier up to 32768, stream tier for the rest
+// FP16 / BF16 rows: warp tier up to 2048 columns, block tier up to 32768, two passes per row beyond; scalar
+// stream tier for rows that cannot be moved in 16-byte vectors
 template <typename T>
 int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStream_t s) {
     KO_REQUIRE(rows >= 0 && cols >= 0, KO_ERR_INVALID_ARG, "softmax: negative shape [%lld, %d]", (long long)rows, cols);
@@ -155,6 +174,11 @@ int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStre
         if (nvec <= 1024 * 2) return block(ko::softmax16_block_kernel<T, 2, 1024>, 1024);
         return block(ko::softmax16_block_kernel<T, 4, 1024>, 1024);
     }
+    if (vec_ok) {
+        // beyond one block's registers: two passes per row, the second from the L2
+        auto kernel = ko::softmax16_reread_kernel<T, 2, 1024>;
+        return ko::launch_overlapped(kernel, ko::clamp_grid(rows, info.sm_count), 1024u, 0, s, in, out, (long long)rows, (int)cols);
+    }
     ko::softmax16_stream_kernel<T><<<ko::clamp_grid(rows, (long long)info.sm_count * 8), 256, 0, s>>>(in, out, rows, cols);
     KO_CHECK_LAUNCH("softmax16_stream_kernel");
     return KO_OK;
@@ -180,7 +204,7 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
     if (rows == 0 || cols == 0) return KO_OK;
     KO_REQUIRE(in != nullptr && out != nullptr, KO_ERR_INVALID_ARG, "softmax: NULL pointer");
     const ko_row_knobs_t k = knobs ? *knobs : ko_row_knobs_t{};
-    KO_REQUIRE((k.tier >= 0 && k.tier <= 4) || k.tier == 6 || k.tier == 7, KO_ERR_INVALID_ARG, "softmax: unknown tier %d", k.tier);
+    KO_REQUIRE((k.tier >= 0 && k.tier <= 4) || (k.tier >= 6 && k.tier <= 8), KO_ERR_INVALID_ARG, "softmax: unknown tier %d", k.tier);
     KO_REQUIRE(k.cluster == 0 || k.cluster == 2 || k.cluster == 4 || k.cluster == 8, KO_ERR_INVALID_ARG,
                "softmax: cluster size %d not in {2,4,8}", k.cluster);
     KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
@@ -197,8 +221,17 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
         else if (nvec <= 32 * 16) tier = 1;  // measured faster than the staged tier at every benchmark shape
         else if (nvec <= 1024 * 4) tier = 2;
         else if (nvec <= 1024 * 8) tier = 7;  // beyond 16384 columns one block per SM: prefetch the next row (5.8 vs 4.4 TB/s at 32768)
-        else if (nvec <= 8 * 1024 * 8) tier = 6;  // beyond one block's registers: a cluster holds the row
-        else tier = 3;
+        // beyond one block's registers: with fewer rows than SMs a cluster spreads each row over several SMs; otherwise
+        // one block per row in two passes, the second from the L2 (5.2 against 4.2 TB/s at [1024,65536], 4.5 against
+        // 3.5 TB/s at [256,262144]; rows of any length)
+        else if (rows < info.sm_count && nvec <= 8 * 1024 * 8) tier = 6;
+        else tier = 8;
+    }
+    if (tier == 8) {
+        KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "softmax: the reread tier needs cols %% 4 == 0 and 16-byte aligned pointers");
+        if (k.block == 256) return launch_reread<256>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+        if (k.block == 512) return launch_reread<512>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+        return launch_reread<1024>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
     }
     if (tier == 6) {
         KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "softmax: the cluster tier needs cols %% 4 == 0 and 16-byte aligned pointers");

@@ -152,6 +152,22 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The same load without the wait: the registers may be read only after tmem_ld_wait().  Lets the load of the next
+// 32 columns run while the current ones are written out.
+__device__ __forceinline__ void tmem_ld_32x32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the
 // 128-byte swizzle (what the TMA load above produces): 8-row groups are 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t smem_addr) {
@@ -174,11 +190,20 @@ __host__ __device__ constexpr uint32_t make_idesc(int fmt, int m, int n) {
 // tile order: groups of kGroupM tile-rows, tile-columns fastest inside a group's rows
 constexpr int kGroupM = 8;
 __device__ __forceinline__ void tile_coords(long long t, int tiles_m, int tiles_n, int &tm, int &tn) {
+    // 32-bit division whenever the tile index allows: the 64-bit one is emulated, a few hundred nanoseconds on the
+    // single thread that issues the MMAs, at every tile boundary
     const long long per_group = (long long)kGroupM * tiles_n;
-    const int group = (int)(t / per_group);
+    int group, in_group;
+    if (t <= 0x7fffffffLL) {
+        const unsigned tt = (unsigned)t, pg = (unsigned)per_group;
+        group = (int)(tt / pg);
+        in_group = (int)(tt - (unsigned)group * pg);
+    } else {
+        group = (int)(t / per_group);
+        in_group = (int)(t % per_group);
+    }
     const int first_m = group * kGroupM;
     const int rows_in_group = min(kGroupM, tiles_m - first_m);
-    const int in_group = (int)(t % per_group);
     tm = first_m + in_group % rows_in_group;
     tn = in_group / rows_in_group;
 }
@@ -306,10 +331,9 @@ __device__ __forceinline__ void epilogue_block(const CUtensorMap *map_d, const G
     if constexpr (kTmaStore) {
         // row = lane, 8 chunks of 16 B, chunk j stored at j ^ (row & 7): conflict-free, and exactly the 128-byte
         // swizzle the store's tensor map undoes
-#pragma unroll 1
-        for (int c0 = 0; c0 < bn; c0 += 32, ++store_seq) {
-            float v[32];
-            tmem_ld_32x32(t_row + c0, v);
+        // two register sets: the load of the next 32 columns is in flight while these are written out
+        uint32_t ra[32], rb[32];
+        auto write_out = [&](const uint32_t (&r)[32], int c0) {
             const uint32_t box = warp_boxes + (store_seq % kBoxes) * box_bytes;
             if (lane == 0) bulk_wait_group_read<kBoxes - 1>();  // the store issued from this box kBoxes chunks ago has read it
             __syncwarp();
@@ -317,8 +341,8 @@ __device__ __forceinline__ void epilogue_block(const CUtensorMap *map_d, const G
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const uint32_t dst = box + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
-                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]),
-                                 "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(r[4 * j]), "r"(r[4 * j + 1]),
+                                 "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
                                  : "memory");
                 }
             } else {
@@ -328,8 +352,10 @@ __device__ __forceinline__ void epilogue_block(const CUtensorMap *map_d, const G
                 for (int j = 0; j < 4; ++j) {
                     const uint32_t dst = box + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
-                                 "r"(pack16(v[8 * j], v[8 * j + 1], p.out_fmt)), "r"(pack16(v[8 * j + 2], v[8 * j + 3], p.out_fmt)),
-                                 "r"(pack16(v[8 * j + 4], v[8 * j + 5], p.out_fmt)), "r"(pack16(v[8 * j + 6], v[8 * j + 7], p.out_fmt))
+                                 "r"(pack16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]), p.out_fmt)),
+                                 "r"(pack16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]), p.out_fmt)),
+                                 "r"(pack16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]), p.out_fmt)),
+                                 "r"(pack16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]), p.out_fmt))
                                  : "memory");
                 }
             }
@@ -341,6 +367,19 @@ __device__ __forceinline__ void epilogue_block(const CUtensorMap *map_d, const G
                 // skipped, but still closes a (then empty) group so that the box rotation holds
                 if (row_base < p.M && col < p.N) tma_store_2d(map_d, col, row_base, box);
                 bulk_commit_group();
+            }
+            ++store_seq;
+        };
+        tmem_ld_32x32_issue(t_row, ra);
+#pragma unroll 1
+        for (int c0 = 0; c0 < bn; c0 += 64) {
+            tmem_ld_wait();
+            if (c0 + 32 < bn) tmem_ld_32x32_issue(t_row + c0 + 32, rb);
+            write_out(ra, c0);
+            if (c0 + 32 < bn) {
+                tmem_ld_wait();
+                if (c0 + 64 < bn) tmem_ld_32x32_issue(t_row + c0 + 64, ra);
+                write_out(rb, c0 + 32);
             }
         }
     } else {

@@ -650,6 +650,130 @@ __device__ __forceinline__ void layernorm_cluster_tier(const T *in, T *out, long
 }
 
 // ---------------------------------------------------------------------------------------------
+// reread tier: one row per thread block, two passes, the second one served by the L2
+// ---------------------------------------------------------------------------------------------
+// For rows longer than one block's registers when there are enough rows to fill every SM several times.  Pass 1
+// streams the row once (lines marked evict-last): each thread turns every chunk of kUnroll vectors into an exact
+// (count, mean, M2) triple -- mean first, then squared deviations from it, as the block tier does -- and merges it
+// into its running triple (Chan); the block merges the threads' triples.  Pass 2 reads the row again, from the L2
+// as long as the rows in flight (one per block) fit there, normalises and writes.  No block waits for another.
+// Statistics of one row for the reread tier: block-wide (count, mean, M2), every thread gets the result.
+template <typename T, int kUnroll>
+__device__ __forceinline__ Welford reread_row_stats(const typename RowIo<T>::Raw *x_v, int nvec, uint64_t keep, float *s_exchange) {
+    using Io = RowIo<T>;
+    using Raw = typename Io::Raw;
+    constexpr int kPer = Io::kPerVec;
+    const int step = (int)blockDim.x * kUnroll;
+    Welford run{0.f, 0.f, 0.f};
+    for (int base = 0; base < nvec; base += step) {
+        Raw raw[kUnroll];
+        int have = 0;
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const int v = base + (int)threadIdx.x + (int)blockDim.x * j;
+            if (v < nvec) {
+                raw[j] = ld_keep(x_v + v, keep);
+                ++have;
+            } else {
+                raw[j] = Raw{};
+            }
+        }
+        if (have == 0) continue;
+        float x[kUnroll][kPer];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            Io::unpack(raw[j], x[j]);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) sum += x[j][e];  // padded vectors are zero
+        }
+        Welford c;
+        c.n = (float)(have * kPer);
+        c.mean = sum / c.n;
+        c.m2 = 0.f;
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            float part = 0.f;
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                const float d = x[j][e] - c.mean;
+                part = fmaf(d, d, part);
+            }
+            c.m2 += j < have ? part : 0.f;
+        }
+        run = welford_merge(run, c);
+    }
+    return block_allreduce_welford(run, s_exchange);
+}
+
+// kPair: a block takes two consecutive rows at a time -- statistics of both first, then one joint second pass in
+// which a gamma / beta vector is loaded once for both rows (the second pass of an affine row is bound by its three
+// loads per output vector, all from the L2; pairing makes that two).
+template <typename T, int kStatUnroll, int kUnroll, bool kPair>
+__device__ __forceinline__ void layernorm_reread_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                      const T *gamma, const T *beta, int ddof, float *s_exchange) {
+    using Io = RowIo<T>;
+    using Raw = typename Io::Raw;
+    constexpr int kPer = Io::kPerVec;
+    constexpr int kRows = kPair ? 2 : 1;
+    const int nvec = cols / kPer;
+    const int step = (int)blockDim.x * kUnroll;
+    const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma);
+    const Raw *beta_v = reinterpret_cast<const Raw *>(beta);
+    const uint64_t keep = l2_keep_policy();
+    for (long long row = (long long)blockIdx.x * kRows; row < rows; row += (long long)gridDim.x * kRows) {
+        const Raw *x_v = reinterpret_cast<const Raw *>(in) + row * nvec;
+        Raw *y_v = reinterpret_cast<Raw *>(out) + row * nvec;
+        const bool second = kPair && row + 1 < rows;
+        float mean[kRows], rstd[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            if (r == 0 || second) {
+                const Welford w = reread_row_stats<T, kStatUnroll>(x_v + (long long)r * nvec, nvec, keep, s_exchange);
+                mean[r] = w.mean;
+                rstd[r] = rstd_from(w, cols, ddof, eps);
+            } else {
+                mean[r] = 0.f;
+                rstd[r] = 0.f;
+            }
+        }
+        for (int base = 0; base < nvec; base += step) {
+            Raw raw[kRows][kUnroll];
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = base + (int)threadIdx.x + (int)blockDim.x * j;
+                if (v < nvec) {
+                    raw[0][j] = ld_stream(x_v + v);
+                    if (kPair && second) raw[kRows - 1][j] = ld_stream(x_v + nvec + v);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = base + (int)threadIdx.x + (int)blockDim.x * j;
+                if (v >= nvec) continue;
+                if (!kPair) {
+                    st_stream(y_v + v, normalise_vector<T>(raw[0][j], mean[0], rstd[0], gamma_v, beta_v, v));
+                } else {
+                    float g[kPer], b[kPer], x[kPer], y[kPer];
+#pragma unroll
+                    for (int e = 0; e < kPer; ++e) { g[e] = 1.f; b[e] = 0.f; }
+                    if (gamma_v) Io::unpack(__ldg(gamma_v + v), g);
+                    if (beta_v) Io::unpack(__ldg(beta_v + v), b);
+#pragma unroll
+                    for (int r = 0; r < kRows; ++r) {
+                        if (r == 1 && !second) continue;
+                        Io::unpack(raw[r][j], x);
+#pragma unroll
+                        for (int e = 0; e < kPer; ++e) y[e] = fmaf((x[e] - mean[r]) * rstd[r], g[e], b[e]);
+                        st_stream(y_v + (long long)r * nvec + v, Io::pack(y));
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // stream tier: any cols / alignment; per-thread running Welford, two passes over global memory
 // ---------------------------------------------------------------------------------------------
 template <typename T>
@@ -721,6 +845,14 @@ __global__ void __launch_bounds__(kThreads) layernorm_cluster_kernel(const T *in
     __shared__ __align__(8) WelfordMailbox s_mail;
     layernorm_cluster_tier<T, kVecs>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange, s_part, use_mailbox ? &s_mail : nullptr,
                                      status);
+}
+template <typename T, int kStatUnroll, int kUnroll, int kThreads, bool kPair>
+__global__ void __launch_bounds__(kThreads) layernorm_reread_kernel(const T *in, T *out, long long rows, int cols, float eps,
+                                                                    const T *gamma, const T *beta, int ddof) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    __shared__ float s_exchange[96];
+    layernorm_reread_tier<T, kStatUnroll, kUnroll, kPair>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
 }
 template <typename T>
 __global__ void __launch_bounds__(256) layernorm_stream_kernel(const T *in, T *out, long long rows, int cols, float eps,

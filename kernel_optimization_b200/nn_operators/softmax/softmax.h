@@ -443,6 +443,66 @@ __device__ __forceinline__ void softmax_cluster_tier(const float *in, float *out
 }
 
 // ---------------------------------------------------------------------------------------------
+// reread tier: one row per thread block, two passes, the second one served by the L2
+// ---------------------------------------------------------------------------------------------
+// For rows longer than one block's registers when there are enough rows to fill every SM several times: pass 1
+// streams the row once and keeps only a running (max, sum) pair per thread (online softmax: the sum is rescaled when the
+// maximum grows), marking the lines evict-last; pass 2 reads the row again -- from the L2, as long as the rows in
+// flight (one per block) fit there -- and writes the result.  HBM sees the row once in each direction, no block waits
+// for another, and blocks drift apart so that some are in their read-only pass while others write.
+template <int kUnroll>
+__device__ __forceinline__ void softmax_reread_tier(const float *in, float *out, long long rows, int cols, float *s_exchange) {
+    const int nvec = cols >> 2;
+    const int step = (int)blockDim.x * kUnroll;
+    const uint64_t keep = l2_keep_policy();
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4 *x4 = reinterpret_cast<const float4 *>(in) + row * nvec;
+        float4 *y4 = reinterpret_cast<float4 *>(out) + row * nvec;
+        float m = kNegInf, s = 0.f;
+        for (int base = 0; base < nvec; base += step) {
+            float4 x[kUnroll];
+            float cm = kNegInf;
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = base + (int)threadIdx.x + (int)blockDim.x * j;
+                x[j] = v < nvec ? ld_keep(x4 + v, keep) : neg_inf4();
+                cm = fmaxf(cm, max4(x[j]));
+            }
+            const float grown = fmaxf(m, cm);
+            if (grown != kNegInf) {  // a chunk of nothing but -inf adds nothing
+                const float neg = -grown * kLog2e;
+                float cs = 0.f;
+#pragma unroll
+                for (int j = 0; j < kUnroll; ++j) cs += exp_shifted4(x[j], neg);
+                s = fmaf(s, exp2_approx(fmaf(m, kLog2e, neg)), cs);  // m = -inf: 2^(-inf) = 0 and s is still 0
+                m = grown;
+            }
+        }
+        const float row_max = block_allreduce<true>(m, s_exchange);
+        const float neg = -row_max * kLog2e;
+        s = m == kNegInf ? 0.f : s * exp2_approx(fmaf(m, kLog2e, neg));
+        const float inv = rcp_approx(block_allreduce<false>(s, s_exchange));
+        for (int base = 0; base < nvec; base += step) {
+            float4 x[kUnroll];
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = base + (int)threadIdx.x + (int)blockDim.x * j;
+                if (v < nvec) x[j] = ld_stream(x4 + v);
+            }
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = base + (int)threadIdx.x + (int)blockDim.x * j;
+                if (v < nvec) {
+                    exp_shifted4(x[j], neg);
+                    scale4(x[j], inv);
+                    st_stream(y4 + v, x[j]);
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // stream tier: any cols, any alignment; three passes over global memory
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void softmax_stream_tier(const float *in, float *out, long long rows, int cols,
@@ -510,6 +570,13 @@ __global__ void __launch_bounds__(kThreads) softmax_cluster_prefetch_kernel(cons
     __shared__ __align__(8) ClusterMailbox s_mail;
     softmax_cluster_tier<kVecs, true>(in, out, rows, cols, s_exchange, s_part, reinterpret_cast<float4 *>(ko_row_buffer), &s_bar, status,
                                       use_mailbox ? &s_mail : nullptr);
+}
+template <int kUnroll, int kThreads>
+__global__ void __launch_bounds__(kThreads) softmax_reread_kernel(const float *in, float *out, long long rows, int cols) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    __shared__ float s_exchange[33];
+    softmax_reread_tier<kUnroll>(in, out, rows, cols, s_exchange);
 }
 __global__ void __launch_bounds__(256) softmax_stream_kernel(const float *in, float *out, long long rows, int cols) {
     __shared__ float s_exchange[33];

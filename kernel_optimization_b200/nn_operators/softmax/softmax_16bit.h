@@ -13,6 +13,7 @@
 //   warp tier   a row over a group of 8, 16 or 32 lanes, up to 8 vectors (64 elements) per lane,
 //               two rows per lane group in flight; columns a multiple of 8, up to 2048
 //   block tier  one row per block of 256 or 1024 threads, up to 4 vectors per thread (32768 columns)
+//   reread tier one row per block in two passes, the second from the L2: rows beyond 32768 columns
 //   stream tier any column count and alignment, scalar accesses, three passes
 #pragma once
 
@@ -172,6 +173,78 @@ __global__ void __launch_bounds__(kThreads) softmax16_block_kernel(const T *in, 
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[j][e] *= inv;
                 st_stream(out_v + row * nvec + v, Io::pack(x[j]));
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// reread tier: one row per block in two passes, the second served by the L2 (see softmax_reread_tier)
+// ---------------------------------------------------------------------------------------------
+template <typename T, int kUnroll, int kThreads>
+__global__ void __launch_bounds__(kThreads) softmax16_reread_kernel(const T *in, T *out, long long rows, int cols) {
+    using Io = Half8<T>;
+    __shared__ float s_exchange[33];
+    const int nvec = cols >> 3;
+    constexpr int kStep = kThreads * kUnroll;
+    const uint64_t keep = l2_keep_policy();
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint4 *x_v = reinterpret_cast<const uint4 *>(in) + row * nvec;
+        uint4 *y_v = reinterpret_cast<uint4 *>(out) + row * nvec;
+        float m = kNegInf, s = 0.f;
+        for (int base = 0; base < nvec; base += kStep) {
+            uint4 raw[kUnroll];
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = base + (int)threadIdx.x + kThreads * j;
+                raw[j] = v < nvec ? ld_keep(x_v + v, keep) : uint4{0u, 0u, 0u, 0u};
+            }
+            float x[kUnroll][8];
+            float cm = kNegInf;
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = base + (int)threadIdx.x + kThreads * j;
+                Io::unpack(raw[j], x[j]);
+                if (v >= nvec) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x[j][e] = kNegInf;
+                }
+                cm = fmaxf(cm, max8(x[j]));
+            }
+            const float grown = fmaxf(m, cm);
+            if (grown != kNegInf) {  // a chunk of nothing but -inf adds nothing
+                const float neg = -grown * kLog2e;
+                float cs = 0.f;
+#pragma unroll
+                for (int j = 0; j < kUnroll; ++j) cs += exp_shifted8(x[j], neg);
+                s = fmaf(s, exp2_approx(fmaf(m, kLog2e, neg)), cs);
+                m = grown;
+            }
+        }
+        const float row_max = block_allreduce<true>(m, s_exchange);
+        const float neg = -row_max * kLog2e;
+        s = m == kNegInf ? 0.f : s * exp2_approx(fmaf(m, kLog2e, neg));
+        const float inv = rcp_approx(block_allreduce<false>(s, s_exchange));
+        for (int base = 0; base < nvec; base += kStep) {
+            uint4 raw[kUnroll];
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = base + (int)threadIdx.x + kThreads * j;
+                if (v < nvec) raw[j] = ld_stream(x_v + v);
+            }
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = base + (int)threadIdx.x + kThreads * j;
+                if (v < nvec) {
+                    float x[8];
+                    Io::unpack(raw[j], x);
+                    exp_shifted8(x, neg);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x[e] *= inv;
+                    st_stream(y_v + v, Io::pack(x));
+                }
             }
         }
     }

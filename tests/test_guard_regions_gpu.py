@@ -71,6 +71,7 @@ F32_TIERS = {  # tier -> (rows, cols) it accepts among the shapes above
     4: lambda r, c: c % 4 == 0 and c <= 2048 and c >= 64,
     6: lambda r, c: c % 4 == 0 and c >= 4096,
     7: lambda r, c: c % 4 == 0 and c <= 32768,
+    8: lambda r, c: c % 4 == 0,
 }
 
 
@@ -89,26 +90,27 @@ def test_softmax_f32_stays_inside_its_buffers(cuda, lib, oracle, rows, cols, tie
     assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= 1e-6
 
 
-@pytest.mark.parametrize("tier", [0, 1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("tier", [0, 1, 2, 3, 4, 5, 6, 8, 82])
 @pytest.mark.parametrize("rows,cols", ROW_SHAPES_F32)
 def test_layernorm_f32_stays_inside_its_buffers(cuda, lib, oracle, rows, cols, tier):
     from kernel_optimization_b200.native import RowKnobs
 
     ok = {0: True, 1: cols % 4 == 0 and cols <= 2048, 2: cols % 4 == 0 and cols <= 32768, 3: True,
-          4: cols % 4 == 0 and 64 <= cols <= 2048, 5: cols % 4 == 0 and cols <= 16384, 6: cols % 4 == 0 and cols >= 4096}[tier]
+          4: cols % 4 == 0 and 64 <= cols <= 2048, 5: cols % 4 == 0 and cols <= 16384, 6: cols % 4 == 0 and cols >= 4096,
+          8: cols % 4 == 0, 82: cols % 4 == 0}[tier]
     if not ok:
         pytest.skip("shape outside this tier")
     x = oracle.fill_normal((rows, cols), 1, 0, 0.0, 1.0)
     g, b = oracle.fill_uniform((cols,), 1, 1, 0.5, 1.5), oracle.fill_normal((cols,), 1, 2, 0.0, 0.1)
     gin, gout, gg, gb = Guarded.of(cuda, x), Guarded(cuda, x.nbytes), Guarded.of(cuda, g), Guarded.of(cuda, b)
-    rc = lib.ko_layernorm_f32_tuned(gin.ptr(), gout.ptr(), rows, cols, 1e-5, gg.ptr(), gb.ptr(), 0, RowKnobs(tier=tier) if tier else None,
-                                    _stream(cuda))
+    knobs = RowKnobs(tier=8, rows_per_warp=2) if tier == 82 else (RowKnobs(tier=tier) if tier else None)  # 82: rows in pairs
+    rc = lib.ko_layernorm_f32_tuned(gin.ptr(), gout.ptr(), rows, cols, 1e-5, gg.ptr(), gb.ptr(), 0, knobs, _stream(cuda))
     _finish(cuda, lib, rc, gin, gout, gg, gb)
     y = gout.numpy(np.float32, (rows, cols))
     assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-5, g, b)) <= 1e-5
 
 
-ROW_SHAPES_16 = [(1, 8), (7, 100), (9, 136), (33, 256), (100, 768), (17, 2048), (9, 2056), (5, 4096), (3, 20000), (2, 40008)]
+ROW_SHAPES_16 = [(1, 8), (7, 100), (9, 136), (33, 256), (100, 768), (17, 2048), (9, 2056), (5, 4096), (3, 20000), (2, 40008), (150, 65544)]
 
 
 @pytest.mark.parametrize("kind", ["f16", "bf16"])

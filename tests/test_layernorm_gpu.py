@@ -122,6 +122,38 @@ def test_cluster_tier_merges_triples_through_dsmem(cuda, lib, oracle, cluster):
     assert oracle.max_rel_err(got, want) <= 2.0 ** -8 * 1.01
 
 
+@pytest.mark.parametrize("block", [0, 256, 512, 1024])
+@pytest.mark.parametrize("pair", [1, 2])
+def test_reread_tier_two_passes_per_row(cuda, lib, oracle, block, pair):
+    """tier 8: statistics in a first pass (chunked exact triples merged Chan-wise), the row again from the L2 in the
+    second; rows_per_warp = 2 takes two rows at a time and loads gamma / beta once for both (an odd row count leaves
+    the last block with one row).  Rows shorter than a step, rows ending inside a step, more rows than blocks."""
+    for rows, cols in ((5, 4), (3, 4100), (7, 40000), (301, 36864), (3, 262144), (2, 524288 + 8)):
+        x, g, b = _inputs(oracle, rows, cols)
+        x += 3.0  # a mean well away from zero: a one-pass sum of squares would lose digits here
+        y = _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=8, block=block, rows_per_warp=pair)
+        assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+        assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=8, block=block, rows_per_warp=pair, grid_cap=3))
+        y = _run_f32(cuda, lib, x, 1e-5, None, None, 1, tier=8, block=block, rows_per_warp=pair)
+        assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-5, None, None, 1)) <= TOL_REL
+    x, g, b = _inputs(oracle, 5, 65536 + 16)
+    xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
+    got = oracle.from_bf16_bits(_run_bf16(cuda, lib, xb, 1e-12, gb, bb, tier=8, block=block, rows_per_warp=pair))
+    want = oracle.layernorm_f64(oracle.from_bf16_bits(xb), 1e-12, oracle.from_bf16_bits(gb), oracle.from_bf16_bits(bb))
+    assert oracle.max_rel_err(got, want) <= 2.0 ** -8 * 1.01
+
+
+def test_long_rows_default_to_the_reread_tier_or_the_cluster_tier(cuda, lib, oracle):
+    """FP32 rows beyond 16384 columns take two passes per row unless there are fewer rows than SMs and a cluster can
+    hold the row; rows of any length are served."""
+    for rows, cols, knobs in ((3, 65536, dict(tier=6)), (200, 40000, dict(tier=8)), (300, 20480, dict(tier=8, block=256)),
+                              (2, 600000, dict(tier=8)), (150, 131072, dict(tier=8, rows_per_warp=2))):
+        x, g, b = _inputs(oracle, rows, cols)
+        y = _run_f32(cuda, lib, x, 1e-12, g, b)
+        assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+        assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, **knobs))
+
+
 def test_f32_stream_tier_and_staged_ring_wrap(cuda, lib, oracle):
     x, g, b = _inputs(oracle, 23, 768)
     assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=3), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL

@@ -96,6 +96,32 @@ def test_prefetching_block_tier_matches_the_block_tier(cuda, lib, oracle, rows, 
     assert lib.ko_poll_device_status() == 0
 
 
+@pytest.mark.parametrize("block", [0, 256, 512, 1024])
+def test_reread_tier_two_passes_per_row(cuda, lib, oracle, block):
+    """tier 8: one row per block in two passes (online max / sum, then the row again from the L2).  Rows shorter than
+    one step of the block, rows that end inside a step, more rows than blocks, and fully masked stretches (-inf) that
+    span whole chunks of a thread."""
+    for rows, cols in ((5, 4), (3, 4100), (7, 40000), (300, 36864), (2, 262144), (3, 524288 + 8), (150, 65536)):
+        x = oracle.fill_normal((rows, cols), 0, 0, 0.0, 2.0)
+        if cols >= 40000:
+            x[0, : cols // 2] = -np.inf      # the first half of a row contributes nothing
+            x[-1, 17:cols - 5] = -np.inf     # almost everything masked
+        y = _run(cuda, lib, x, tier=8, block=block)
+        assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS and oracle.max_rowsum_err(y) <= TOL_ROWSUM
+        assert np.array_equal(y, _run(cuda, lib, x, tier=8, block=block, grid_cap=3))  # three blocks take all rows
+    assert lib.ko_poll_device_status() == 0
+
+
+def test_long_rows_default_to_the_reread_tier_or_the_cluster_tier(cuda, lib, oracle):
+    """Beyond 32768 columns: fewer rows than SMs -> one row per cluster; otherwise two passes per row.  Same results
+    as the forced tiers, and rows of any length are served (the cluster tier stops at 262144 columns)."""
+    for rows, cols, tier in ((3, 65536, 6), (200, 40000, 8), (2, 300000, 8)):
+        x = oracle.fill_normal((rows, cols), 0, 0, 0.0, 2.0)
+        y = _run(cuda, lib, x)
+        assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS
+        assert np.array_equal(y, _run(cuda, lib, x, tier=tier))
+
+
 def test_cluster_tier_with_and_without_prefetch(cuda, lib, oracle):
     """Slices beyond 4096 vectors per block are prefetched into shared memory (stages=1 turns that off): same bits."""
     for rows, cols in ((5, 65536), (40, 40000), (3, 262144), (300, 36864)):
