@@ -658,8 +658,10 @@ CASES = {
     "softmax_c5_shard": "softmax FP32 [196608,512] with the causal -1e4 pattern (1/8 of benchmark config 5)",
     "layernorm_bf16_c5_shard": "LayerNorm BF16 [32768,4096] (1/8 of benchmark config 5)",
     "softmax_long_rows": "softmax FP32 [2048,32768]: one row per block in registers, the next row prefetched by a bulk copy",
-    "softmax_cluster_rows": "softmax FP32 [256,131072]: one row per cluster of 4 blocks, (max, sum) pairs exchanged through DSMEM mailboxes",
-    "layernorm_cluster_rows": "LayerNorm FP32 [256,131072] affine: one row per cluster of 4 blocks, Welford triples exchanged through DSMEM mailboxes",
+    "softmax_cluster_rows": "softmax FP32 [256,131072], cluster tier forced: one row per cluster of 4 blocks, (max, sum) pairs exchanged through DSMEM mailboxes",
+    "layernorm_cluster_rows": "LayerNorm FP32 [256,131072] affine, cluster tier forced: one row per cluster of 4 blocks, Welford triples exchanged through DSMEM mailboxes",
+    "softmax_reread_rows": "softmax FP32 [1024,65536]: one row per block in two passes, the second served by the L2 (the default for such rows)",
+    "layernorm_reread_rows": "LayerNorm FP32 [1024,131072] affine: two rows per block at a time, two passes, gamma / beta loaded once per pair (the default for such rows)",
     "layernorm_c2": "LayerNorm FP32 [16384,768] affine (benchmark config 2), 8 rotating buffer sets",
     "softmax_c1": "softmax FP32 [196608,128] (benchmark config 1), 4 rotating buffer sets",
     "gemm_bf16_ffn_pair": "BF16 GEMM 16384x3072x768 on the two-SM kernel (tcgen05 cta_group::2)",
@@ -696,9 +698,11 @@ def run_case(args):
         else:
             launch = lambda: native.check(lib.ko_gemm_bf16_f32(M, N, K, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s()), name)  # noqa: E731
         work, unit = 2.0 * M * N * K, "TFLOP/s"
-    elif name in ("softmax_cluster_rows", "layernorm_cluster_rows", "layernorm_c2", "softmax_c1"):
+    elif name in ("softmax_cluster_rows", "layernorm_cluster_rows", "softmax_reread_rows", "layernorm_reread_rows", "layernorm_c2", "softmax_c1"):
         rows, cols, nsets = {"softmax_cluster_rows": (256, 131072, 3), "layernorm_cluster_rows": (256, 131072, 3),
+                             "softmax_reread_rows": (1024, 65536, 2), "layernorm_reread_rows": (1024, 131072, 2),
                              "layernorm_c2": (LN_ROWS, LN_COLS, 8), "softmax_c1": (SOFTMAX_ROWS, SOFTMAX_COLS, 4)}[name]
+        knobs = native.RowKnobs(tier=6) if "cluster" in name else None
         host = ko.fill_normal((rows, cols), 1, 0, 0.0, 1.0)
         xs = [torch.from_numpy(host).to(dev) for _ in range(nsets)]
         ys = [torch.empty_like(xs[0]) for _ in range(nsets)]
@@ -710,9 +714,10 @@ def run_case(args):
             j = turn[0] % nsets
             turn[0] += 1
             if name.startswith("softmax"):
-                native.check(lib.ko_softmax_f32(xs[j].data_ptr(), ys[j].data_ptr(), rows, cols, s()), name)
+                native.check(lib.ko_softmax_f32_tuned(xs[j].data_ptr(), ys[j].data_ptr(), rows, cols, knobs, s()), name)
             else:
-                native.check(lib.ko_layernorm_f32(xs[j].data_ptr(), ys[j].data_ptr(), rows, cols, LN_EPS, g.data_ptr(), b.data_ptr(), 0, s()), name)
+                native.check(lib.ko_layernorm_f32_tuned(xs[j].data_ptr(), ys[j].data_ptr(), rows, cols, LN_EPS, g.data_ptr(), b.data_ptr(), 0,
+                                                        knobs, s()), name)
         work, unit = 2.0 * rows * cols * 4, "GB/s"
     elif name == "softmax_long_rows":
         rows, cols = 2048, 32768
