@@ -316,6 +316,11 @@ int ko_probe_composed_rowop(int op, const float *in, float *out, int64_t rows, i
 int ko_probe_gemm_tensor_core_template(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
                                        const uint16_t *C, uint16_t *D, void *stream);
 
+/* One warp computes D[16,8] = A[16,K] * B[K,8] + C with the reference's warp-level helpers in the call shapes of its
+ * warp loop (nn_operators/gemm/tensor_core_gemm.h:207, :218, :231): LDMatrix<2,false> for A, LDMatrix<1,true> for B,
+ * MMA<16,8,8> with FP16 accumulation.  FP16 storage, everything row-major, K a multiple of 8 in [8, 64]. */
+int ko_probe_mma_ldmatrix(const uint16_t *A, const uint16_t *B, const uint16_t *C, uint16_t *D, int32_t K, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -447,3 +447,42 @@ extern "C" int ko_probe_gemm_tensor_core_template(int64_t M, int64_t N, int64_t 
     KO_CHECK_LAUNCH("gemm<GemmKernelTensorCore>");
     return KO_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// MMA<16,8,8> and LDMatrix<2,false> / <1,true> as the reference's warp loop uses them
+// (nn_operators/gemm/tensor_core_gemm.h:207, :218, :231): one warp, D[16,8] = A[16,K] * B[K,8] + C, FP16 everywhere,
+// K a multiple of 8 up to 64; A, C, D row-major, B row-major [K,8]
+// ---------------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(32) probe_mma_ldmatrix_kernel(const half *A, const half *B, const half *C, half *D, int K) {
+    __shared__ __align__(16) half s_a[16 * 64];
+    __shared__ __align__(16) half s_b[64 * 8];
+    const int lane = threadIdx.x;
+    for (int i = lane; i < 16 * K; i += 32) s_a[(i / K) * 64 + i % K] = A[i];
+    for (int i = lane; i < K * 8; i += 32) s_b[i] = B[i];
+    __syncwarp();
+    const int row = lane >> 2, col = (lane & 3) * 2;
+    uint32_t acc[2];
+    acc[0] = *reinterpret_cast<const uint32_t *>(C + row * 8 + col);
+    acc[1] = *reinterpret_cast<const uint32_t *>(C + (row + 8) * 8 + col);
+    for (int k0 = 0; k0 < K; k0 += 8) {
+        uint32_t frag_a[2], frag_b;
+        // lanes 0..15 address the 16 rows of the A tile (8 halves = 16 bytes each); the other lanes' addresses are ignored
+        LDMatrix<2, false>()(frag_a, s_a + (lane % 16) * 64 + k0);
+        // lanes 0..7 address the 8 k-rows of the B tile; transposed on the way in: the "col" operand of the MMA
+        LDMatrix<1, true>()(&frag_b, s_b + (k0 + lane % 8) * 8);
+        MMA<16, 8, 8>()(frag_a, &frag_b, acc, acc);
+    }
+    *reinterpret_cast<uint32_t *>(D + row * 8 + col) = acc[0];
+    *reinterpret_cast<uint32_t *>(D + (row + 8) * 8 + col) = acc[1];
+}
+}  // namespace
+
+extern "C" int ko_probe_mma_ldmatrix(const uint16_t *A, const uint16_t *B, const uint16_t *C, uint16_t *D, int32_t K, void *stream) {
+    KO_REQUIRE(A && B && C && D, KO_ERR_INVALID_ARG, "probe: NULL operand");
+    KO_REQUIRE(K >= 8 && K <= 64 && K % 8 == 0, KO_ERR_INVALID_ARG, "probe: K must be a multiple of 8 in [8, 64], got %d", K);
+    probe_mma_ldmatrix_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const half *>(A), reinterpret_cast<const half *>(B), reinterpret_cast<const half *>(C), reinterpret_cast<half *>(D), K);
+    KO_CHECK_LAUNCH("probe_mma_ldmatrix_kernel");
+    return KO_OK;
+}

@@ -73,6 +73,7 @@ PROTOTYPES = {
     "ko_probe_limits": (_int, [_vp, _vp, _vp, _vp, _vp]),
     "ko_probe_welford": (_int, [_int, _vp, _i64, _i32, _vp, _int, _vp]),
     "ko_probe_gemm_tensor_core_template": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "ko_probe_mma_ldmatrix": (_int, [_vp, _vp, _vp, _vp, _i32, _vp]),
     "ko_probe_composed_rowop": (_int, [_int, _vp, _vp, _i64, _i32, _f32, _vp, _vp, _int, _vp]),
 }
 

@@ -23,6 +23,59 @@
 #include "../../common/common.h"
 #include "tensor_core_gemm.h"
 
+// ---------------------------------------------------------------------------------------------
+// Warp-level primitives under the reference's names (nn_operators/gemm/tensor_core_gemm.h:30-99): MMA<16,8,8> is one
+// mma.sync m16n8k8 with FP16 operands AND FP16 accumulation, LDMatrix<N, transpose> one ldmatrix of N 8x8 tiles of
+// 16-bit elements.  Same call operators (untyped pointers to the lane's fragment registers / to the lane's row in shared
+// memory).  They are the legacy tensor path, kept for code written against the reference's header; nothing in this
+// library's own GEMMs uses them (those run on tcgen05).  Fragment layouts are PTX's: for m16n8k8, lane l holds A rows
+// l/4 and l/4+8, columns 2(l%4)..+1; B row (k) 2(l%4)..+1, column l/4; C and D rows l/4 and l/4+8, columns 2(l%4)..+1.
+// ---------------------------------------------------------------------------------------------
+template <int M, int N, int K>
+struct MMA;
+
+template <>
+struct MMA<16, 8, 8> {
+    __device__ __forceinline__ void operator()(void *ptr_A, void *ptr_B, void *ptr_C, void *ptr_D) const {
+        const uint32_t *a = static_cast<const uint32_t *>(ptr_A);
+        const uint32_t b = *static_cast<const uint32_t *>(ptr_B);
+        const uint32_t c0 = static_cast<const uint32_t *>(ptr_C)[0], c1 = static_cast<const uint32_t *>(ptr_C)[1];  // C may alias D
+        uint32_t d0, d1;
+        asm volatile("mma.sync.aligned.m16n8k8.row.col.f16.f16.f16.f16 {%0, %1}, {%2, %3}, {%4}, {%5, %6};"
+                     : "=r"(d0), "=r"(d1)
+                     : "r"(a[0]), "r"(a[1]), "r"(b), "r"(c0), "r"(c1));
+        static_cast<uint32_t *>(ptr_D)[0] = d0;
+        static_cast<uint32_t *>(ptr_D)[1] = d1;
+    }
+};
+
+template <int N, bool transpose>
+struct LDMatrix {
+    static_assert(N == 1 || N == 2 || N == 4, "ldmatrix loads one, two or four 8x8 tiles");
+    // data_ptr: N 32-bit registers of this lane; smem_ptr: the 16-byte row this lane addresses (lanes 0..8N-1 count)
+    __device__ __forceinline__ void operator()(void *data_ptr, void *smem_ptr) const {
+        uint32_t *d = static_cast<uint32_t *>(data_ptr);
+        const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem_ptr));
+        if constexpr (N == 1) {
+            if constexpr (transpose) asm volatile("ldmatrix.sync.aligned.x1.trans.m8n8.shared.b16 {%0}, [%1];" : "=r"(d[0]) : "r"(addr));
+            else asm volatile("ldmatrix.sync.aligned.x1.m8n8.shared.b16 {%0}, [%1];" : "=r"(d[0]) : "r"(addr));
+        } else if constexpr (N == 2) {
+            if constexpr (transpose)
+                asm volatile("ldmatrix.sync.aligned.x2.trans.m8n8.shared.b16 {%0, %1}, [%2];" : "=r"(d[0]), "=r"(d[1]) : "r"(addr));
+            else asm volatile("ldmatrix.sync.aligned.x2.m8n8.shared.b16 {%0, %1}, [%2];" : "=r"(d[0]), "=r"(d[1]) : "r"(addr));
+        } else {
+            if constexpr (transpose)
+                asm volatile("ldmatrix.sync.aligned.x4.trans.m8n8.shared.b16 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                             : "r"(addr));
+            else
+                asm volatile("ldmatrix.sync.aligned.x4.m8n8.shared.b16 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                             : "r"(addr));
+        }
+    }
+};
+
 template <typename ElementA_, typename ElementB_, typename ElementC_, typename ThreadBlockShape_, typename WarpShape_,
           typename InstructionShape_, int AlignmentA, int AlignmentB, int AlignmentC>
 struct GemmKernelTensorCore {

@@ -77,6 +77,27 @@ __global__ void every_helper_name(float *data, half *hdata, int32_t *idata) {
     idata[0] = best;
 }
 
+// the reference's warp-level tensor-core helpers (nn_operators/gemm/tensor_core_gemm.h:30-99), in the call shapes of
+// its warp loop (:207, :218, :231)
+__global__ void tensor_core_helper_names(half *tile_a, half *tile_b, half *out) {
+    __shared__ __align__(16) half s_a[16 * 8];
+    __shared__ __align__(16) half s_b[8 * 8];
+    const int lane_id = threadIdx.x % 32;
+    for (int i = lane_id; i < 16 * 8; i += 32) s_a[i] = tile_a[i];
+    for (int i = lane_id; i < 8 * 8; i += 32) s_b[i] = tile_b[i];
+    __syncwarp();
+    AlignedArray<uint32_t, 2> warp_frag_a, warp_frag_accum;
+    uint32_t warp_frag_b;
+    warp_frag_accum.clear();
+    LDMatrix<2, false>()(&warp_frag_a, s_a + (lane_id % 16) * 8);
+    LDMatrix<1, true>()(&warp_frag_b, s_b + (lane_id % 8) * 8);
+    MMA<16, 8, 8>()(&warp_frag_a, &warp_frag_b, &warp_frag_accum, &warp_frag_accum);
+    uint32_t one, two[2];
+    LDMatrix<1, false>()(&one, s_b + (lane_id % 8) * 8);
+    LDMatrix<2, true>()(two, s_a + (lane_id % 16) * 8);
+    *reinterpret_cast<uint32_t *>(out + lane_id * 2) = warp_frag_accum[0] ^ one ^ two[0];
+}
+
 // the operator templates and their launch wrappers, with the reference drivers' template arguments
 void launch_syntax(float *in, float *out, cudaStream_t stream) {
     using Softmax = SoftMaxWarpImpl<float, 4, 196608, 128>;
@@ -95,5 +116,8 @@ void launch_syntax(float *in, float *out, cudaStream_t stream) {
     shape::GemmCoord problem(1024, 1024, 1024);
     gemm<Gemm><<<256, Gemm::thread_per_block, Gemm::smem_total_size_in_bytes, stream>>>(problem, in, in, nullptr, out);
     (void)problem.mk(); (void)problem.kn(); (void)problem.mn(); (void)problem.mnk(); (void)problem.to_string();
+    using Tc = GemmKernelTensorCore<half, half, half, shape::GemmShape<128, 128, 32>, shape::GemmShape<64, 64, 32>, shape::GemmShape<16, 8, 8>, 8, 8, 8>;
+    half *h_in = reinterpret_cast<half *>(in), *h_out = reinterpret_cast<half *>(out);
+    gemm<Tc><<<64, Tc::thread_per_block, Tc::smem_total_size_in_bytes, stream>>>(problem, h_in, h_in, nullptr, h_out);
     checkCudaErrors(cudaGetLastError());
 }

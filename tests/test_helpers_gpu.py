@@ -317,3 +317,21 @@ def test_reference_tensor_core_template_through_its_launch_syntax(cuda, lib, ora
         want = want + oracle.from_f16_bits(cb).astype(np.float64)
     assert np.isfinite(got).all()
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+
+
+@pytest.mark.parametrize("K", [8, 16, 64])
+def test_reference_mma_and_ldmatrix_names(cuda, lib, oracle, K):
+    """MMA<16,8,8> (mma.sync, FP16 accumulation) fed by LDMatrix<2,false> / LDMatrix<1,true> as in the reference's warp loop.
+    Small integers: every product and partial sum is exact in FP16, so D must equal A @ B + C exactly."""
+    rng = np.random.default_rng(K)
+    a = rng.integers(-4, 5, size=(16, K)).astype(np.float32)
+    b = rng.integers(-4, 5, size=(K, 8)).astype(np.float32)
+    c = rng.integers(-8, 9, size=(16, 8)).astype(np.float32)
+    dev = lambda m: cuda.from_numpy(oracle.to_f16_bits(m).view(np.int16)).cuda()  # noqa: E731
+    ad, bd, cd = dev(a), dev(b), dev(c)
+    dd = cuda.full((16, 8), 0x7E00, dtype=cuda.int16, device="cuda")  # NaN
+    _ok(lib, lib.ko_probe_mma_ldmatrix(ad.data_ptr(), bd.data_ptr(), cd.data_ptr(), dd.data_ptr(), K, _stream(cuda)))
+    cuda.cuda.synchronize()
+    got = oracle.from_f16_bits(dd.cpu().numpy().view(np.uint16))
+    assert np.array_equal(got, a @ b + c)
+    assert lib.ko_probe_mma_ldmatrix(ad.data_ptr(), bd.data_ptr(), cd.data_ptr(), dd.data_ptr(), 12, _stream(cuda)) != 0

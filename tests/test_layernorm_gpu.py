@@ -134,6 +134,7 @@ def test_reread_tier_two_passes_per_row(cuda, lib, oracle, block, pair):
         y = _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=8, block=block, rows_per_warp=pair)
         assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
         assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=8, block=block, rows_per_warp=pair, grid_cap=3))
+        assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, inplace=True, tier=8, block=block, rows_per_warp=pair))
         y = _run_f32(cuda, lib, x, 1e-5, None, None, 1, tier=8, block=block, rows_per_warp=pair)
         assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-5, None, None, 1)) <= TOL_REL
     x, g, b = _inputs(oracle, 5, 65536 + 16)

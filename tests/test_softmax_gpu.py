@@ -109,6 +109,7 @@ def test_reread_tier_two_passes_per_row(cuda, lib, oracle, block):
         y = _run(cuda, lib, x, tier=8, block=block)
         assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS and oracle.max_rowsum_err(y) <= TOL_ROWSUM
         assert np.array_equal(y, _run(cuda, lib, x, tier=8, block=block, grid_cap=3))  # three blocks take all rows
+        assert np.array_equal(y, _run(cuda, lib, x, inplace=True, tier=8, block=block))  # out == in: a thread rewrites only what it read
     assert lib.ko_poll_device_status() == 0
 
 
