@@ -56,6 +56,8 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
  * 64 / 128 / 256 = columns of D per 128-row tile, 512 = the 256 x 256 tile (two 128-row halves per CTA share each B tile),
  * all with equal column tiles; 1024 / 1280 = the 128- / 256-row tile with N cut into uneven column tiles of at most 256
  * columns that fill the last round of CTAs (KO_ERR_SHAPE when that gains nothing; 0 uses them when they gain);
+ * 2048 = the two-SM kernel (tcgen05 cta_group::2: a pair of CTAs per 256 x 256 tile, either B layout), 2304 = the same
+ * with uneven column tiles (column-major B only);
  * store_mode: 0 = choose, 1 = TMA-store epilogue (KO_ERR_SHAPE when not possible), 2 = direct stores */
 int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
                      const void *C, void *D, int bn, int store_mode, void *stream);

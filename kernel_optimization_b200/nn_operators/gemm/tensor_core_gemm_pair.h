@@ -188,7 +188,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     const uint32_t leader_full = map_to_cluster_rank(full_bar(s), 0);
                     const uint32_t dst = ring + s * Cfg::kStageBytes;
                     tma_load_2d_pair(dst, &map_a, kb * kBK, tm * kTileM + (int)rank * kBM, leader_full);
-                    tma_load_2d_pair(dst + Cfg::kBytesA, b_map, kb * kBK, col0 + (int)rank * half, leader_full);
+                    if (!p.b_row_major) {
+                        tma_load_2d_pair(dst + Cfg::kBytesA, b_map, kb * kBK, col0 + (int)rank * half, leader_full);
+                    } else {
+                        // row-major B: this CTA's 128 columns as two boxes of 64 K-rows x 64 columns (MN-major operand)
+#pragma unroll
+                        for (int nb = 0; nb < BN / 128; ++nb)
+                            tma_load_2d_pair(dst + Cfg::kBytesA + nb * 8192, &map_b, col0 + (int)rank * (BN / 2) + nb * 64, kb * kBK,
+                                             leader_full);
+                    }
                 }
             }
         }
@@ -204,7 +212,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 int tm, tn, col0, bn;
                 tile_of(p, t, tiles_m, tiles_n, tm, tn);
                 column_tile<BN>(p, tn, col0, bn);
-                const uint32_t idesc = make_idesc(p.fmt, kTileM, bn);
+                const uint32_t idesc = make_idesc(p.fmt, kTileM, bn) | (p.b_row_major ? 1u << 16 : 0u);  // bit 16: B is MN-major
                 const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
                 if (!mbar_wait_remote(acc_free_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
@@ -218,7 +226,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
                         const uint64_t da = smem_desc_k_major_sw128(a_addr + k * kUmmaK * 2);
-                        const uint64_t db = smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
+                        const uint64_t db = p.b_row_major ? smem_desc_mn_major_sw128(b_addr + k * 2048)
+                                                          : smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
                         umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     // the stage is reusable once these MMAs have read it (in both CTAs: the commit tracks both SMs); the

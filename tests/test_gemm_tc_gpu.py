@@ -333,6 +333,24 @@ def test_two_sm_kernel_gives_the_bits_of_the_one_sm_kernel(cuda, lib, oracle, ki
 
 
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (128, 64, 64), (100, 40, 56), (129, 264, 136), (1000, 520, 200), (2048, 1024, 512),
+                                   (5000, 304, 320), (20000, 1032, 72)])
+def test_two_sm_kernel_with_row_major_b(cuda, lib, oracle, kind, M, N, K):
+    """Row-major B [K,N] on the two-SM kernel: each CTA loads its 128 columns as two MN-major boxes.  Same bits as the
+    column-major two-SM call on the transposed matrix and as the single-CTA row-major call; FP32 and 16-bit D."""
+    to_bits, from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 3, 0)), to_bits(oracle.fill_uniform((N, K), 3, 1))
+    b_rm = np.ascontiguousarray(bb.T)
+    base = _run(cuda, lib, kind, ab, bb, bn=2048)
+    assert np.array_equal(_run(cuda, lib, kind, ab, b_rm, bn=2048, b_row_major=True), base)
+    assert np.array_equal(_run(cuda, lib, kind, ab, b_rm, bn=256, b_row_major=True), base)
+    assert np.array_equal(_run(cuda, lib, kind, ab, b_rm, bn=2048, b_row_major=True, store_mode=2), base)
+    assert np.array_equal(_run(cuda, lib, kind, ab, b_rm, bn=2048, b_row_major=True, out16=True), _run(cuda, lib, kind, ab, bb, bn=256, out16=True))
+    err = oracle.rel_frobenius(base, oracle.gemm_tn_f64(from_bits(ab), from_bits(bb)))
+    assert err <= TOL_FRO and err <= tight(K)
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
 @pytest.mark.parametrize("M,N,K", [(4096, 4096, 128), (19000, 1032, 64), (38000, 520, 64)])
 def test_two_sm_kernel_with_uneven_column_tiles(cuda, lib, oracle, kind, M, N, K):
     to_bits, _from_bits = _bits(oracle, kind)
