@@ -444,6 +444,30 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
         native.check(lib.ko_poll_device_status(), "ko_poll_device_status")
 
+    # ---- long rows (every rank its own rows): the tiers beyond one block's registers, with a parity spot check
+    long_rows = {}
+    if not args.skip_gemm:
+        lr_rows, lr_cols, lr_sets = 1024, 65536, 2
+        lr_bytes = 2.0 * lr_rows * lr_cols * 4
+        x_h = ko.fill_normal((lr_rows, lr_cols), 5, 0, 0.0, 2.0, elem_offset=rank * lr_rows * lr_cols)
+        g_h, b_h = ko.fill_uniform((lr_cols,), 5, 1, 0.5, 1.5), ko.fill_normal((lr_cols,), 5, 2, 0.0, 0.1)
+        xs = [torch.from_numpy(x_h).to(dev) for _ in range(lr_sets)]
+        ys = [torch.empty_like(xs[0]) for _ in range(lr_sets)]
+        gd, bd = torch.from_numpy(g_h).to(dev), torch.from_numpy(b_h).to(dev)
+        ms = timed(lambda i: native.check(lib.ko_softmax_f32(xs[i % lr_sets].data_ptr(), ys[i % lr_sets].data_ptr(), lr_rows, lr_cols,
+                                                             stream()), "ko_softmax_f32"), 20, 3)
+        err = oracle.max_abs_err(ys[0][:4].cpu().numpy(), oracle.softmax_f64(x_h[:4])) if rank == 0 else None
+        long_rows["softmax_f32_1024x65536"] = {"gbs": lr_bytes * world / (ms * 1e-3) / 1e9, "us": ms * 1e3,
+                                               "of_peak_per_gpu": lr_bytes / (ms * 1e-3) / 1e9 / hbm_peak, "max_abs_4_rows": err}
+        ms = timed(lambda i: native.check(lib.ko_layernorm_f32(xs[i % lr_sets].data_ptr(), ys[i % lr_sets].data_ptr(), lr_rows, lr_cols,
+                                                               LN_EPS, gd.data_ptr(), bd.data_ptr(), 0, stream()), "ko_layernorm_f32"), 20, 3)
+        err = oracle.max_rel_err(ys[0][:4].cpu().numpy(), oracle.layernorm_f64(x_h[:4], LN_EPS, g_h, b_h)) if rank == 0 else None
+        long_rows["layernorm_f32_1024x65536"] = {"gbs": lr_bytes * world / (ms * 1e-3) / 1e9, "us": ms * 1e3,
+                                                 "of_peak_per_gpu": lr_bytes / (ms * 1e-3) / 1e9 / hbm_peak, "max_rel_4_rows": err}
+        long_rows["note"] = ("rows longer than one block's registers: one row per block in two passes, the second served by the L2; "
+                             "2 rotating buffer sets of 537 MB per rank")
+        del xs, ys, gd, bd
+
     # ---- the reference's own kernels, recompiled for sm_100a (test-only library; informational)
     ref_rows = None
     ref_path = os.path.join(ROOT, "oracle", "_ref", "libko_ref_kernels.so")
@@ -519,7 +543,7 @@ def run_gpu_arm(args):
                     "note": "us / gbs: median of 5 batches of --steps launches back to back (consecutive launches overlap their "
                             "ramps through programmatic dependent launch); us_per_launch_*: single launches with an event between them"},
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks.summary(),
-            "parity": parity, "gemm": gemm, "scaled": scaled, "reference_kernels_on_b200": ref_rows,
+            "parity": parity, "gemm": gemm, "long_rows": long_rows, "scaled": scaled, "reference_kernels_on_b200": ref_rows,
         }
         emit(line)
     rig.close()
