@@ -794,7 +794,7 @@ SWEEP_ROW_SHAPES = {
                 "f16": [(196608, 128), (49152, 1024)], "bf16": [(196608, 512), (49152, 1024), (2048, 131072)]},
     "layernorm": {"f32": [(16384, 768), (49152, 1024), (8192, 4096), (4096, 20480), (512, 65536), (1024, 65536), (2048, 131072),
                           (64, 131072)],
-                  "f16": [(16384, 768), (32768, 4096)], "bf16": [(16384, 768), (32768, 4096), (2048, 131072)]},
+                  "f16": [(16384, 768), (32768, 4096)], "bf16": [(16384, 768), (32768, 4096), (32768, 5120), (2048, 131072)]},
 }
 SWEEP_SGEMM = [512, 1024, 2048, 4096]
 # (the largest case last: its seconds at the power cap would otherwise colour the entries that follow it)

@@ -59,28 +59,40 @@ int launch_block_vecs(int vecs, const Args<T> &a, long long grid_cap, cudaStream
     return launch_block<T, 8, kThreads>(a, grid_cap, s);
 }
 
-template <typename T, int kVecs, int kThreads>
+template <typename T, int kVecs, int kThreads, int kRing>
 int launch_resident(const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
     // persistent blocks: exactly as many as the device holds at once, so that no block waits for a slot and the
     // rows are dealt evenly (more blocks than that would run as a partly filled second wave)
     const bool affine = a.gamma || a.beta;
+    auto with_affine = ko::layernorm_resident_kernel<T, kVecs, kThreads, true, kRing>;
+    auto without = ko::layernorm_resident_kernel<T, kVecs, kThreads, false, kRing>;
     int per_sm = 0;
-    if (affine) KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ko::layernorm_resident_kernel<T, kVecs, kThreads, true>, kThreads, 0));
-    else KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ko::layernorm_resident_kernel<T, kVecs, kThreads, false>, kThreads, 0));
+    if (affine) KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, with_affine, kThreads, 0));
+    else KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, without, kThreads, 0));
     const long long cap = grid_cap > 0 ? grid_cap : (long long)sm_count * (per_sm > 0 ? per_sm : 1);
     const unsigned grid = ko::clamp_grid(a.rows, cap);
     if (affine)
-        return ko::launch_overlapped(ko::layernorm_resident_kernel<T, kVecs, kThreads, true>, grid, kThreads, 0, s, a.in, a.out,
-                                     (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
-    return ko::launch_overlapped(ko::layernorm_resident_kernel<T, kVecs, kThreads, false>, grid, kThreads, 0, s, a.in, a.out,
-                                 (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+        return ko::launch_overlapped(with_affine, grid, kThreads, 0, s, a.in, a.out, (long long)a.rows, a.cols, a.eps, a.gamma, a.beta,
+                                     a.ddof);
+    return ko::launch_overlapped(without, grid, kThreads, 0, s, a.in, a.out, (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+}
+
+// ring: rows in flight into shared memory per block (cp.async) instead of one row into registers; the depth that fits
+// the 48 KB of static shared memory
+template <typename T, int kVecs, int kThreads>
+int launch_resident_ring(bool ring, const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
+    constexpr int kDepth = kThreads * kVecs <= 512 ? 3 : (kThreads * kVecs <= 1024 ? 2 : 0);
+    if constexpr (kDepth > 0) {
+        if (ring) return launch_resident<T, kVecs, kThreads, kDepth>(a, grid_cap, sm_count, s);
+    }
+    return launch_resident<T, kVecs, kThreads, 0>(a, grid_cap, sm_count, s);
 }
 
 template <typename T, int kThreads>
-int launch_resident_vecs(int vecs, const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
-    if (vecs <= 1) return launch_resident<T, 1, kThreads>(a, grid_cap, sm_count, s);
-    if (vecs <= 2) return launch_resident<T, 2, kThreads>(a, grid_cap, sm_count, s);
-    return launch_resident<T, 4, kThreads>(a, grid_cap, sm_count, s);
+int launch_resident_vecs(int vecs, bool ring, const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
+    if (vecs <= 1) return launch_resident_ring<T, 1, kThreads>(ring, a, grid_cap, sm_count, s);
+    if (vecs <= 2) return launch_resident_ring<T, 2, kThreads>(ring, a, grid_cap, sm_count, s);
+    return launch_resident_ring<T, 4, kThreads>(ring, a, grid_cap, sm_count, s);
 }
 
 // one row per cluster of `c` blocks of 1024 threads, up to 8 vectors per thread
@@ -219,11 +231,17 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         }
         KO_REQUIRE(nvec <= threads * 4, KO_ERR_SHAPE, "layernorm: %d threads hold at most %d vectors per row", threads, threads * 4);
         const int per_thread = (nvec + threads - 1) / threads;
+        // The next rows of a block in flight into shared memory (cp.async) instead of one row into registers: measured
+        // faster whenever the threads are not exactly filled with two vectors each (BF16 [32768,5120] 191 -> 108 us,
+        // [32768,3072] 81 -> 66, [32768,8192] 231 -> 187; FP32 [16384,2560] 68 -> 61) and slower when they are (BF16
+        // [32768,4096] 96 -> 100 us, FP32 [16384,4096] 91 -> 95).  stages: 0 = that rule, 1 = registers, 3 = ring.
+        const bool full = nvec == threads * per_thread;
+        const bool ring = k.stages == 3 || (k.stages == 0 && (!full || (sizeof(T) == 2 && per_thread >= 3)));
         switch (threads) {
-            case 128: return launch_resident_vecs<T, 128>(per_thread, a, k.grid_cap, info.sm_count, s);
-            case 256: return launch_resident_vecs<T, 256>(per_thread, a, k.grid_cap, info.sm_count, s);
-            case 512: return launch_resident_vecs<T, 512>(per_thread, a, k.grid_cap, info.sm_count, s);
-            case 1024: return launch_resident_vecs<T, 1024>(per_thread, a, k.grid_cap, info.sm_count, s);
+            case 128: return launch_resident_vecs<T, 128>(per_thread, ring, a, k.grid_cap, info.sm_count, s);
+            case 256: return launch_resident_vecs<T, 256>(per_thread, ring, a, k.grid_cap, info.sm_count, s);
+            case 512: return launch_resident_vecs<T, 512>(per_thread, ring, a, k.grid_cap, info.sm_count, s);
+            case 1024: return launch_resident_vecs<T, 1024>(per_thread, ring, a, k.grid_cap, info.sm_count, s);
             default: return ko::fail(KO_ERR_INVALID_ARG, "layernorm: resident tier needs 128/256/512/1024 threads, got %d", threads);
         }
     }
@@ -251,6 +269,12 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         }
         while (threads < 1024 && nvec > threads * kMaxVecsPerThread) threads *= 2;
         const int per_thread = (nvec + threads - 1) / threads;
+        // The next rows of a block in flight into shared memory (cp.async) instead of one row into registers: measured
+        // faster whenever the threads are not exactly filled with two vectors each (BF16 [32768,5120] 191 -> 108 us,
+        // [32768,3072] 81 -> 66, [32768,8192] 231 -> 187; FP32 [16384,2560] 68 -> 61) and slower when they are (BF16
+        // [32768,4096] 96 -> 100 us, FP32 [16384,4096] 91 -> 95).  stages: 0 = that rule, 1 = registers, 3 = ring.
+        const bool full = nvec == threads * per_thread;
+        const bool ring = k.stages == 3 || (k.stages == 0 && (!full || (sizeof(T) == 2 && per_thread >= 3)));
         switch (threads) {
             case 128: return launch_block_vecs<T, 128>(per_thread, a, k.grid_cap, s);
             case 256: return launch_block_vecs<T, 256>(per_thread, a, k.grid_cap, s);

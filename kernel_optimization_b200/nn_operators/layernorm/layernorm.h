@@ -468,9 +468,15 @@ __device__ __forceinline__ float block_sum_fixed(float v, float *s_exchange, int
 // sums its registers, one block-wide sum gives the row mean, then the squared deviations from that
 // mean are summed the same way.  (Merging per-thread (n, mean, M2) triples gives the same numbers but
 // costs about 100 instructions per thread and row, which dominates when a thread holds 16 values.)
-template <typename T, int kVecs, int kThreads, bool kAffine>
+// kRing > 0: the block's next kRing rows are in flight into shared memory (cp.async, 16 bytes per thread and vector)
+// instead of one row into registers.  A thread copies exactly the vectors it will consume, so the ring needs no block
+// barrier -- only the thread's own cp.async.wait_group -- and works like extra registers that hold loads in flight:
+// with 3 blocks of 256 threads per SM, 3 rows of 8 KB each in flight per block are 72 KB per SM instead of 24 KB.
+// ring: kRing * kThreads * kVecs vectors of 16 bytes.
+template <typename T, int kVecs, int kThreads, bool kAffine, int kRing = 0>
 __device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, long long rows, int cols, float eps,
-                                                        const T *gamma, const T *beta, int ddof, float *s_exchange) {
+                                                        const T *gamma, const T *beta, int ddof, float *s_exchange,
+                                                        uint4 *ring = nullptr) {
     using Io = RowIo<T>;
     using Raw = typename Io::Raw;
     constexpr int kPer = Io::kPerVec, kPairsPerVec = kPer / 2;
@@ -510,12 +516,43 @@ __device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, lon
             else next[j] = Raw{};
         }
     };
-    fetch(blockIdx.x);
+    // ring slot `slot`, vector j of this thread; one commit group per row (empty groups keep the count uniform)
+    auto ring_fetch = [&](long long row, int slot) {
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int v = threadIdx.x + kThreads * j;
+            if (row < rows && v < nvec) {
+                const uint32_t dst = smem_u32(ring + (slot * kVecs + j) * kThreads + threadIdx.x);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(in_v + row * nvec + v) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int slot = 0;
+    if constexpr (kRing > 0) {
+#pragma unroll
+        for (int i = 0; i < kRing; ++i) ring_fetch(blockIdx.x + (long long)i * gridDim.x, i);
+    } else {
+        fetch(blockIdx.x);
+    }
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
         f32x2 x2[kVecs * kPairsPerVec];
+        if constexpr (kRing > 0) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");  // this row's copies have landed
 #pragma unroll
-        for (int j = 0; j < kVecs; ++j) Io::unpack_pairs(next[j], x2 + j * kPairsPerVec);
-        fetch(row + gridDim.x);  // in flight while this row is processed
+            for (int j = 0; j < kVecs; ++j) {
+                const int v = threadIdx.x + kThreads * j;
+                uint4 r = uint4{0u, 0u, 0u, 0u};
+                if (v < nvec) r = ring[(slot * kVecs + j) * kThreads + threadIdx.x];
+                Io::unpack_pairs(*reinterpret_cast<const Raw *>(&r), x2 + j * kPairsPerVec);
+            }
+            ring_fetch(row + (long long)kRing * gridDim.x, slot);  // refill the slot just read (same thread: no hazard)
+            slot = slot + 1 == kRing ? 0 : slot + 1;
+        } else {
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) Io::unpack_pairs(next[j], x2 + j * kPairsPerVec);
+            fetch(row + gridDim.x);  // in flight while this row is processed
+        }
 
         f32x2 acc = pair_of(0.f, 0.f);
 #pragma unroll
@@ -828,13 +865,14 @@ __global__ void __launch_bounds__(kThreads) layernorm_block_kernel(const T *in, 
     grid_dependency_wait();
     layernorm_block_tier<T, kVecs>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
 }
-template <typename T, int kVecs, int kThreads, bool kAffine>
+template <typename T, int kVecs, int kThreads, bool kAffine, int kRing = 0>
 __global__ void __launch_bounds__(kThreads) layernorm_resident_kernel(const T *in, T *out, long long rows, int cols,
                                                                       float eps, const T *gamma, const T *beta, int ddof) {
     __shared__ float s_exchange[96];
+    __shared__ __align__(16) uint4 s_ring[kRing > 0 ? kRing * kThreads * kVecs : 1];
     grid_launch_dependents();
     grid_dependency_wait();
-    layernorm_resident_tier<T, kVecs, kThreads, kAffine>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
+    layernorm_resident_tier<T, kVecs, kThreads, kAffine, kRing>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange, s_ring);
 }
 template <typename T, int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) layernorm_cluster_kernel(const T *in, T *out, long long rows, int cols, float eps,

@@ -108,6 +108,32 @@ def test_f32_resident_tier(cuda, lib, oracle, block):
             assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, gg, bb)) <= TOL_REL
 
 
+@pytest.mark.parametrize("block", [0, 128, 256, 512, 1024])
+def test_resident_tier_row_ring_gives_the_bits_of_the_register_prefetch(cuda, lib, oracle, block):
+    """stages = 3: the block's next rows are in flight into shared memory (cp.async, every thread copies the vectors it
+    will consume); stages = 1: one row prefetched into registers.  Same arithmetic, so the same bits -- for rows that
+    fill the threads exactly, partly, or leave whole warps without data; more rows than ring slots per block (the
+    slots are refilled), fewer rows than slots, FP32 and BF16."""
+    for rows, cols in ((19, 768), (300, 2048), (7, 2052), (40, 4096), (33, 2560), (50, 3072), (2, 1024), (101, 520)):
+        if block and cols // 4 > block * 4:
+            continue
+        x, g, b = _inputs(oracle, rows, cols)
+        for cap in (0, 3):
+            ring = _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=5, block=block, stages=3, grid_cap=cap)
+            assert oracle.max_rel_err(ring, oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+            assert np.array_equal(ring, _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=5, block=block, stages=1, grid_cap=cap))
+        assert np.array_equal(_run_f32(cuda, lib, x, 1e-12, g, b, 0, inplace=True, tier=5, block=block, stages=3), ring)
+    for rows, cols in ((21, 4096), (50, 5120), (33, 3072), (9, 8192), (300, 2304)):
+        if block and cols // 8 > block * 4:
+            continue
+        x, g, b = _inputs(oracle, rows, cols)
+        xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
+        ring = _run_bf16(cuda, lib, xb, 1e-12, gb, bb, tier=5, block=block, stages=3, grid_cap=2)
+        assert np.array_equal(ring, _run_bf16(cuda, lib, xb, 1e-12, gb, bb, tier=5, block=block, stages=1, grid_cap=2))
+        want = oracle.layernorm_f64(oracle.from_bf16_bits(xb), 1e-12, oracle.from_bf16_bits(gb), oracle.from_bf16_bits(bb))
+        assert oracle.max_rel_err(oracle.from_bf16_bits(ring), want) <= 2.0 ** -8 * 1.01
+
+
 @pytest.mark.parametrize("cluster", [0, 2, 4, 8])
 def test_cluster_tier_merges_triples_through_dsmem(cuda, lib, oracle, cluster):
     for rows, cols in ((5, 4096), (3, 40000), (37, 8192), (2, 131072), (300, 2048), (3, 1028)):
