@@ -195,11 +195,13 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         // (16 of FP32); beyond that the resident tier (row unpacked once, packed FP32 math) is faster
         // (BF16 [32768,2048]: resident tier with 128-thread blocks 46.0 us, warp tier 51.8 us; at 1024 columns they tie)
         else if (warp_ok && (sizeof(T) == 4 || nvec <= 128)) tier = 1;
-        else if (nvec <= 1024 * 4) tier = 5;
+        // (16-bit rows of more than 16384 columns would need 1024 threads with 32 unpacked values each and spill:
+        // two passes per row with 256-thread blocks instead, BF16 [3276,20480] 2.4 -> 3.6 TB/s)
+        else if (nvec <= 1024 * 4 && !(sizeof(T) == 2 && nvec > 512 * 4)) tier = 5;
         // FP32 rows of more than 16384 columns: two passes per row, the second from the L2, measured faster than the
-        // row in registers (5.1 against 4.4 TB/s at [4096,20480], 5.1 against 4.8 at [8192,32768]); 16-bit rows stay in
-        // registers up to 65536 columns (3.9 TB/s either way at [4096,65536])
-        else if (nvec <= 1024 * kMaxVecsPerThread && sizeof(T) == 2) tier = 2;
+        // row in registers (5.1 against 4.4 TB/s at [4096,20480], 5.1 against 4.8 at [8192,32768]); 16-bit rows of
+        // 49153..65536 columns stay in registers (3.9 TB/s either way at [4096,65536])
+        else if (nvec > 1024 * 6 && nvec <= 1024 * kMaxVecsPerThread && sizeof(T) == 2) tier = 2;
         // beyond one block's registers: with fewer rows than SMs a cluster spreads each row over several SMs
         else if (nvec > 1024 * kMaxVecsPerThread && a.rows < info.sm_count && nvec <= 8 * 1024 * kMaxVecsPerThread) tier = 6;
         else tier = 8;
@@ -210,7 +212,10 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         // (FP32 [512,131072]: 4.1 against 3.6 TB/s; [1024,65536]: 4.2 against 4.5)
         const bool pair = k.rows_per_warp == 2 || (k.rows_per_warp == 0 && (long long)a.cols * (long long)sizeof(T) >= (512ll << 10));
         int block = k.block;
-        if (block == 0) block = nvec <= 1024 * 5 ? 256 : (nvec <= 1024 * kMaxVecsPerThread ? 512 : 1024);
+        if (block == 0) {
+            if (sizeof(T) == 2) block = nvec <= 1024 * 6 ? 256 : 1024;  // BF16 [1365,49152]: 3.8 TB/s with 256, 3.3 with 1024
+            else block = nvec <= 1024 * 5 ? 256 : (nvec <= 1024 * kMaxVecsPerThread ? 512 : 1024);
+        }
         if (block == 256) return pair ? launch_reread<T, 256, true>(a, k.grid_cap, info.sm_count, s) : launch_reread<T, 256, false>(a, k.grid_cap, info.sm_count, s);
         if (block == 512) return pair ? launch_reread<T, 512, true>(a, k.grid_cap, info.sm_count, s) : launch_reread<T, 512, false>(a, k.grid_cap, info.sm_count, s);
         return pair ? launch_reread<T, 1024, true>(a, k.grid_cap, info.sm_count, s) : launch_reread<T, 1024, false>(a, k.grid_cap, info.sm_count, s);

@@ -142,7 +142,7 @@ int dispatch_rows(int nvec, int slots, const float *in, float *out, long long ro
 #undef KO_GO
 }
 
-// FP16 / BF16 rows: warp tier up to 2048 columns, block tier up to 32768, two passes per row beyond; scalar
+// FP16 / BF16 rows: warp tier up to 2048 columns, block tier up to 16384, two passes per row beyond; scalar
 // stream tier for rows that cannot be moved in 16-byte vectors
 template <typename T>
 int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStream_t s) {
@@ -165,19 +165,26 @@ int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStre
         if (nvec <= 128) return warp(ko::softmax16_warp_kernel<T, 4, 2, 32>, 2);
         return warp(ko::softmax16_warp_kernel<T, 8, 1, 32>, 1);
     }
-    if (vec_ok && nvec <= 1024 * 4) {
+    if (vec_ok && nvec <= 512 * 4) {
         auto block = [&](auto kernel, int threads) -> int {
             return ko::launch_overlapped(kernel, ko::clamp_grid(rows, 0), (unsigned)threads, 0, s, in, out, (long long)rows, (int)cols);
         };
         if (nvec <= 256 * 2) return block(ko::softmax16_block_kernel<T, 2, 256>, 256);
         if (nvec <= 256 * 4) return block(ko::softmax16_block_kernel<T, 4, 256>, 256);
-        if (nvec <= 1024 * 2) return block(ko::softmax16_block_kernel<T, 2, 1024>, 1024);
-        return block(ko::softmax16_block_kernel<T, 4, 1024>, 1024);
+        // threads by row bytes, as the FP32 tiers do: several blocks per SM while a row is short enough
+        // (BF16 [6553,10240] 2.3 -> 4.0 TB/s, [4096,16384] 3.1 -> 4.9 against 1024-thread blocks)
+        if (nvec <= 256 * 6) return block(ko::softmax16_block_kernel<T, 8, 256>, 256);
+        return block(ko::softmax16_block_kernel<T, 4, 512>, 512);
     }
     if (vec_ok) {
-        // beyond one block's registers: two passes per row, the second from the L2
-        auto kernel = ko::softmax16_reread_kernel<T, 2, 1024>;
-        return ko::launch_overlapped(kernel, ko::clamp_grid(rows, info.sm_count), 1024u, 0, s, in, out, (long long)rows, (int)cols);
+        // beyond 16384 columns: two passes per row, the second from the L2, in 256-thread blocks so that several rows
+        // per SM are in flight (BF16 [3276,20480] 3.0 -> 4.8 TB/s, [2048,32768] 3.8 -> 4.8 against a 1024-thread block
+        // holding the row; [1024,65536] 4.2 -> 4.5 against one 1024-thread reread block per SM)
+        auto kernel = ko::softmax16_reread_kernel<T, 4, 256>;
+        int per_sm = 1;
+        KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0));
+        return ko::launch_overlapped(kernel, ko::clamp_grid(rows, (long long)info.sm_count * (per_sm > 0 ? per_sm : 1)), 256u, 0, s, in, out,
+                                     (long long)rows, (int)cols);
     }
     ko::softmax16_stream_kernel<T><<<ko::clamp_grid(rows, (long long)info.sm_count * 8), 256, 0, s>>>(in, out, rows, cols);
     KO_CHECK_LAUNCH("softmax16_stream_kernel");

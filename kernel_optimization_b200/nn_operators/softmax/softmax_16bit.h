@@ -12,8 +12,8 @@
 //
 //   warp tier   a row over a group of 8, 16 or 32 lanes, up to 8 vectors (64 elements) per lane,
 //               two rows per lane group in flight; columns a multiple of 8, up to 2048
-//   block tier  one row per block of 256 or 1024 threads, up to 4 vectors per thread (32768 columns)
-//   reread tier one row per block in two passes, the second from the L2: rows beyond 32768 columns
+//   block tier  one row per block of 256 or 512 threads, up to 8 vectors per thread (16384 columns)
+//   reread tier one row per block in two passes, the second from the L2: rows beyond 16384 columns
 //   stream tier any column count and alignment, scalar accesses, three passes
 #pragma once
 

@@ -36,10 +36,12 @@ def _softmax(cuda, lib, kind, xb, inplace=False):
     return _bits(cuda, yd)
 
 
-# every tier and lane-group size: 8..2048 columns (warp tier), ..32768 (block tier), longer rows in two passes (reread
-# tier: a row that ends inside a step, several steps per row, more rows than blocks), odd counts (stream tier)
+# every tier and lane-group size: 8..2048 columns (warp tier), ..16384 (block tier: 256 threads with up to 4 or 8
+# vectors each, 512 with 4), longer rows in two passes (reread tier: a row that ends inside a step, several steps per
+# row, more rows than blocks), odd counts (stream tier)
 SOFTMAX_SHAPES = [(1, 8), (5, 64), (7, 128), (9, 136), (33, 256), (100, 512), (64, 1024), (17, 2048), (9, 2056), (5, 4096),
-                  (3, 8192), (3, 16384), (2, 32768), (2, 40000), (3, 262152), (200, 65536), (3, 1), (5, 7), (4, 100), (3, 1001)]
+                  (3, 8192), (5, 10248), (4, 12288), (3, 16384), (4, 16392), (2, 32768), (2, 40000), (3, 262152), (200, 65536),
+                  (3000, 20480), (3, 1), (5, 7), (4, 100), (3, 1001)]
 
 
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
