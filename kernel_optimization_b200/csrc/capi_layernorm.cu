@@ -66,25 +66,28 @@ int launch_resident(const Args<T> &a, long long grid_cap, int sm_count, cudaStre
     const bool affine = a.gamma || a.beta;
     auto with_affine = ko::layernorm_resident_kernel<T, kVecs, kThreads, true, kRing>;
     auto without = ko::layernorm_resident_kernel<T, kVecs, kThreads, false, kRing>;
+    constexpr size_t kRingBytes = (size_t)kRing * kThreads * kVecs * 16;
+    const void *fn = affine ? reinterpret_cast<const void *>(with_affine) : reinterpret_cast<const void *>(without);
+    if (kRingBytes > (48u << 10))
+        if (int st = ko::ensure_dynamic_smem(fn, kRingBytes)) return st;
     int per_sm = 0;
-    if (affine) KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, with_affine, kThreads, 0));
-    else KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, without, kThreads, 0));
+    if (affine) KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, with_affine, kThreads, kRingBytes));
+    else KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, without, kThreads, kRingBytes));
     const long long cap = grid_cap > 0 ? grid_cap : (long long)sm_count * (per_sm > 0 ? per_sm : 1);
     const unsigned grid = ko::clamp_grid(a.rows, cap);
     if (affine)
-        return ko::launch_overlapped(with_affine, grid, kThreads, 0, s, a.in, a.out, (long long)a.rows, a.cols, a.eps, a.gamma, a.beta,
-                                     a.ddof);
-    return ko::launch_overlapped(without, grid, kThreads, 0, s, a.in, a.out, (long long)a.rows, a.cols, a.eps, a.gamma, a.beta, a.ddof);
+        return ko::launch_overlapped(with_affine, grid, kThreads, kRingBytes, s, a.in, a.out, (long long)a.rows, a.cols, a.eps, a.gamma,
+                                     a.beta, a.ddof);
+    return ko::launch_overlapped(without, grid, kThreads, kRingBytes, s, a.in, a.out, (long long)a.rows, a.cols, a.eps, a.gamma, a.beta,
+                                 a.ddof);
 }
 
-// ring: rows in flight into shared memory per block (cp.async) instead of one row into registers; the depth that fits
-// the 48 KB of static shared memory
+// ring: rows in flight into shared memory per block (cp.async) instead of one row into registers: three rows while a
+// row is at most 8 KB, two beyond (up to 2 x 64 KB)
 template <typename T, int kVecs, int kThreads>
 int launch_resident_ring(bool ring, const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
-    constexpr int kDepth = kThreads * kVecs <= 512 ? 3 : (kThreads * kVecs <= 1024 ? 2 : 0);
-    if constexpr (kDepth > 0) {
-        if (ring) return launch_resident<T, kVecs, kThreads, kDepth>(a, grid_cap, sm_count, s);
-    }
+    constexpr int kDepth = kThreads * kVecs <= 512 ? 3 : 2;
+    if (ring) return launch_resident<T, kVecs, kThreads, kDepth>(a, grid_cap, sm_count, s);
     return launch_resident<T, kVecs, kThreads, 0>(a, grid_cap, sm_count, s);
 }
 
@@ -232,16 +235,22 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         int threads = k.block;
         if (threads == 0) {
             threads = nvec <= 256 ? 128 : 256;  // two vectors per thread at 2048 and 4096 columns of 16-bit data
+            // FP32 rows of 3072..4096 columns: 512 threads with at most two vectors each ([10922,3072] 5.2 -> 5.8 TB/s)
+            if (sizeof(T) == 4 && nvec >= 768) threads = 512;
             while (threads < 1024 && nvec > threads * 4) threads *= 2;
         }
         KO_REQUIRE(nvec <= threads * 4, KO_ERR_SHAPE, "layernorm: %d threads hold at most %d vectors per row", threads, threads * 4);
         const int per_thread = (nvec + threads - 1) / threads;
         // The next rows of a block in flight into shared memory (cp.async) instead of one row into registers: measured
         // faster whenever the threads are not exactly filled with two vectors each (BF16 [32768,5120] 191 -> 108 us,
-        // [32768,3072] 81 -> 66, [32768,8192] 231 -> 187; FP32 [16384,2560] 68 -> 61) and slower when they are (BF16
-        // [32768,4096] 96 -> 100 us, FP32 [16384,4096] 91 -> 95).  stages: 0 = that rule, 1 = registers, 3 = ring.
-        const bool full = nvec == threads * per_thread;
-        const bool ring = k.stages == 3 || (k.stages == 0 && (!full || (sizeof(T) == 2 && per_thread >= 3)));
+        // [32768,3072] 81 -> 66, [32768,8192] 231 -> 187; FP32 [16384,2560] 68 -> 61,
+        // [5461,6144] 5.1 -> 5.8 TB/s); with exactly two vectors per thread it measured slower (BF16 [32768,4096] 96 -> 100
+        // us, FP32 [16384,4096] 91 -> 95), as it did with four FP32 vectors in 256 threads.  stages: 0 = that rule,
+        // 1 = registers, 3 = ring.
+        const int held = per_thread <= 1 ? 1 : (per_thread <= 2 ? 2 : 4);  // vectors per thread of the instantiation
+        const bool full = nvec == threads * held;
+        const bool ring = k.stages == 3 ||
+                          (k.stages == 0 && (!full || (held == 4 && (sizeof(T) == 2 || threads >= 512))));
         switch (threads) {
             case 128: return launch_resident_vecs<T, 128>(per_thread, ring, a, k.grid_cap, info.sm_count, s);
             case 256: return launch_resident_vecs<T, 256>(per_thread, ring, a, k.grid_cap, info.sm_count, s);
@@ -276,10 +285,14 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         const int per_thread = (nvec + threads - 1) / threads;
         // The next rows of a block in flight into shared memory (cp.async) instead of one row into registers: measured
         // faster whenever the threads are not exactly filled with two vectors each (BF16 [32768,5120] 191 -> 108 us,
-        // [32768,3072] 81 -> 66, [32768,8192] 231 -> 187; FP32 [16384,2560] 68 -> 61) and slower when they are (BF16
-        // [32768,4096] 96 -> 100 us, FP32 [16384,4096] 91 -> 95).  stages: 0 = that rule, 1 = registers, 3 = ring.
-        const bool full = nvec == threads * per_thread;
-        const bool ring = k.stages == 3 || (k.stages == 0 && (!full || (sizeof(T) == 2 && per_thread >= 3)));
+        // [32768,3072] 81 -> 66, [32768,8192] 231 -> 187; FP32 [16384,2560] 68 -> 61,
+        // [5461,6144] 5.1 -> 5.8 TB/s); with exactly two vectors per thread it measured slower (BF16 [32768,4096] 96 -> 100
+        // us, FP32 [16384,4096] 91 -> 95), as it did with four FP32 vectors in 256 threads.  stages: 0 = that rule,
+        // 1 = registers, 3 = ring.
+        const int held = per_thread <= 1 ? 1 : (per_thread <= 2 ? 2 : 4);  // vectors per thread of the instantiation
+        const bool full = nvec == threads * held;
+        const bool ring = k.stages == 3 ||
+                          (k.stages == 0 && (!full || (held == 4 && (sizeof(T) == 2 || threads >= 512))));
         switch (threads) {
             case 128: return launch_block_vecs<T, 128>(per_thread, a, k.grid_cap, s);
             case 256: return launch_block_vecs<T, 256>(per_thread, a, k.grid_cap, s);

@@ -472,7 +472,7 @@ __device__ __forceinline__ float block_sum_fixed(float v, float *s_exchange, int
 // instead of one row into registers.  A thread copies exactly the vectors it will consume, so the ring needs no block
 // barrier -- only the thread's own cp.async.wait_group -- and works like extra registers that hold loads in flight:
 // with 3 blocks of 256 threads per SM, 3 rows of 8 KB each in flight per block are 72 KB per SM instead of 24 KB.
-// ring: kRing * kThreads * kVecs vectors of 16 bytes.
+// ring: kRing * kThreads * kVecs vectors of 16 bytes of (dynamic) shared memory.
 template <typename T, int kVecs, int kThreads, bool kAffine, int kRing = 0>
 __device__ __forceinline__ void layernorm_resident_tier(const T *in, T *out, long long rows, int cols, float eps,
                                                         const T *gamma, const T *beta, int ddof, float *s_exchange,
@@ -869,10 +869,10 @@ template <typename T, int kVecs, int kThreads, bool kAffine, int kRing = 0>
 __global__ void __launch_bounds__(kThreads) layernorm_resident_kernel(const T *in, T *out, long long rows, int cols,
                                                                       float eps, const T *gamma, const T *beta, int ddof) {
     __shared__ float s_exchange[96];
-    __shared__ __align__(16) uint4 s_ring[kRing > 0 ? kRing * kThreads * kVecs : 1];
+    extern __shared__ __align__(16) uint4 ko_ln_row_ring[];  // kRing * kThreads * kVecs vectors (dynamic: up to 128 KB)
     grid_launch_dependents();
     grid_dependency_wait();
-    layernorm_resident_tier<T, kVecs, kThreads, kAffine, kRing>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange, s_ring);
+    layernorm_resident_tier<T, kVecs, kThreads, kAffine, kRing>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange, ko_ln_row_ring);
 }
 template <typename T, int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) layernorm_cluster_kernel(const T *in, T *out, long long rows, int cols, float eps,
