@@ -158,22 +158,34 @@ int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStre
             const long long groups = (rows + rows_per_step - 1) / rows_per_step;
             return ko::launch_overlapped(kernel, ko::clamp_grid((groups + 7) / 8, 0), 256, 0, s, in, out, (long long)rows, (int)cols);
         };
+        // the smallest lane group x vectors per lane that holds the row: padded vectors cost as much as real ones
+        // (BF16 768 columns: 4 vectors per lane 4.8 TB/s, 3 vectors per lane 5.5; 1280 columns: 8 vectors 4.5, 5 vectors 6.4)
         if (nvec <= 8) return warp(ko::softmax16_warp_kernel<T, 1, 2, 8>, 8);
         if (nvec <= 16) return warp(ko::softmax16_warp_kernel<T, 2, 2, 8>, 8);
+        if (nvec <= 24) return warp(ko::softmax16_warp_kernel<T, 3, 1, 8>, 4);
         if (nvec <= 32) return warp(ko::softmax16_warp_kernel<T, 2, 2, 16>, 4);
-        if (nvec <= 64) return warp(ko::softmax16_warp_kernel<T, 2, 2, 32>, 2);
-        if (nvec <= 128) return warp(ko::softmax16_warp_kernel<T, 4, 2, 32>, 2);
-        return warp(ko::softmax16_warp_kernel<T, 8, 1, 32>, 1);
+        if (nvec <= 48) return warp(ko::softmax16_warp_kernel<T, 3, 1, 16>, 2);
+        if (nvec <= 64) return warp(ko::softmax16_warp_kernel<T, 2, 1, 32>, 1);
+        if (nvec <= 96) return warp(ko::softmax16_warp_kernel<T, 3, 1, 32>, 1);
+        if (nvec <= 128) return warp(ko::softmax16_warp_kernel<T, 4, 1, 32>, 1);
+        if (nvec <= 160) return warp(ko::softmax16_warp_kernel<T, 5, 1, 32>, 1);
+        if (nvec <= 192) return warp(ko::softmax16_warp_kernel<T, 6, 1, 32>, 1);
     }
+    if (vec_ok && nvec <= 128 * 2)
+        return ko::launch_overlapped(ko::softmax16_block_kernel<T, 2, 128>, ko::clamp_grid(rows, 0), 128u, 0, s, in, out, (long long)rows,
+                                     (int)cols);
     if (vec_ok && nvec <= 512 * 4) {
         auto block = [&](auto kernel, int threads) -> int {
             return ko::launch_overlapped(kernel, ko::clamp_grid(rows, 0), (unsigned)threads, 0, s, in, out, (long long)rows, (int)cols);
         };
-        if (nvec <= 256 * 2) return block(ko::softmax16_block_kernel<T, 2, 256>, 256);
+        // the smallest threads x vectors per thread that holds the row (padded vectors cost as much as real ones)
+        if (nvec <= 128 * 3) return block(ko::softmax16_block_kernel<T, 3, 128>, 128);
+        if (nvec <= 128 * 4) return block(ko::softmax16_block_kernel<T, 4, 128>, 128);
+        if (nvec <= 128 * 5) return block(ko::softmax16_block_kernel<T, 5, 128>, 128);
+        if (nvec <= 128 * 6) return block(ko::softmax16_block_kernel<T, 6, 128>, 128);
         if (nvec <= 256 * 4) return block(ko::softmax16_block_kernel<T, 4, 256>, 256);
-        // threads by row bytes, as the FP32 tiers do: several blocks per SM while a row is short enough
-        // (BF16 [6553,10240] 2.3 -> 4.0 TB/s, [4096,16384] 3.1 -> 4.9 against 1024-thread blocks)
-        if (nvec <= 256 * 6) return block(ko::softmax16_block_kernel<T, 8, 256>, 256);
+        if (nvec <= 256 * 5) return block(ko::softmax16_block_kernel<T, 5, 256>, 256);
+        if (nvec <= 256 * 6) return block(ko::softmax16_block_kernel<T, 6, 256>, 256);
         return block(ko::softmax16_block_kernel<T, 4, 512>, 512);
     }
     if (vec_ok) {
