@@ -279,10 +279,15 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
                    "softmax: the prefetching block tier needs cols %% 4 == 0, cols <= 32768 and 16-byte aligned pointers");
         if (nvec <= 512 * 4) return launch_block_prefetch<4, 512>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
         if (nvec <= 1024 * 4) return launch_block_prefetch<4, 1024>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+        if (nvec <= 1024 * 5) return launch_block_prefetch<5, 1024>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+        if (nvec <= 1024 * 6) return launch_block_prefetch<6, 1024>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
         return launch_block_prefetch<8, 1024>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
     }
     if (tier == 2) {
         KO_REQUIRE(vec_ok && nvec <= 1024 * 8, KO_ERR_SHAPE, "softmax: the block tier needs cols %% 4 == 0, cols <= 32768 and 16-byte aligned pointers");
+        // three vectors per thread for 2049..3072 columns ([13107,2560] 5.7 -> 6.2 TB/s); five or six vectors in 256 or
+        // 512 threads measured slower than four in twice the threads ([6553,5120] 5.4 against 5.6, [3276,10240] 4.7 / 5.4)
+        if (nvec <= 256 * 3) return launch_block<3, 256>(in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 256 * 4) return launch_block<4, 256>(in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 512 * 4) return launch_block<4, 512>(in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 1024 * 4) return launch_block<4, 1024>(in, out, rows, cols, k.grid_cap, s);
