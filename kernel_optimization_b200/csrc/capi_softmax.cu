@@ -192,11 +192,18 @@ int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStre
         // beyond 16384 columns: two passes per row, the second from the L2, in 256-thread blocks so that several rows
         // per SM are in flight (BF16 [3276,20480] 3.0 -> 4.8 TB/s, [2048,32768] 3.8 -> 4.8 against a 1024-thread block
         // holding the row; [1024,65536] 4.2 -> 4.5 against one 1024-thread reread block per SM)
-        auto kernel = ko::softmax16_reread_kernel<T, 4, 256>;
-        int per_sm = 1;
-        KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0));
-        return ko::launch_overlapped(kernel, ko::clamp_grid(rows, (long long)info.sm_count * (per_sm > 0 ? per_sm : 1)), 256u, 0, s, in, out,
-                                     (long long)rows, (int)cols);
+        // while at least four rows per SM fit in the L2 besides the output stream; longer rows: one 1024-thread block per
+        // SM (BF16 [2048,131072]: 4.6 TB/s; 3.3 with two 256-thread blocks per SM, 4.2 with eight that overflow the L2)
+        const long long fit = (80ll << 20) / ((long long)cols * 2);
+        if (fit >= 4ll * info.sm_count) {
+            auto kernel = ko::softmax16_reread_kernel<T, 4, 256>;
+            int per_sm = 1;
+            KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0));
+            const long long cap = std::min<long long>((long long)info.sm_count * (per_sm > 0 ? per_sm : 1), fit);
+            return ko::launch_overlapped(kernel, ko::clamp_grid(rows, cap), 256u, 0, s, in, out, (long long)rows, (int)cols);
+        }
+        auto kernel = ko::softmax16_reread_kernel<T, 2, 1024>;
+        return ko::launch_overlapped(kernel, ko::clamp_grid(rows, info.sm_count), 1024u, 0, s, in, out, (long long)rows, (int)cols);
     }
     ko::softmax16_stream_kernel<T><<<ko::clamp_grid(rows, (long long)info.sm_count * 8), 256, 0, s>>>(in, out, rows, cols);
     KO_CHECK_LAUNCH("softmax16_stream_kernel");
