@@ -22,7 +22,10 @@ typedef struct ko_row_knobs {
                                 turns the shared-memory prefetch of the next row's slice off),
                             7 = prefetching block (softmax only: row in registers, next row bulk-copied to shared memory),
                             8 = reread (FP32 softmax and every LayerNorm: one row per block in two passes, the second served
-                                by the L2; block = 256 / 512 / 1024 threads, grid_cap = rows in flight) */
+                                by the L2; block = 256 / 512 / 1024 threads, grid_cap = rows in flight),
+                            9 = lane groups (LayerNorm rows of at most 128 vectors: a row per group of stage_rows = 4 / 8 /
+                                16 / 32 lanes with up to four vectors each, rows_per_warp row slots per group, persistent
+                                warps with gamma and beta held in registers) */
     int rows_per_warp;   /* warp / staged tier: independent row slots a warp processes together (a slot is
                             one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows); LayerNorm reread tier:
                             1 = one row per block at a time, 2 = two (gamma / beta loaded once for both),

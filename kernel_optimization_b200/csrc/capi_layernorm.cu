@@ -147,6 +147,39 @@ int dispatch_rows(int vecs, int rpw, const Args<T> &a, const ko_row_knobs_t &k, 
 #undef KO_GO
 }
 
+// short rows: G lanes per row, kVecs vectors per lane, kSlots x 32/G rows per warp step; persistent warps
+template <typename T, int kVecs, int kSlots, int G>
+int launch_group(const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
+    auto kernel = ko::layernorm_group_kernel<T, kVecs, kSlots, G>;
+    int per_sm = 0;
+    KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0));
+    constexpr int kRowsPerBlock = 8 * kSlots * (32 / G);
+    const long long blocks = (a.rows + kRowsPerBlock - 1) / kRowsPerBlock;
+    const long long cap = grid_cap > 0 ? grid_cap : (long long)sm_count * (per_sm > 0 ? per_sm : 1);
+    return ko::launch_overlapped(kernel, ko::clamp_grid(blocks, cap), 256u, 0, s, a.in, a.out, (long long)a.rows, a.cols, a.eps, a.gamma,
+                                 a.beta, a.ddof);
+}
+
+template <typename T, int G>
+int launch_group_g(int nvec, int slots, const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
+    const int per_lane = (nvec + G - 1) / G;
+    if (per_lane <= 1) {
+        if (slots == 1) return launch_group<T, 1, 1, G>(a, grid_cap, sm_count, s);
+        if (slots == 4) return launch_group<T, 1, 4, G>(a, grid_cap, sm_count, s);
+        return launch_group<T, 1, 2, G>(a, grid_cap, sm_count, s);
+    }
+    if (per_lane <= 2) {
+        if (slots == 1) return launch_group<T, 2, 1, G>(a, grid_cap, sm_count, s);
+        if (slots == 4) return launch_group<T, 2, 4, G>(a, grid_cap, sm_count, s);
+        return launch_group<T, 2, 2, G>(a, grid_cap, sm_count, s);
+    }
+    if (per_lane <= 4) {
+        if (slots == 2) return launch_group<T, 4, 2, G>(a, grid_cap, sm_count, s);
+        return launch_group<T, 4, 1, G>(a, grid_cap, sm_count, s);
+    }
+    return ko::fail(KO_ERR_SHAPE, "layernorm: %d lanes hold at most %d vectors per row", G, G * 4);
+}
+
 // one row per block, read twice (the second time from the L2); blocks per SM: as many as fit, fewer when the rows in
 // flight would not fit in `l2_budget` bytes
 template <typename T, int kThreads, bool kPair>
@@ -175,7 +208,7 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
     if (a.rows == 0 || a.cols == 0) return KO_OK;
     KO_REQUIRE(a.in != nullptr && a.out != nullptr, KO_ERR_INVALID_ARG, "layernorm: NULL pointer");
     const ko_row_knobs_t k = knobs ? *knobs : ko_row_knobs_t{};
-    KO_REQUIRE((k.tier >= 0 && k.tier <= 6) || k.tier == 8, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
+    KO_REQUIRE((k.tier >= 0 && k.tier <= 6) || k.tier == 8 || k.tier == 9, KO_ERR_INVALID_ARG, "layernorm: unknown tier %d", k.tier);
     KO_REQUIRE(k.cluster == 0 || k.cluster == 2 || k.cluster == 4 || k.cluster == 8, KO_ERR_INVALID_ARG,
                "layernorm: cluster size %d not in {2,4,8}", k.cluster);
     KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
@@ -197,6 +230,10 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         // measured on B200: the warp tier wins while a lane holds at most 8 vectors of 16-bit data
         // (16 of FP32); beyond that the resident tier (row unpacked once, packed FP32 math) is faster
         // (BF16 [32768,2048]: resident tier with 128-thread blocks 46.0 us, warp tier 51.8 us; at 1024 columns they tie)
+        // short rows: a row does not fill a warp's lanes, or fills them with so little data that per-row costs dominate
+        // (BF16 64 columns 1.3 -> 5.5 TB/s, 128: 2.4 -> 5.4, 256: 4.1 -> 5.5, 512: 4.7 -> 5.3; FP32 32 columns 1.9 -> 5.9,
+        // 64: 3.5 -> 5.9, 128: 5.5 -> 5.9)
+        else if (vec_ok && nvec <= (sizeof(T) == 2 ? 64 : 48)) tier = 9;
         else if (warp_ok && (sizeof(T) == 4 || nvec <= 128)) tier = 1;
         // (16-bit rows of more than 16384 columns would need 1024 threads with 32 unpacked values each and spill:
         // two passes per row with 256-thread blocks instead, BF16 [3276,20480] 2.4 -> 3.6 TB/s)
@@ -208,6 +245,23 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         // beyond one block's registers: with fewer rows than SMs a cluster spreads each row over several SMs
         else if (nvec > 1024 * kMaxVecsPerThread && a.rows < info.sm_count && nvec <= 8 * 1024 * kMaxVecsPerThread) tier = 6;
         else tier = 8;
+    }
+    if (tier == 9) {
+        KO_REQUIRE(vec_ok && nvec <= 128, KO_ERR_SHAPE, "layernorm: the group tier needs 16-byte aligned rows of at most 128 vectors");
+        int g = k.stage_rows;  // lanes per row
+        if (g == 0) {
+            // few lanes with several vectors each: up to four 16-bit vectors per lane, two FP32 vectors
+            const int per_lane = sizeof(T) == 2 ? 4 : 2;
+            g = 4;
+            while (g < 32 && g * per_lane < nvec) g *= 2;
+        }
+        switch (g) {
+            case 4: return launch_group_g<T, 4>(nvec, k.rows_per_warp, a, k.grid_cap, info.sm_count, s);
+            case 8: return launch_group_g<T, 8>(nvec, k.rows_per_warp, a, k.grid_cap, info.sm_count, s);
+            case 16: return launch_group_g<T, 16>(nvec, k.rows_per_warp, a, k.grid_cap, info.sm_count, s);
+            case 32: return launch_group_g<T, 32>(nvec, k.rows_per_warp, a, k.grid_cap, info.sm_count, s);
+            default: return ko::fail(KO_ERR_INVALID_ARG, "layernorm: the group tier takes 4, 8, 16 or 32 lanes per row, got %d", g);
+        }
     }
     if (tier == 8) {
         KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "layernorm: the reread tier needs 16-byte aligned rows");

@@ -319,6 +319,123 @@ __device__ __forceinline__ void layernorm_warp_tier(const T *in, T *out, long lo
 }
 
 // ---------------------------------------------------------------------------------------------
+// group tier: short rows.  A row lives in a group of G lanes (kVecs vectors per lane), a warp works on
+// kSlots * 32/G rows per step, warps walk the rows in a grid-stride loop
+// ---------------------------------------------------------------------------------------------
+// For rows that do not fill 32 lanes, or fill them with so little data that the per-row costs dominate (two 32-lane
+// reductions, gamma and beta fetched and unpacked again for every row): the reductions span G lanes only and serve
+// 32/G rows per instruction, several independent rows per warp are in flight, and -- a lane owning the same columns
+// of every row -- gamma and beta are unpacked to FP32 pairs ONCE, before the row loop.  Statistics are the exact
+// two-pass form of the warp tier (group-wide sum -> mean, squared deviations from that mean).
+template <int G>
+__device__ __forceinline__ float lane_group_sum(float v) {
+#pragma unroll
+    for (int m = G / 2; m > 0; m >>= 1) v += __shfl_xor_sync(kFullMask, v, m);
+    return v;
+}
+
+template <typename T, int kVecs, int kSlots, int G>
+__device__ __forceinline__ void layernorm_group_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                     const T *gamma, const T *beta, int ddof) {
+    using Io = RowIo<T>;
+    using Raw = typename Io::Raw;
+    constexpr int kPer = Io::kPerVec, kPairsPerVec = kPer / 2, kPairs = kVecs * kPairsPerVec;
+    constexpr int kRowsPerSlot = 32 / G, kRowsPerStep = kSlots * kRowsPerSlot;
+    const int lane = threadIdx.x & 31, sub = lane / G, gl = lane % G;
+    const int nvec = cols / kPer;
+    const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const Raw *in_v = reinterpret_cast<const Raw *>(in);
+    Raw *out_v = reinterpret_cast<Raw *>(out);
+    const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma), *beta_v = reinterpret_cast<const Raw *>(beta);
+    const float inv_cols = 1.0f / (float)cols;
+    const float inv_denom = cols - ddof > 0 ? 1.0f / (float)(cols - ddof) : 0.f;
+    int my_vecs = 0;
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) my_vecs += (gl + G * j < nvec) ? 1 : 0;
+
+    f32x2 g2[kPairs], b2[kPairs];
+#pragma unroll
+    for (int q = 0; q < kPairs; ++q) {
+        g2[q] = pair_of(1.f, 1.f);
+        b2[q] = pair_of(0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) {
+        const int v = gl + G * j;
+        if (v < nvec) {
+            if (gamma_v) Io::unpack_pairs(__ldg(gamma_v + v), g2 + j * kPairsPerVec);
+            if (beta_v) Io::unpack_pairs(__ldg(beta_v + v), b2 + j * kPairsPerVec);
+        }
+    }
+
+    for (long long row0 = warp * kRowsPerStep; row0 < rows; row0 += warps * kRowsPerStep) {
+        f32x2 x2[kSlots][kPairs];
+        float mean[kSlots], rstd[kSlots];
+#pragma unroll
+        for (int r = 0; r < kSlots; ++r) {
+            const long long row = row0 + r * kRowsPerSlot + sub;
+            Raw raw[kVecs];
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const int v = gl + G * j;
+                if (row < rows && v < nvec) raw[j] = ld_stream(in_v + row * nvec + v);
+                else raw[j] = Raw{};
+            }
+            f32x2 acc = pair_of(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                Io::unpack_pairs(raw[j], x2[r] + j * kPairsPerVec);  // padded vectors are zero
+#pragma unroll
+                for (int q = 0; q < kPairsPerVec; ++q) acc = pair_add(acc, x2[r][j * kPairsPerVec + q]);
+            }
+            float lo, hi;
+            pair_split(acc, lo, hi);
+            mean[r] = lo + hi;
+        }
+#pragma unroll
+        for (int r = 0; r < kSlots; ++r) mean[r] = lane_group_sum<G>(mean[r]) * inv_cols;
+#pragma unroll
+        for (int r = 0; r < kSlots; ++r) {
+            const f32x2 neg_mean = pair_of(-mean[r], -mean[r]);
+            f32x2 dev2 = pair_of(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                f32x2 part = pair_of(0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < kPairsPerVec; ++q) {
+                    const f32x2 d = pair_add(x2[r][j * kPairsPerVec + q], neg_mean);
+                    x2[r][j * kPairsPerVec + q] = d;  // centred value, reused by the last pass
+                    part = pair_fma(d, d, part);
+                }
+                if (j < my_vecs) dev2 = pair_add(dev2, part);  // a padded vector would add mean^2
+            }
+            float lo, hi;
+            pair_split(dev2, lo, hi);
+            rstd[r] = lo + hi;
+        }
+#pragma unroll
+        for (int r = 0; r < kSlots; ++r) rstd[r] = rsqrtf(lane_group_sum<G>(rstd[r]) * inv_denom + eps);
+#pragma unroll
+        for (int r = 0; r < kSlots; ++r) {
+            const long long row = row0 + r * kRowsPerSlot + sub;
+            if (row >= rows) continue;
+            const f32x2 rstd2 = pair_of(rstd[r], rstd[r]);
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const int v = gl + G * j;
+                if (v >= nvec) continue;
+                f32x2 y2[kPairsPerVec];
+#pragma unroll
+                for (int q = 0; q < kPairsPerVec; ++q)
+                    y2[q] = pair_fma(pair_mul(x2[r][j * kPairsPerVec + q], rstd2), g2[j * kPairsPerVec + q], b2[j * kPairsPerVec + q]);
+                st_stream(out_v + row * nvec + v, Io::pack_pairs(y2));
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // staged tier: consumer side of the row pipeline (common/row_pipeline.h)
 // ---------------------------------------------------------------------------------------------
 template <typename T, int kVecs, int kRows, int kConsumerWarps>
@@ -848,6 +965,13 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const T *in, T *out
     grid_launch_dependents();  // the next kernel of the stream may take SMs as this one's blocks retire
     grid_dependency_wait();    // nothing is read before the previous kernel's writes are visible
     layernorm_warp_tier<T, kVecs, kRows>(in, out, rows, cols, eps, gamma, beta, ddof);
+}
+template <typename T, int kVecs, int kSlots, int G>
+__global__ void __launch_bounds__(256) layernorm_group_kernel(const T *in, T *out, long long rows, int cols, float eps,
+                                                              const T *gamma, const T *beta, int ddof) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    layernorm_group_tier<T, kVecs, kSlots, G>(in, out, rows, cols, eps, gamma, beta, ddof);
 }
 template <typename T, int kVecs, int kRows, int kConsumerWarps>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * 32)

@@ -90,14 +90,14 @@ def test_softmax_f32_stays_inside_its_buffers(cuda, lib, oracle, rows, cols, tie
     assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= 1e-6
 
 
-@pytest.mark.parametrize("tier", [0, 1, 2, 3, 4, 5, 6, 8, 82])
+@pytest.mark.parametrize("tier", [0, 1, 2, 3, 4, 5, 6, 8, 82, 9])
 @pytest.mark.parametrize("rows,cols", ROW_SHAPES_F32)
 def test_layernorm_f32_stays_inside_its_buffers(cuda, lib, oracle, rows, cols, tier):
     from kernel_optimization_b200.native import RowKnobs
 
     ok = {0: True, 1: cols % 4 == 0 and cols <= 2048, 2: cols % 4 == 0 and cols <= 32768, 3: True,
           4: cols % 4 == 0 and 64 <= cols <= 2048, 5: cols % 4 == 0 and cols <= 16384, 6: cols % 4 == 0 and cols >= 4096,
-          8: cols % 4 == 0, 82: cols % 4 == 0}[tier]
+          8: cols % 4 == 0, 82: cols % 4 == 0, 9: cols % 4 == 0 and cols <= 512}[tier]
     if not ok:
         pytest.skip("shape outside this tier")
     x = oracle.fill_normal((rows, cols), 1, 0, 0.0, 1.0)

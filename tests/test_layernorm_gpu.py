@@ -108,6 +108,48 @@ def test_f32_resident_tier(cuda, lib, oracle, block):
             assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, gg, bb)) <= TOL_REL
 
 
+@pytest.mark.parametrize("lanes", [0, 4, 8, 16, 32])
+@pytest.mark.parametrize("slots", [0, 1, 2, 4])
+def test_lane_group_tier_for_short_rows(cuda, lib, oracle, lanes, slots):
+    """tier 9: a row per group of 4 / 8 / 16 / 32 lanes (up to four vectors per lane), several row slots per group,
+    persistent warps with gamma / beta unpacked once.  Rows that fill the group exactly, partly, or leave lanes idle;
+    row counts that are not a multiple of the rows per warp step; one block walking every row (grid_cap = 1); with and
+    without the affine parameters; ddof; FP32 and BF16; in place."""
+    for rows, cols in ((1, 4), (7, 8), (1000, 32), (333, 64), (77, 96), (501, 128), (65, 200), (129, 256), (40, 512)):
+        nvec = cols // 4
+        if lanes and (lanes * 4 < nvec):
+            continue
+        x, g, b = _inputs(oracle, rows, cols)
+        x += 2.0
+        knobs = dict(tier=9, stage_rows=lanes, rows_per_warp=slots)
+        y = _run_f32(cuda, lib, x, 1e-12, g, b, 0, **knobs)
+        assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+        assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, grid_cap=1, **knobs))
+        assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, inplace=True, **knobs))
+        y = _run_f32(cuda, lib, x, 1e-5, None, None, 1, **knobs)
+        assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-5, None, None, 1)) <= TOL_REL
+        y = _run_f32(cuda, lib, x, 1e-5, None, b, 0, **knobs)
+        assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-5, None, b)) <= TOL_REL
+    for rows, cols in ((9, 8), (1001, 64), (77, 96), (300, 128), (65, 200), (129, 256), (33, 320), (40, 512), (17, 1024)):
+        nvec = cols // 8
+        if lanes and (lanes * 4 < nvec):
+            continue
+        x, g, b = _inputs(oracle, rows, cols)
+        xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
+        got = oracle.from_bf16_bits(_run_bf16(cuda, lib, xb, 1e-12, gb, bb, tier=9, stage_rows=lanes, rows_per_warp=slots))
+        want = oracle.layernorm_f64(oracle.from_bf16_bits(xb), 1e-12, oracle.from_bf16_bits(gb), oracle.from_bf16_bits(bb))
+        assert oracle.max_rel_err(got, want) <= 2.0 ** -8 * 1.01
+
+
+def test_short_rows_default_to_the_lane_group_tier(cuda, lib, oracle):
+    for rows, cols in ((1000, 32), (500, 64), (300, 192)):
+        x, g, b = _inputs(oracle, rows, cols)
+        assert np.array_equal(_run_f32(cuda, lib, x, 1e-12, g, b), _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=9))
+    x, g, b = _inputs(oracle, 400, 512)
+    xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
+    assert np.array_equal(_run_bf16(cuda, lib, xb, 1e-12, gb, bb), _run_bf16(cuda, lib, xb, 1e-12, gb, bb, tier=9))
+
+
 @pytest.mark.parametrize("block", [0, 128, 256, 512, 1024])
 def test_resident_tier_row_ring_gives_the_bits_of_the_register_prefetch(cuda, lib, oracle, block):
     """stages = 3: the block's next rows are in flight into shared memory (cp.async, every thread copies the vectors it
