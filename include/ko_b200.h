@@ -141,9 +141,9 @@ int ko_softmax_bf16(const uint16_t *in, uint16_t *out, int64_t rows, int32_t col
  * LayerNormBlockNoCacheImpl<E, vec, rows, cols, affine>><<<...>>>(in, out, eps, gamma, beta):
  * nn_operators/layernorm/layernorm.h:145-201, :204-252, :254-300, :302-312.
  * y = (x - mean) * rsqrt(var + eps) [* gamma] [+ beta]; var = M2 / (cols - ddof), ddof in {0, 1};
- * statistics in FP32.  Which form of them runs depends on the row length only: rows a warp holds
- * unpacked in registers (FP32 up to 1024 columns, 16-bit up to 1024) and the rows of the resident
- * tier (to 16384 / 32768 columns) use the exact two-pass form over registers -- the mean from the
+ * statistics in FP32.  Which form of them runs depends on the row length only: rows a lane group
+ * or a warp holds unpacked in registers (FP32 up to 1024 columns, 16-bit up to 1024) and the rows
+ * of the resident tier (to 16384 columns) use the exact two-pass form over registers -- the mean from the
  * row sum, then M2 as the sum of squared deviations from that mean, i.e. the value the merge of
  * Welford triples converges to; longer rows (block, cluster, two-pass and scalar tiers) form
  * per-thread (count, mean, M2) triples and merge them pairwise (Chan et al.) across lanes, warps
