@@ -208,6 +208,22 @@ __device__ __forceinline__ float4 ld_keep(const float4 *p, uint64_t policy) {
     return v;
 }
 
+__device__ __forceinline__ uint64_t l2_stream_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+// 16 bytes global -> this thread's shared-memory slot, asynchronously, with an L2 eviction policy; completion through
+// cp.async.commit_group / wait_group of the issuing thread
+__device__ __forceinline__ void cp_async16_policy(void *smem_dst, const void *src, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+                 "l"(src), "l"(policy)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ uint4 ld_keep(const uint4 *p, uint64_t policy) {
     uint4 v;
     asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"

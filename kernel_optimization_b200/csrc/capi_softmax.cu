@@ -70,6 +70,22 @@ int launch_reread(const float *in, float *out, long long rows, int cols, long lo
     return ko::launch_overlapped(kernel, ko::clamp_grid(rows, cap), (unsigned)kThreads, 0, s, in, out, rows, cols);
 }
 
+// the reread tier with every load through a per-thread shared-memory ring of kDepth items
+template <int kThreads, int kUnroll, int kDepth>
+int launch_reread_ring(const float *in, float *out, long long rows, int cols, long long grid_cap, int sm_count, cudaStream_t s) {
+    auto kernel = ko::softmax_reread_ring_kernel<kUnroll, kThreads, kDepth>;
+    constexpr size_t kBytes = (size_t)kDepth * kUnroll * kThreads * 16;
+    if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), kBytes)) return st;
+    long long cap = grid_cap;
+    if (cap <= 0) {
+        int per_sm = 0;
+        KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, kBytes));
+        const long long fit = (80ll << 20) / ((long long)cols * 4 * sm_count);
+        cap = (long long)sm_count * std::max(1ll, std::min<long long>(per_sm, fit));
+    }
+    return ko::launch_overlapped(kernel, ko::clamp_grid(rows, cap), (unsigned)kThreads, kBytes, s, in, out, rows, cols);
+}
+
 // one row per cluster of `c` blocks; a block holds up to 8 vectors per thread.  256-thread blocks when the slice
 // allows: several clusters (rows) then share an SM and one row's reductions and cluster barriers overlap another's
 // loads, which a single 1024-thread block per SM cannot do.  threads: 0 = choose, 256 or 1024.
@@ -255,6 +271,15 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
     }
     if (tier == 8) {
         KO_REQUIRE(vec_ok, KO_ERR_SHAPE, "softmax: the reread tier needs cols %% 4 == 0 and 16-byte aligned pointers");
+        // loads through a shared-memory ring of items (stages: 3 = on, 1 = off, 0 = on for rows of at most 256 KB, where it
+        // measured faster: [1024,65536] 5.3 -> 5.7 TB/s, [4096,65536] 5.5 -> 6.1; beyond, the items fetched ahead across
+        // the end of a row compete for the L2 with the rows being re-read: [2048,131072] 5.2 either way)
+        if (k.stages == 3 || (k.stages == 0 && k.block == 0 && (long long)cols * 4 <= (256ll << 10))) {
+            if (k.block == 256) return launch_reread_ring<256, 4, 4>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+            if (k.block == 512) return launch_reread_ring<512, 4, 3>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+            if (k.rows_per_warp == 2) return launch_reread_ring<1024, 2, 4>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+            return launch_reread_ring<1024, 4, 3>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
+        }
         if (k.block == 256) return launch_reread<256>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
         if (k.block == 512) return launch_reread<512>(in, out, rows, cols, k.grid_cap, info.sm_count, s);
         return launch_reread<1024>(in, out, rows, cols, k.grid_cap, info.sm_count, s);

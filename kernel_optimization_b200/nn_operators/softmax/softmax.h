@@ -502,6 +502,94 @@ __device__ __forceinline__ void softmax_reread_tier(const float *in, float *out,
     }
 }
 
+// The same two passes with every load going through a per-thread shared-memory ring (cp.async): the block's work is
+// a stream of items -- (row, pass, chunk of kUnroll vectors per thread) -- and the loads of the next kDepth - 1 items
+// are always in flight, across the end of a pass and the end of a row, so the memory pipeline neither drains at the
+// two block reductions of a row nor ramps up again at the start of the next.  A thread copies exactly the vectors it
+// consumes, so the ring needs no block barrier.  ring: kDepth * kUnroll * kThreads vectors.
+template <int kUnroll, int kThreads, int kDepth>
+__device__ __forceinline__ void softmax_reread_ring_tier(const float *in, float *out, long long rows, int cols, float *s_exchange,
+                                                         float4 *ring) {
+    const int nvec = cols >> 2;
+    constexpr int kStep = kThreads * kUnroll;
+    const int chunks = (nvec + kStep - 1) / kStep;
+    const float4 *in4 = reinterpret_cast<const float4 *>(in);
+    const uint64_t keep = l2_keep_policy(), once = l2_stream_policy();
+    // producer: the item kDepth - 1 ahead of the consumer
+    long long p_row = blockIdx.x;
+    int p_pass = 0, p_chunk = 0, p_slot = 0;
+    auto produce = [&]() {
+        if (p_row < rows) {
+            const float4 *x4 = in4 + p_row * nvec;
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = p_chunk * kStep + (int)threadIdx.x + kThreads * j;
+                if (v < nvec) cp_async16_policy(ring + (p_slot * kUnroll + j) * kThreads + threadIdx.x, x4 + v, p_pass == 0 ? keep : once);
+            }
+            if (++p_chunk == chunks) {
+                p_chunk = 0;
+                if (++p_pass == 2) {
+                    p_pass = 0;
+                    p_row += gridDim.x;
+                }
+            }
+        }
+        cp_async_commit_group();  // also when nothing was issued: the group count stays one per item
+        p_slot = p_slot + 1 == kDepth ? 0 : p_slot + 1;
+    };
+#pragma unroll
+    for (int i = 0; i < kDepth - 1; ++i) produce();
+    int c_slot = 0;
+    auto consume = [&](int chunk, float4 (&x)[kUnroll]) {
+        produce();  // refills the slot read one item ago (by this same thread)
+        cp_async_wait_group<kDepth - 1>();
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const int v = chunk * kStep + (int)threadIdx.x + kThreads * j;
+            x[j] = v < nvec ? ring[(c_slot * kUnroll + j) * kThreads + threadIdx.x] : neg_inf4();
+        }
+        c_slot = c_slot + 1 == kDepth ? 0 : c_slot + 1;
+    };
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        float4 *y4 = reinterpret_cast<float4 *>(out) + row * nvec;
+        float m = kNegInf, s = 0.f;
+        for (int chunk = 0; chunk < chunks; ++chunk) {
+            float4 x[kUnroll];
+            consume(chunk, x);
+            float cm = kNegInf;
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) cm = fmaxf(cm, max4(x[j]));
+            const float grown = fmaxf(m, cm);
+            if (grown != kNegInf) {  // a chunk of nothing but -inf adds nothing
+                const float neg = -grown * kLog2e;
+                float cs = 0.f;
+#pragma unroll
+                for (int j = 0; j < kUnroll; ++j) cs += exp_shifted4(x[j], neg);
+                s = fmaf(s, exp2_approx(fmaf(m, kLog2e, neg)), cs);
+                m = grown;
+            }
+        }
+        const float row_max = block_allreduce<true>(m, s_exchange);
+        const float neg = -row_max * kLog2e;
+        s = m == kNegInf ? 0.f : s * exp2_approx(fmaf(m, kLog2e, neg));
+        const float inv = rcp_approx(block_allreduce<false>(s, s_exchange));
+        for (int chunk = 0; chunk < chunks; ++chunk) {
+            float4 x[kUnroll];
+            consume(chunk, x);
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = chunk * kStep + (int)threadIdx.x + kThreads * j;
+                if (v < nvec) {
+                    exp_shifted4(x[j], neg);
+                    scale4(x[j], inv);
+                    st_stream(y4 + v, x[j]);
+                }
+            }
+        }
+    }
+    cp_async_wait_group<0>();
+}
+
 // ---------------------------------------------------------------------------------------------
 // stream tier: any cols, any alignment; three passes over global memory
 // ---------------------------------------------------------------------------------------------
@@ -577,6 +665,14 @@ __global__ void __launch_bounds__(kThreads) softmax_reread_kernel(const float *i
     grid_dependency_wait();
     __shared__ float s_exchange[33];
     softmax_reread_tier<kUnroll>(in, out, rows, cols, s_exchange);
+}
+template <int kUnroll, int kThreads, int kDepth>
+__global__ void __launch_bounds__(kThreads) softmax_reread_ring_kernel(const float *in, float *out, long long rows, int cols) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    __shared__ float s_exchange[33];
+    extern __shared__ __align__(16) float4 ko_softmax_item_ring[];
+    softmax_reread_ring_tier<kUnroll, kThreads, kDepth>(in, out, rows, cols, s_exchange, ko_softmax_item_ring);
 }
 __global__ void __launch_bounds__(256) softmax_stream_kernel(const float *in, float *out, long long rows, int cols) {
     __shared__ float s_exchange[33];

@@ -110,6 +110,12 @@ def test_reread_tier_two_passes_per_row(cuda, lib, oracle, block):
         assert oracle.max_abs_err(y, oracle.softmax_f64(x)) <= TOL_ABS and oracle.max_rowsum_err(y) <= TOL_ROWSUM
         assert np.array_equal(y, _run(cuda, lib, x, tier=8, block=block, grid_cap=3))  # three blocks take all rows
         assert np.array_equal(y, _run(cuda, lib, x, inplace=True, tier=8, block=block))  # out == in: a thread rewrites only what it read
+        # every load through the per-thread shared-memory ring of (row, pass, chunk) items, or none: same arithmetic
+        ring = _run(cuda, lib, x, tier=8, block=block, stages=3)
+        assert np.array_equal(ring, _run(cuda, lib, x, tier=8, block=block, stages=1))
+        assert np.array_equal(ring, _run(cuda, lib, x, tier=8, block=block, stages=3, grid_cap=3))
+        assert np.array_equal(ring, _run(cuda, lib, x, inplace=True, tier=8, block=block, stages=3))
+        assert oracle.max_abs_err(ring, oracle.softmax_f64(x)) <= TOL_ABS
     assert lib.ko_poll_device_status() == 0
 
 
