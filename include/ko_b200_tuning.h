@@ -34,7 +34,8 @@ typedef struct ko_row_knobs {
     int64_t grid_cap;    /* warp / block / stream tier: upper bound on the grid (0 = one pass per warp) */
     int stage_rows;      /* staged tier: rows per bulk copy (0 = about 16-32 KB) */
     int stages;          /* staged tier: ring depth (0 = fill about 100 KB); LayerNorm resident tier: 1 = the block's next
-                            row prefetched into registers, 3 = its next rows in flight into shared memory (cp.async), 0 = choose */
+                            row prefetched into registers, 3 = its next rows in flight into shared memory (cp.async), 0 = choose;
+                            reread tier: 1 = direct loads, 3 = loads through a shared-memory ring of items, 0 = choose */
     int ctas_per_sm;     /* staged tier: persistent blocks per SM (0 = 1) */
     int cluster;         /* cluster tier: blocks per cluster, 2 / 4 / 8 (0 = smallest that holds the row) */
 } ko_row_knobs_t;

@@ -201,6 +201,23 @@ int launch_reread(const Args<T> &a, long long grid_cap, int sm_count, cudaStream
                                  a.gamma, a.beta, a.ddof);
 }
 
+// the single-row reread tier with every row load through a per-thread shared-memory ring of kDepth items
+template <typename T, int kThreads, int kUnroll, int kDepth>
+int launch_reread_ring(const Args<T> &a, long long grid_cap, int sm_count, cudaStream_t s) {
+    auto kernel = ko::layernorm_reread_ring_kernel<T, kUnroll, kThreads, kDepth>;
+    constexpr size_t kBytes = (size_t)kDepth * kUnroll * kThreads * 16;
+    if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), kBytes)) return st;
+    long long cap = grid_cap;
+    if (cap <= 0) {
+        int per_sm = 0;
+        KO_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, kBytes));
+        const long long fit = (80ll << 20) / ((long long)a.cols * (long long)sizeof(T) * sm_count);
+        cap = (long long)sm_count * std::max(1ll, std::min<long long>(per_sm, fit));
+    }
+    return ko::launch_overlapped(kernel, ko::clamp_grid(a.rows, cap), (unsigned)kThreads, kBytes, s, a.in, a.out, a.rows, a.cols, a.eps,
+                                 a.gamma, a.beta, a.ddof);
+}
+
 template <typename T>
 int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream_t s) {
     KO_REQUIRE(a.rows >= 0 && a.cols >= 0, KO_ERR_INVALID_ARG, "layernorm: negative shape [%lld, %d]", a.rows, a.cols);
@@ -272,6 +289,26 @@ int layernorm_dispatch(const Args<T> &a, const ko_row_knobs_t *knobs, cudaStream
         if (block == 0) {
             if (sizeof(T) == 2) block = nvec <= 1024 * 6 ? 256 : 1024;  // BF16 [1365,49152]: 3.8 TB/s with 256, 3.3 with 1024
             else block = nvec <= 1024 * 5 ? 256 : (nvec <= 1024 * kMaxVecsPerThread ? 512 : 1024);
+        }
+        // row loads through a shared-memory ring of items (stages: 3 = on, 1 = off, 0 = where it measured faster: rows of
+        // 128..256 KB with 1024 threads -- FP32 [1024,65536] 4.3 -> 4.8 TB/s, [4096,65536] 4.6 -> 5.3, BF16 [2048,131072]
+        // 4.0 -> 4.2 -- and FP32 rows of 80..128 KB with 512 threads: [1365,24576] 4.4 -> 4.7, [8192,32768] 5.2 -> 5.3)
+        const long long row_bytes = (long long)a.cols * (long long)sizeof(T);
+        bool ring = k.stages == 3;
+        if (k.stages == 0 && k.block == 0 && k.rows_per_warp == 0 && !pair) {
+            if (row_bytes > (128ll << 10) && row_bytes <= (256ll << 10)) {
+                ring = true;
+                block = 1024;
+            } else if (sizeof(T) == 4 && row_bytes > (80ll << 10) && row_bytes <= (128ll << 10)) {
+                ring = true;
+                block = 512;
+            }
+        }
+        if (ring && !pair) {
+            constexpr int kU = sizeof(T) == 2 ? 2 : 4;
+            if (block == 256) return launch_reread_ring<T, 256, 4, 4>(a, k.grid_cap, info.sm_count, s);
+            if (block == 512) return launch_reread_ring<T, 512, kU, 3>(a, k.grid_cap, info.sm_count, s);
+            return launch_reread_ring<T, 1024, kU, 3>(a, k.grid_cap, info.sm_count, s);
         }
         if (block == 256) return pair ? launch_reread<T, 256, true>(a, k.grid_cap, info.sm_count, s) : launch_reread<T, 256, false>(a, k.grid_cap, info.sm_count, s);
         if (block == 512) return pair ? launch_reread<T, 512, true>(a, k.grid_cap, info.sm_count, s) : launch_reread<T, 512, false>(a, k.grid_cap, info.sm_count, s);

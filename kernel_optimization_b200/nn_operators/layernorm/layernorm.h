@@ -927,6 +927,111 @@ __device__ __forceinline__ void layernorm_reread_tier(const T *in, T *out, long 
     }
 }
 
+// The single-row reread tier with every row load going through a per-thread shared-memory ring (cp.async): the
+// block's work is a stream of items -- (row, pass, chunk of kUnroll vectors per thread) -- and the loads of the next
+// kDepth - 1 items are always in flight, across the end of a pass and of a row (see softmax_reread_ring_tier).
+// ring: kDepth * kUnroll * kThreads vectors of 16 bytes.
+template <typename T, int kUnroll, int kThreads, int kDepth>
+__device__ __forceinline__ void layernorm_reread_ring_tier(const T *in, T *out, long long rows, int cols, float eps,
+                                                           const T *gamma, const T *beta, int ddof, float *s_exchange,
+                                                           uint4 *ring) {
+    using Io = RowIo<T>;
+    using Raw = typename Io::Raw;
+    constexpr int kPer = Io::kPerVec, kStep = kThreads * kUnroll;
+    const int nvec = cols / kPer;
+    const int chunks = (nvec + kStep - 1) / kStep;
+    const Raw *in_v = reinterpret_cast<const Raw *>(in);
+    const Raw *gamma_v = reinterpret_cast<const Raw *>(gamma), *beta_v = reinterpret_cast<const Raw *>(beta);
+    const uint64_t keep = l2_keep_policy(), once = l2_stream_policy();
+    long long p_row = blockIdx.x;
+    int p_pass = 0, p_chunk = 0, p_slot = 0;
+    auto produce = [&]() {
+        if (p_row < rows) {
+            const Raw *x_v = in_v + p_row * nvec;
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = p_chunk * kStep + (int)threadIdx.x + kThreads * j;
+                if (v < nvec) cp_async16_policy(ring + (p_slot * kUnroll + j) * kThreads + threadIdx.x, x_v + v, p_pass == 0 ? keep : once);
+            }
+            if (++p_chunk == chunks) {
+                p_chunk = 0;
+                if (++p_pass == 2) {
+                    p_pass = 0;
+                    p_row += gridDim.x;
+                }
+            }
+        }
+        cp_async_commit_group();  // also when nothing was issued: one group per item
+        p_slot = p_slot + 1 == kDepth ? 0 : p_slot + 1;
+    };
+#pragma unroll
+    for (int i = 0; i < kDepth - 1; ++i) produce();
+    int c_slot = 0;
+    // this thread's vectors of the item, zero where the row has ended; returns how many are real
+    auto consume = [&](int chunk, Raw (&raw)[kUnroll]) -> int {
+        produce();  // refills the slot read one item ago (by this same thread)
+        cp_async_wait_group<kDepth - 1>();
+        int have = 0;
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const int v = chunk * kStep + (int)threadIdx.x + kThreads * j;
+            uint4 r = uint4{0u, 0u, 0u, 0u};
+            if (v < nvec) {
+                r = ring[(c_slot * kUnroll + j) * kThreads + threadIdx.x];
+                ++have;
+            }
+            raw[j] = *reinterpret_cast<const Raw *>(&r);
+        }
+        c_slot = c_slot + 1 == kDepth ? 0 : c_slot + 1;
+        return have;
+    };
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        Raw *y_v = reinterpret_cast<Raw *>(out) + row * nvec;
+        Welford run{0.f, 0.f, 0.f};
+        for (int chunk = 0; chunk < chunks; ++chunk) {
+            Raw raw[kUnroll];
+            const int have = consume(chunk, raw);
+            if (have == 0) continue;
+            float x[kUnroll][kPer];
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                Io::unpack(raw[j], x[j]);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) sum += x[j][e];  // padded vectors are zero
+            }
+            Welford c;
+            c.n = (float)(have * kPer);
+            c.mean = sum / c.n;
+            c.m2 = 0.f;
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                float part = 0.f;
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    const float d = x[j][e] - c.mean;
+                    part = fmaf(d, d, part);
+                }
+                c.m2 += j < have ? part : 0.f;
+            }
+            run = welford_merge(run, c);
+        }
+        const Welford w = block_allreduce_welford(run, s_exchange);
+        const float mean = w.mean;
+        const float rstd = rstd_from(w, cols, ddof, eps);
+        for (int chunk = 0; chunk < chunks; ++chunk) {
+            Raw raw[kUnroll];
+            consume(chunk, raw);
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int v = chunk * kStep + (int)threadIdx.x + kThreads * j;
+                if (v < nvec) st_stream(y_v + v, normalise_vector<T>(raw[j], mean, rstd, gamma_v, beta_v, v));
+            }
+        }
+    }
+    cp_async_wait_group<0>();
+}
+
 // ---------------------------------------------------------------------------------------------
 // stream tier: any cols / alignment; per-thread running Welford, two passes over global memory
 // ---------------------------------------------------------------------------------------------
@@ -1015,6 +1120,15 @@ __global__ void __launch_bounds__(kThreads) layernorm_reread_kernel(const T *in,
     grid_dependency_wait();
     __shared__ float s_exchange[96];
     layernorm_reread_tier<T, kStatUnroll, kUnroll, kPair>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange);
+}
+template <typename T, int kUnroll, int kThreads, int kDepth>
+__global__ void __launch_bounds__(kThreads) layernorm_reread_ring_kernel(const T *in, T *out, long long rows, int cols, float eps,
+                                                                         const T *gamma, const T *beta, int ddof) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    __shared__ float s_exchange[96];
+    extern __shared__ __align__(16) uint4 ko_ln_item_ring[];
+    layernorm_reread_ring_tier<T, kUnroll, kThreads, kDepth>(in, out, rows, cols, eps, gamma, beta, ddof, s_exchange, ko_ln_item_ring);
 }
 template <typename T>
 __global__ void __launch_bounds__(256) layernorm_stream_kernel(const T *in, T *out, long long rows, int cols, float eps,

@@ -205,10 +205,19 @@ def test_reread_tier_two_passes_per_row(cuda, lib, oracle, block, pair):
         assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, g, b, 0, inplace=True, tier=8, block=block, rows_per_warp=pair))
         y = _run_f32(cuda, lib, x, 1e-5, None, None, 1, tier=8, block=block, rows_per_warp=pair)
         assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-5, None, None, 1)) <= TOL_REL
+        if pair == 1:
+            # every row load through the per-thread shared-memory ring of (row, pass, chunk) items: the same chunks, so
+            # the same bits as the direct loads
+            ring = _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=8, block=block, rows_per_warp=1, stages=3)
+            assert np.array_equal(ring, _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=8, block=block, rows_per_warp=1, stages=1))
+            assert np.array_equal(ring, _run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=8, block=block, rows_per_warp=1, stages=3, grid_cap=3))
+            assert np.array_equal(ring, _run_f32(cuda, lib, x, 1e-12, g, b, 0, inplace=True, tier=8, block=block, rows_per_warp=1, stages=3))
     x, g, b = _inputs(oracle, 5, 65536 + 16)
     xb, gb, bb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(g), oracle.to_bf16_bits(b)
     got = oracle.from_bf16_bits(_run_bf16(cuda, lib, xb, 1e-12, gb, bb, tier=8, block=block, rows_per_warp=pair))
     want = oracle.layernorm_f64(oracle.from_bf16_bits(xb), 1e-12, oracle.from_bf16_bits(gb), oracle.from_bf16_bits(bb))
+    assert oracle.max_rel_err(got, want) <= 2.0 ** -8 * 1.01
+    got = oracle.from_bf16_bits(_run_bf16(cuda, lib, xb, 1e-12, gb, bb, tier=8, block=block, rows_per_warp=1, stages=3))
     assert oracle.max_rel_err(got, want) <= 2.0 ** -8 * 1.01
 
 
