@@ -60,7 +60,8 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
 /* fmt: 0 = F16, 1 = BF16 (A, B); out_fmt: 0 = FP32, 1 = F16, 2 = BF16 (D, C); b_row_major: 0 / 1; bn: 0 = choose,
  * 64 / 128 / 256 = columns of D per 128-row tile, 512 = the 256 x 256 tile (two 128-row halves per CTA share each B tile),
  * all with equal column tiles; 1024 / 1280 = the 128- / 256-row tile with N cut into uneven column tiles of at most 256
- * columns that fill the last round of CTAs (KO_ERR_SHAPE when that gains nothing; 0 uses them when they gain);
+ * columns that fill the last round of CTAs (KO_ERR_SHAPE when the tiles fit one round anyway; 0 uses them when the cost
+ * model predicts a gain);
  * 2048 = the two-SM kernel (tcgen05 cta_group::2: a pair of CTAs per 256 x 256 tile, either B layout), 2304 = the same
  * with uneven column tiles (column-major B only);
  * store_mode: 0 = choose, 1 = TMA-store epilogue (KO_ERR_SHAPE when not possible), 2 = direct stores */

@@ -126,17 +126,23 @@ struct ColumnPlan {
     int tiles_n = 0, wide_tiles_n = 0, bn_wide = 0, bn_narrow = 0;  // tiles_n == 0: uniform
 };
 // pair: the tile is computed by two CTAs, each with half the rows and half the B columns to load
+// The 256-row tiles (one CTA or a pair) run at the rate their operands arrive even at full width -- measured: a tile
+// of 256 x 168 columns takes 0.83 of the time of 256 x 256, i.e. (256 + 168) / (256 + 256) and not 168 / 256 -- so their
+// cost is rows + width; a narrower tile saves less than its width suggests (8192 x 3072 x 4096: 18 column tiles of
+// 192 / 160 columns took 173 us against 157 us for 12 of 256).
 double tile_cost(int rows, int width, bool pair) {
     const double mma = (double)(pair ? rows / 2 : rows) * width;
-    const double operands = (128.0 * 256.0 / 0.87 / 384.0) * (pair ? rows / 2 + width / 2 : rows + width);
+    const double per_unit = rows >= 256 ? 128.0 : 128.0 * 256.0 / 0.87 / 384.0;
+    const double operands = per_unit * (pair ? rows / 2 + width / 2 : rows + width);
     return mma > operands ? mma : operands;
 }
-ColumnPlan plan_columns(long long M, long long N, int tile_m, int bn_max, int slots, bool pair) {
+// force: the cheapest uneven plan even when the uniform one is modelled cheaper (the tuning codes that ask for one)
+ColumnPlan plan_columns(long long M, long long N, int tile_m, int bn_max, int slots, bool pair, bool force) {
     ColumnPlan best;
     const long long tiles_m = (M + tile_m - 1) / tile_m;
     const long long uniform_n = (N + bn_max - 1) / bn_max;
     const long long uniform_rounds = (tiles_m * uniform_n + slots - 1) / slots;
-    double best_cost = (double)uniform_rounds * tile_cost(tile_m, bn_max, pair);
+    double best_cost = force ? 1e300 : (double)uniform_rounds * tile_cost(tile_m, bn_max, pair);
     if (tiles_m * uniform_n <= slots) return best;  // a single, partly filled round: nothing to even out
     const long long units = (N + 31) / 32;
     for (long long tn = uniform_n + 1; tn <= 2 * uniform_n; ++tn) {
@@ -226,7 +232,10 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     if (pair) bn = 256;
     if (bn == 0) {
         const double e256 = wave_efficiency(M, N, 256, info.sm_count);
-        const double e128 = 0.80 * wave_efficiency(M, N, 128, info.sm_count);
+        // a 128 x 128 tile brings twice the operand bytes per MMA of a 128 x 256 tile: on long K it runs at little more
+        // than half the rate per SM (8192 x 768 x 4096: 72.9 us in 128-wide tiles, 54.6 in 256-wide, 51.1 in 256 x 256);
+        // on short K the epilogue dominates and the two are level
+        const double e128 = (K <= 512 ? 0.80 : 0.58) * wave_efficiency(M, N, 128, info.sm_count);
         bn = (N > 128 && e256 >= e128) ? 256 : 128;
         if (N <= 64) bn = 64;
         if (bn == 256 && M > 128) {
@@ -252,7 +261,9 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     ColumnPlan cols;
     const bool may_split = !b_row_major && bn == 256 && N > 256 &&
                            ((bn_request == 0 && !pair) || bn_request == 1024 || bn_request == 1280 || bn_request == 2304);
-    if (may_split) cols = pair ? plan_columns(M, N, 256, 256, pair_slots, true) : plan_columns(M, N, mt * ko::tc::kBM, 256, info.sm_count, false);
+    const bool forced = bn_request == 1024 || bn_request == 1280 || bn_request == 2304;
+    if (may_split)
+        cols = pair ? plan_columns(M, N, 256, 256, pair_slots, true, forced) : plan_columns(M, N, mt * ko::tc::kBM, 256, info.sm_count, false, forced);
     KO_REQUIRE((bn_request != 1024 && bn_request != 1280 && bn_request != 2304) || cols.tiles_n != 0, KO_ERR_SHAPE,
                "gemm: uneven column tiles bring nothing for this shape");
 
