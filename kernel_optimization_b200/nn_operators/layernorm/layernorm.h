@@ -9,15 +9,20 @@
 //
 // Tiers by row length (the reference's warp / block-cached / block-no-cache split,
 // nn_operators/layernorm/layernorm.h:145-201, :204-252, :254-300):
+//   group tier   short rows: a row per group of 4..32 lanes, several rows per warp step, persistent
+//                warps with gamma/beta held in registers;
 //   staged tier  persistent blocks, a producer warp streams chunks of rows into a shared-memory ring
 //                with 1-D bulk copies (TMA), consumer warps work out of shared memory
 //                (common/row_pipeline.h);
 //   warp tier    one warp owns kRows consecutive rows per step, rows in registers;
 //   block tier   one thread block per row, row in registers, one shared-memory exchange;
 //   resident tier persistent blocks for long rows: gamma/beta held in registers, packed FP32 math,
-//                next row prefetched;
+//                next row prefetched into registers or the next rows into a per-thread shared-memory ring;
 //   cluster tier one row per thread-block cluster, Welford triples exchanged through distributed
-//                shared memory (rows beyond one block's registers, or few very long rows);
+//                shared memory (few very long rows);
+//   reread tier  rows beyond one block's registers: one row (or a pair sharing gamma/beta) per block in
+//                two passes, the second served by the L2; optionally every load through a shared-memory
+//                ring of (row, pass, chunk) items;
 //   stream tier  one thread block per row, two passes over global memory, scalar accesses, any
 //                column count and alignment.
 // y = ((x - mean) * rstd) * gamma + beta, gamma/beta optional, in the I/O element type.

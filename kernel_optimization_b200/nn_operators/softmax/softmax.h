@@ -1,6 +1,6 @@
 // Row softmax over the last dimension for sm_100a.
 //
-// Five tiers, chosen by row length and alignment (the reference's warp / block-cached /
+// Tiers, chosen by row length, row count and alignment (the reference's warp / block-cached /
 // block-no-cache split, nn_operators/softmax/softmax.h:11-60, :62-113, :116-166, re-thought for B200):
 //
 //   staged tier persistent blocks; a producer warp streams chunks of whole rows into a shared-memory
@@ -11,8 +11,13 @@
 //               every load of the step is issued before the first use.
 //   block tier  one thread block per row, the row in registers (kVecs vectors per thread), warp
 //               all-reduce + one shared-memory exchange per statistic.
+//   prefetching block tier  the block tier with the block's next row landing in shared memory (bulk copy)
+//               while the current one is reduced: 16385..32768 columns, one block per SM.
 //   cluster tier one row per thread-block cluster (2, 4 or 8 blocks), each block a slice of the row in
-//               registers, (max, sum) partials exchanged through distributed shared memory.
+//               registers, (max, sum) partials exchanged through distributed shared memory: few very long rows.
+//   reread tier rows beyond one block's registers: one row per block in two passes (online max / sum, then the
+//               row again from the L2); for rows up to 256 KB every load goes through a per-thread
+//               shared-memory ring of (row, pass, chunk) items.
 //   stream tier one thread block per row, three passes over global memory with scalar accesses; any
 //               column count and any alignment (correctness path).
 //
