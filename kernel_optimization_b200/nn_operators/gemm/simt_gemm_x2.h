@@ -9,7 +9,11 @@
 // IEEE-rounded FMAs per instruction.  (Measured alternatives that lost: the same tile with scalar FFMA,
 // 43 against 55 TFLOP/s at 4096^3; 16 x 4 per thread with twice the warps, shared-memory bound; A
 // stored twice in shared memory so that no register moves are needed to build {b, b} pairs, 43 TFLOP/s;
-// 32 x 4 per thread, which halves those moves at the price of three more shared loads per k, 54 TFLOP/s.)
+// 32 x 4 per thread, which halves those moves at the price of three more shared loads per k, 54 TFLOP/s;
+// pairing two consecutive k of one output instead of two rows -- even k in the low half, odd k in the high
+// half, A as [m][k] and B transposed as [n][k] in shared memory so that both operands arrive as ready pairs
+// and no moves are left -- which limits a thread to 8 x 8 outputs, a third more shared-memory data per FMA:
+// shared-memory bound, 1024^3 in 68 us against 49.5 us and 4096^3 at 40 TFLOP/s.)
 //
 // Data path: A[M,K] row-major is copied 4 bytes at a time straight into a TRANSPOSED shared tile
 // As[k][m] (cp.async with a source size of 0 zero-fills out-of-range elements, so every M, N, K is

@@ -48,7 +48,10 @@ class Tensor:
         return cls(int(np.prod(shape, dtype=np.int64)) * byte_per_element, device)
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown: the module globals are already gone, the process frees the buffers
+            pass
 
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h.value:
