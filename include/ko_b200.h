@@ -21,7 +21,10 @@
  *                        scratch lane with cudaMalloc (see ko_context_create below); later calls on
  *                        that stream reuse it;
  *       ko_gemm_*        a combination of (pointer, shape, type) not seen before encodes its TMA
- *                        descriptors (host work only, no device call);
+ *                        descriptors (host work only, no device call); a problem of few tiles and long K
+ *                        is cut into K slices and uses the same per-stream scratch lane as
+ *                        ko_sgemm_f32 -- inside a capture on a stream whose lane does not exist yet
+ *                        it runs unsliced instead;
  *       ko_*_f32_host    the first call on a device creates two copy streams and their events;
  *                        these calls also take one process-wide lock while they enqueue;
  *       ko_sgemm_f32_no_alloc  looks up its scratch address on first use per device (see there);
@@ -252,6 +255,10 @@ int ko_sgemm_f32_no_alloc(int64_t M, int64_t N, int64_t K, const float *A, const
  * nn_operators/gemm/main.cu:190-192; the FP32 sum plus C is rounded to nearest even once).
  * Requires K % 8 == 0 (and N % 8 == 0 for row-major B) and 16-byte aligned A and B; M, N, K tails
  * are handled; an unaligned or odd-pitch D falls back from 16-byte to scalar stores.
+ * A problem whose tiles fill less than the device and whose K is long is computed as K slices: the
+ * tensor-core kernel writes FP32 partial tiles to the context's scratch and a second kernel adds
+ * them in K order (deterministic) and rounds once; the result then differs from the unsliced one
+ * by FP32 summation order only.
  * ---------------------------------------------------------------------------------------- */
 int ko_gemm_f16_f32(int64_t M, int64_t N, int64_t K, const uint16_t *A, const uint16_t *B,
                     const float *C, float *D, void *stream);

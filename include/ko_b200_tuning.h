@@ -64,6 +64,9 @@ int ko_sgemm_f32_tuned(int64_t M, int64_t N, int64_t K, const float *A, const fl
  * model predicts a gain);
  * 2048 = the two-SM kernel (tcgen05 cta_group::2: a pair of CTAs per 256 x 256 tile, either B layout), 2304 = the same
  * with uneven column tiles (column-major B only);
+ * bits 16-23 of bn, added to one of the codes above (single-CTA kernels, i.e. not 2048 / 2304): K slices per tile,
+ * 0 = choose (slices only when bn is 0 too), 1 = none, n <= 64 = n slices (at most K / 64 rounded up) whose FP32 partial
+ * tiles go through the context's scratch lane of `stream` and are added in K order by a second kernel;
  * store_mode: 0 = choose, 1 = TMA-store epilogue (KO_ERR_SHAPE when not possible), 2 = direct stores */
 int ko_gemm_tc_tuned(int fmt, int out_fmt, int b_row_major, int64_t M, int64_t N, int64_t K, const void *A, const void *B,
                      const void *C, void *D, int bn, int store_mode, void *stream);

@@ -5,6 +5,7 @@
 #include "../../include/ko_b200_tuning.h"
 #include "row_launch.h"
 
+#include <algorithm>
 #include <mutex>
 
 #include <cudaTypedefs.h>
@@ -70,8 +71,8 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mb_n
     auto kernel = ko::tc::gemm_tcgen05_kernel<BN, kTmaStore, MT, kBoxes>;
     if (int st = ko::ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), Cfg::kSmemBytes)) return st;
     const long long tiles_n = p.tiles_n ? p.tiles_n : (p.N + BN - 1) / BN;
-    const long long tiles = (long long)((p.M + MT * ko::tc::kBM - 1) / (MT * ko::tc::kBM)) * tiles_n;
-    const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
+    const long long units = (long long)((p.M + MT * ko::tc::kBM - 1) / (MT * ko::tc::kBM)) * tiles_n * (p.split_k > 1 ? p.split_k : 1);
+    const unsigned grid = (unsigned)(units < sm_count ? units : sm_count);
     return ko::launch_overlapped(kernel, grid, (unsigned)ko::tc::kThreads, (size_t)Cfg::kSmemBytes, s, ma, mb, mb_narrow, md, p);
 }
 
@@ -218,6 +219,9 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     ko::Context *ctx = nullptr;
     if (int st = ko::resolve_context(handle, &ctx)) return st;
 
+    // bits 16-23 of the tile code: K slices per tile (0 = choose, 1 = none, n = n slices; single-CTA kernels)
+    int split_request = (bn >> 16) & 0xff;
+    bn &= 0xffff;
     const int bn_request = bn;
     // The two-SM kernel when the caller asks for it, and by default where it measured fastest: medium K, where the
     // single-CTA tiles are limited by bringing operands in (128 x 256) or by their exposed epilogue (256 x 256) --
@@ -230,6 +234,37 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     if (bn == 1024) bn = 256;  // 128 x 256 tiles, uneven column tiles forced
     if (bn == 1280) bn = 512;  // 256 x 256 tiles, uneven column tiles forced
     if (pair) bn = 256;
+    // K slices chosen by default (see below where they are set up): few tiles and a long K.  Modelled time in
+    // microseconds of the 128-row tile in 128 or 256 columns with 1 .. SMs / tiles slices: 3.3 (ramp, first loads,
+    // epilogue) + rounds x K-blocks per slice x time per K-block (0.335 us for 128 x 256, 0.29 us for 128 x 128) and,
+    // when sliced, 3.0 for the second kernel plus the partial tiles' way through the L2 (every slice written once and
+    // read once, D written once, about 5 TB/s).  Fits the measurements within 10 %: 1024 x 384 x 4096 24.7 us unsliced,
+    // 13.9 as 24 tiles x 4 slices; 1024 x 1536 x 4096 26.8 / 22.2 (48 x 3); 256 x 256 x 16384 86.0 / 12.9 (2 x 32).
+    int auto_split = 1;
+    if (bn == 0 && split_request == 0 && !pair) {
+        const long long k_blocks = (K + ko::tc::kBK - 1) / ko::tc::kBK;
+        const long long tiles_m = (M + ko::tc::kBM - 1) / ko::tc::kBM;
+        double best = 1e300, unsliced = 1e300;
+        int best_bn = 0, best_split = 1;
+        for (int width : {128, 256}) {
+            if (width == 256 && N <= 128) continue;
+            const long long tiles = tiles_m * ((N + width - 1) / width);
+            const double t_kb = width == 256 ? 0.335 : 0.29;
+            const long long max_split = std::min<long long>(std::max<long long>(info.sm_count / tiles, 1), std::max<long long>(k_blocks / 4, 1));
+            for (long long sp = 1; sp <= max_split && sp <= 64; ++sp) {
+                const long long rounds = (tiles * sp + info.sm_count - 1) / info.sm_count;
+                // (unsliced, a few tiles on an otherwise idle device take 0.35 us per K-block in either width)
+                double cost = 3.3 + (double)rounds * (double)((k_blocks + sp - 1) / sp) * (sp == 1 ? 0.35 : t_kb);
+                if (sp > 1) cost += 3.0 + (2.0 * sp + 1.0) * (double)M * (double)N * 4.0 / 5e6;
+                if (sp == 1 && cost < unsliced) unsliced = cost;
+                if (cost < best) { best = cost; best_bn = width; best_split = (int)sp; }
+            }
+        }
+        if (best_split > 1 && best < 0.95 * unsliced && k_blocks >= 16) {
+            bn = best_bn;
+            auto_split = best_split;
+        }
+    }
     if (bn == 0) {
         const double e256 = wave_efficiency(M, N, 256, info.sm_count);
         // a 128 x 128 tile brings twice the operand bytes per MMA of a 128 x 256 tile: on long K it runs at little more
@@ -250,6 +285,7 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     }
     KO_REQUIRE(bn == 64 || bn == 128 || bn == 256 || bn == 512, KO_ERR_INVALID_ARG,
                "gemm: tile code %d not in {64,128,256,512,1024,1280,2048,2304}", bn_request);
+    KO_REQUIRE(split_request <= 64, KO_ERR_INVALID_ARG, "gemm: %d K slices out of range (at most 64)", split_request);
     const int mt = bn == 512 ? 2 : 1;
     if (bn == 512) bn = 256;
 
@@ -303,19 +339,55 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.C = C; p.D = D; p.fmt = fmt; p.out_fmt = out_fmt; p.b_row_major = b_row_major;
     p.tiles_n = cols.tiles_n; p.wide_tiles_n = cols.wide_tiles_n; p.bn_wide = cols.bn_wide; p.bn_narrow = cols.bn_narrow;
+    p.split_k = 1; p.partials = nullptr;
     if (int st = ko::device_status_word(0, &p.status)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    // K slices.  A tile's main loop is a serial chain of K / 64 K-blocks (about 0.34 us each), so a problem with fewer
+    // tiles than SMs and a long K leaves most of the device idle for the whole chain: 1024 x 384 x 4096 took 24.5 us
+    // whatever the tile shape.  Cut into slices, every SM gets a part of the chain; the price is one FP32 partial tile
+    // per slice, written by the GEMM kernel and summed into D by a second, small kernel (both L2-resident).
+    KO_REQUIRE(split_request <= 1 || !pair, KO_ERR_INVALID_ARG, "gemm: K slices are not available in the two-SM kernel");
+    long long sum_blocks = 0;  // blocks of the kernel that adds the slices (one per 32 x 32 chunk of every tile)
+    if (!pair) {
+        const long long tile_m = (long long)mt * ko::tc::kBM;
+        const long long tiles = ((M + tile_m - 1) / tile_m) * (cols.tiles_n ? cols.tiles_n : (N + bn - 1) / bn);
+        const long long k_blocks = (K + ko::tc::kBK - 1) / ko::tc::kBK;
+        long long split = split_request ? split_request : auto_split;
+        if (split > k_blocks) split = k_blocks;
+        if (split > 1) {
+            // the scratch lane of this stream in the context, shared with the SGEMM's K split (launches of one stream
+            // run one after the other); sized once for the largest default request: one slot per SM
+            const size_t slot_floats = (size_t)tile_m * bn;
+            const size_t floor_tiles = (size_t)4 * info.sm_count;
+            ko::SgemmScratch sc;
+            const int st = ctx->sgemm_scratch(s, (size_t)(tiles * split) * slot_floats, 0, floor_tiles * 128 * 128, floor_tiles, &sc);
+            if (st == KO_OK) {
+                p.split_k = (int)split;
+                p.partials = sc.partials;
+                sum_blocks = tiles * (tile_m / 32) * (bn / 32);
+            } else if (split_request > 1) {
+                return st;
+            }  // chosen by default but no scratch to be had (a stream being captured): one slice
+        }
+    }
     if (pair)
         return tma_store ? launch_pair<true>(map_a, map_b, map_b_narrow, map_d, p, pair_slots, s)
                          : launch_pair<false>(map_a, map_b, map_b_narrow, map_d, p, pair_slots, s);
-    if (mt == 2)
-        return tma_store ? launch<256, true, 2>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s)
-                         : launch<256, false, 2>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s);
-    switch (bn) {
-        case 64: return tma_store ? launch<64, true>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s) : launch<64, false>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s);
-        case 128: return tma_store ? launch<128, true>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s) : launch<128, false>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s);
-        default: return tma_store ? launch<256, true>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s) : launch<256, false>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s);
+    int st;
+    if (mt == 2) {
+        st = tma_store ? launch<256, true, 2>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s)
+                       : launch<256, false, 2>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s);
+    } else {
+        switch (bn) {
+            case 64: st = tma_store ? launch<64, true>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s) : launch<64, false>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s); break;
+            case 128: st = tma_store ? launch<128, true>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s) : launch<128, false>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s); break;
+            default: st = tma_store ? launch<256, true>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s) : launch<256, false>(map_a, map_b, map_b_narrow, map_d, p, info.sm_count, s); break;
+        }
     }
+    if (st != KO_OK || p.split_k <= 1) return st;
+    KO_REQUIRE(sum_blocks <= 0x7fffffffLL, KO_ERR_SHAPE, "gemm: %lld chunks exceed the grid limit", sum_blocks);
+    return ko::launch_overlapped(ko::tc::gemm_slice_sum_kernel<256>, (unsigned)sum_blocks, 256u, (size_t)0, s, p, mt * ko::tc::kBM, bn);
 }
 
 }  // namespace

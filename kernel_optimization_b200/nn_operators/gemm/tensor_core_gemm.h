@@ -221,6 +221,12 @@ struct GemmParams {
     // bn_narrow <= bn_wide <= BN; column-major B only): a tile count that fills the last wave of CTAs instead of
     // leaving part of it idle.  map_b then has a box of bn_wide rows and map_b_narrow one of bn_narrow rows.
     int tiles_n, wide_tiles_n, bn_wide, bn_narrow;
+    // K slices (single-CTA kernel only).  split_k > 1: every tile is computed by split_k CTAs, each over a contiguous
+    // range of K-blocks, and every CTA writes its FP32 partial tile to `partials` (one slot of kTileM x BN floats per
+    // (tile, slice)) instead of D; gemm_slice_sum_kernel, launched behind this kernel, adds the slices in K order and
+    // writes D.
+    int split_k;
+    float *partials;
 };
 
 // where column tile tn starts and how wide it is
@@ -319,82 +325,106 @@ __device__ __forceinline__ void store_row_segment(const float (&v)[32], const Ge
     }
 }
 
+// One 32 x 32 chunk of D from registers: lane = row row_base + lane, r = its 32 consecutive columns starting at column
+// `col` (FP32 bits).  kTmaStore: registers -> swizzled shared box -> TMA store (box store_seq % kBoxes of this warp's
+// kBoxes staging boxes of box_bytes each, store_seq counts the warp's stores across tiles); otherwise direct 16-byte
+// stores (and + C).  Warp-collective.
+template <bool kTmaStore, int kBoxes>
+__device__ __forceinline__ void store_chunk(const CUtensorMap *map_d, const GemmParams &p, const uint32_t (&r)[32], int row_base,
+                                            int col, int lane, uint32_t warp_boxes, uint32_t box_bytes, uint32_t &store_seq) {
+    if constexpr (kTmaStore) {
+        // row = lane, 8 chunks of 16 B, chunk j stored at j ^ (row & 7): conflict-free, and exactly the 128-byte
+        // swizzle the store's tensor map undoes
+        const uint32_t box = warp_boxes + (store_seq % kBoxes) * box_bytes;
+        if (lane == 0) bulk_wait_group_read<kBoxes - 1>();  // the store issued from this box kBoxes chunks ago has read it
+        __syncwarp();
+        if (p.out_fmt == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t dst = box + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(r[4 * j]), "r"(r[4 * j + 1]),
+                             "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                             : "memory");
+            }
+        } else {
+            // 16-bit D: rows of 64 bytes, 4 chunks of 16 B, chunk j stored at j ^ ((row >> 1) & 3): the
+            // 64-byte swizzle of the store's tensor map, conflict-free for 8 consecutive rows
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t dst = box + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                             "r"(pack16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]), p.out_fmt)),
+                             "r"(pack16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]), p.out_fmt)),
+                             "r"(pack16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]), p.out_fmt)),
+                             "r"(pack16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]), p.out_fmt))
+                             : "memory");
+            }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            // rows / columns beyond M / N are clipped by the map; a box that lies entirely outside is
+            // skipped, but still closes a (then empty) group so that the box rotation holds
+            if (row_base < p.M && col < p.N) tma_store_2d(map_d, col, row_base, box);
+            bulk_commit_group();
+        }
+        ++store_seq;
+    } else {
+        const int row = row_base + lane;
+        if (row < p.M && col < p.N) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            if (p.out_fmt == 0) store_row_segment<float>(v, p, row, col);
+            else if (p.out_fmt == 1) store_row_segment<__half>(v, p, row, col);
+            else store_row_segment<__nv_bfloat16>(v, p, row, col);
+        }
+    }
+}
+
 // One epilogue warp's share of one 128-row block of a tile: its 32 accumulator rows (TMEM lanes of its quadrant),
 // columns [0, bn) of the accumulator that starts at TMEM address t_row, written to D rows row_base .. row_base + 31,
-// columns col0 .. col0 + bn - 1.  kTmaStore: registers -> swizzled shared box -> TMA store (box n % kBoxes of this
-// warp's kBoxes staging boxes of box_bytes each, store_seq counts the warp's stores across tiles); otherwise direct
-// 16-byte stores (and + C).  Warp-collective: all 32 lanes call it.
+// columns col0 .. col0 + bn - 1, chunk by chunk (store_chunk).  Warp-collective: all 32 lanes call it.
 template <bool kTmaStore, int kBoxes>
 __device__ __forceinline__ void epilogue_block(const CUtensorMap *map_d, const GemmParams &p, uint32_t t_row, int row_base,
                                                int col0, int bn, int lane, uint32_t warp_boxes, uint32_t box_bytes,
                                                uint32_t &store_seq) {
     if constexpr (kTmaStore) {
-        // row = lane, 8 chunks of 16 B, chunk j stored at j ^ (row & 7): conflict-free, and exactly the 128-byte
-        // swizzle the store's tensor map undoes
         // two register sets: the load of the next 32 columns is in flight while these are written out
         uint32_t ra[32], rb[32];
-        auto write_out = [&](const uint32_t (&r)[32], int c0) {
-            const uint32_t box = warp_boxes + (store_seq % kBoxes) * box_bytes;
-            if (lane == 0) bulk_wait_group_read<kBoxes - 1>();  // the store issued from this box kBoxes chunks ago has read it
-            __syncwarp();
-            if (p.out_fmt == 0) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint32_t dst = box + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(r[4 * j]), "r"(r[4 * j + 1]),
-                                 "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
-                                 : "memory");
-                }
-            } else {
-                // 16-bit D: rows of 64 bytes, 4 chunks of 16 B, chunk j stored at j ^ ((row >> 1) & 3): the
-                // 64-byte swizzle of the store's tensor map, conflict-free for 8 consecutive rows
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t dst = box + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
-                                 "r"(pack16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]), p.out_fmt)),
-                                 "r"(pack16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]), p.out_fmt)),
-                                 "r"(pack16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]), p.out_fmt)),
-                                 "r"(pack16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]), p.out_fmt))
-                                 : "memory");
-                }
-            }
-            fence_proxy_async();
-            __syncwarp();
-            const int col = col0 + c0;
-            if (lane == 0) {
-                // rows / columns beyond M / N are clipped by the map; a box that lies entirely outside is
-                // skipped, but still closes a (then empty) group so that the box rotation holds
-                if (row_base < p.M && col < p.N) tma_store_2d(map_d, col, row_base, box);
-                bulk_commit_group();
-            }
-            ++store_seq;
-        };
         tmem_ld_32x32_issue(t_row, ra);
 #pragma unroll 1
         for (int c0 = 0; c0 < bn; c0 += 64) {
             tmem_ld_wait();
             if (c0 + 32 < bn) tmem_ld_32x32_issue(t_row + c0 + 32, rb);
-            write_out(ra, c0);
+            store_chunk<true, kBoxes>(map_d, p, ra, row_base, col0 + c0, lane, warp_boxes, box_bytes, store_seq);
             if (c0 + 32 < bn) {
                 tmem_ld_wait();
                 if (c0 + 64 < bn) tmem_ld_32x32_issue(t_row + c0 + 64, ra);
-                write_out(rb, c0 + 32);
+                store_chunk<true, kBoxes>(map_d, p, rb, row_base, col0 + c0 + 32, lane, warp_boxes, box_bytes, store_seq);
             }
         }
     } else {
-        const int row = row_base + lane;
 #pragma unroll 1
         for (int c0 = 0; c0 < bn; c0 += 32) {
-            float v[32];
-            tmem_ld_32x32(t_row + c0, v);  // warp-collective: every lane takes part
-            const int col = col0 + c0;
-            if (row < p.M && col < p.N) {
-                if (p.out_fmt == 0) store_row_segment<float>(v, p, row, col);
-                else if (p.out_fmt == 1) store_row_segment<__half>(v, p, row, col);
-                else store_row_segment<__nv_bfloat16>(v, p, row, col);
-            }
+            uint32_t r[32];
+            tmem_ld_32x32_issue(t_row + c0, r);  // warp-collective: every lane takes part
+            tmem_ld_wait();
+            store_chunk<false, kBoxes>(map_d, p, r, row_base, col0 + c0, lane, warp_boxes, box_bytes, store_seq);
         }
+    }
+}
+
+// One epilogue warp writes its 32 rows x bn columns of a K slice's accumulator into the slice's slot: 32 x 32 chunks
+// of 4 KB, row-major inside a chunk (a lane's 32 columns are 128 contiguous bytes).
+__device__ __forceinline__ void publish_block(float *slot_chunks, uint32_t t_row, int bn, int lane) {
+#pragma unroll 1
+    for (int c0 = 0; c0 < bn; c0 += 32) {
+        float v[32];
+        tmem_ld_32x32(t_row + c0, v);
+        float4 *dst = reinterpret_cast<float4 *>(slot_chunks + ((size_t)(c0 >> 5) << 10) + lane * 32);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) __stcg(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
     }
 }
 
@@ -425,8 +455,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = p.tiles_n ? p.tiles_n : (p.N + BN - 1) / BN;
-    const long long num_tiles = (long long)tiles_m * tiles_n;
     const int k_blocks = (p.K + kBK - 1) / kBK;
+    // work units: (tile, K slice), the slices of a tile next to each other so that they run at the same time
+    const int split = p.split_k > 1 ? p.split_k : 1;
+    const long long num_units = (long long)tiles_m * tiles_n * split;
+    auto unit_of = [&](long long u, long long &t, int &slice, int &kb0, int &kb1) {
+        if (split == 1) {
+            t = u; slice = 0; kb0 = 0; kb1 = k_blocks;
+        } else {
+            t = u / split;
+            slice = (int)(u - t * split);
+            kb0 = (int)((long long)k_blocks * slice / split);
+            kb1 = (int)((long long)k_blocks * (slice + 1) / split);
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) {
@@ -461,13 +503,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                int tm, tn, col0, bn;
+            for (long long u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                long long t;
+                int slice, kb0, kb1, tm, tn, col0, bn;
+                unit_of(u, t, slice, kb0, kb1);
                 tile_of(p, t, tiles_m, tiles_n, tm, tn);
                 column_tile<BN>(p, tn, col0, bn);
                 const CUtensorMap *b_map = (p.tiles_n && bn != p.bn_wide) ? &map_b_narrow : &map_b;  // box of bn rows
                 const uint32_t stage_bytes = (uint32_t)Cfg::kBytesA + (uint32_t)bn * (kBK * 2);
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % Cfg::kStages;
                     const uint32_t phase = (it / Cfg::kStages) & 1u;
                     if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag)) {
@@ -504,8 +548,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
-            for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
-                int tm, tn, col0, bn;
+            for (long long u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++local_tile) {
+                long long t;
+                int slice, kb0, kb1, tm, tn, col0, bn;
+                unit_of(u, t, slice, kb0, kb1);
                 tile_of(p, t, tiles_m, tiles_n, tm, tn);
                 column_tile<BN>(p, tn, col0, bn);
                 const uint32_t idesc = make_idesc(p.fmt, kBM, bn) | (p.b_row_major ? 1u << 16 : 0u);  // bit 16: B is MN-major
@@ -514,7 +560,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!mbar_wait(acc_free_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % Cfg::kStages;
                     const uint32_t phase = (it / Cfg::kStages) & 1u;
                     if (!mbar_wait(full_bar(s), phase, abort_flag)) { ok = false; break; }
@@ -527,10 +573,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         // row-major B: 16 K-rows further = two 8-row atoms = 2048 bytes
                         const uint64_t db = p.b_row_major ? smem_desc_mn_major_sw128(b_addr + k * 2048)
                                                           : smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
-                        umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_f16(d_tmem, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
                         if (MT == 2) {  // rows 128..255 of the tile: 16 KB further in the stage, accumulator columns BN..2BN-1
                             const uint64_t da1 = smem_desc_k_major_sw128(a_addr + kBM * kBK * 2 + k * kUmmaK * 2);
-                            umma_f16(d_tmem + BN, da1, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                            umma_f16(d_tmem + BN, da1, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
                         }
                     }
                     umma_commit(empty_bar(s));  // the stage is reusable once these MMAs have read it
@@ -554,8 +600,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t local_tile = 0;
         uint32_t store_seq = 0;  // TMA stores issued by this warp so far: store n uses staging box n % kBoxes
         bool ok = true;
-        for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
-            int tm, tn, col0, bn;
+        for (long long u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++local_tile) {
+            long long t;
+            int slice, kb0, kb1, tm, tn, col0, bn;
+            unit_of(u, t, slice, kb0, kb1);
             tile_of(p, t, tiles_m, tiles_n, tm, tn);
             column_tile<BN>(p, tn, col0, bn);
             const uint32_t acc = MT == 1 ? (local_tile & 1u) : 0u, acc_phase = (MT == 1 ? (local_tile >> 1) : local_tile) & 1u;
@@ -566,13 +614,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 break;
             }
             tc_fence_after();
+            if (split > 1) {
+                // a K slice: the partial tile goes to its slot, gemm_slice_sum_kernel writes D
+                constexpr size_t kSlotFloats = (size_t)kTileM * BN;
+                float *slot = p.partials + ((size_t)t * split + slice) * kSlotFloats;
 #pragma unroll 1
-            for (int half = 0; half < MT; ++half) {
-                const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (MT == 1 ? acc * BN : half * BN);
-                epilogue_block<kTmaStore, kBoxes>(&map_d, p, t_row, tm * kTileM + half * kBM + quad * 32, col0, bn, lane,
-                                                  store_base + (uint32_t)((warp - 2) * kBoxes) * Cfg::kStoreBoxBytes,
-                                                  (uint32_t)Cfg::kStoreBoxBytes, store_seq);
-            }  // halves
+                for (int half = 0; half < MT; ++half) {
+                    const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (MT == 1 ? acc * BN : half * BN);
+                    publish_block(slot + ((size_t)((half * 4 + quad) * (BN / 32)) << 10), t_row, bn, lane);
+                }
+            } else {
+#pragma unroll 1
+                for (int half = 0; half < MT; ++half) {
+                    const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (MT == 1 ? acc * BN : half * BN);
+                    epilogue_block<kTmaStore, kBoxes>(&map_d, p, t_row, tm * kTileM + half * kBM + quad * 32, col0, bn, lane,
+                                                      store_base + (uint32_t)((warp - 2) * kBoxes) * Cfg::kStoreBoxBytes,
+                                                      (uint32_t)Cfg::kStoreBoxBytes, store_seq);
+                }  // halves
+            }
             // the accumulator buffer may be overwritten once all four warps have read it
             tc_fence_before();
             __syncwarp();
@@ -588,6 +647,75 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// Second step of a GEMM cut into K slices: D = sum over the slices of a tile, in K order, (+ C), rounded once to D's
+// type.  One block per 32 x 32 chunk of a tile (the unit gemm_tcgen05_kernel's epilogue warps write): thread i takes
+// columns 4 * (i % 8) .. + 3 of row i / 8, so a warp reads 512 contiguous bytes of every slice and writes four
+// 128-byte row segments of D.  tile_m / bn_full: the first kernel's tile (kTileM x BN).
+// (a template only so that the header may be included by several translation units)
+template <int kBlock = 256>
+__global__ void __launch_bounds__(kBlock) gemm_slice_sum_kernel(const GemmParams p, int tile_m, int bn_full) {
+    static_assert(kBlock == 256, "one thread per float4 of a 32 x 32 chunk");
+    const int chunks_n = bn_full / 32, chunks_per_tile = (tile_m / 32) * chunks_n;
+    const long long t = blockIdx.x / chunks_per_tile;
+    const int chunk = (int)(blockIdx.x - t * chunks_per_tile);
+    const int tiles_m = (p.M + tile_m - 1) / tile_m, tiles_n = p.tiles_n ? p.tiles_n : (p.N + bn_full - 1) / bn_full;
+    int tm, tn, col0, bn;
+    tile_of(p, t, tiles_m, tiles_n, tm, tn);
+    if (p.tiles_n == 0) {
+        col0 = tn * bn_full;
+        bn = bn_full;
+    } else {
+        column_tile<0>(p, tn, col0, bn);
+    }
+    const int row = tm * tile_m + (chunk / chunks_n) * 32 + (int)threadIdx.x / 8;
+    const int c_in_tile = (chunk % chunks_n) * 32 + ((int)threadIdx.x & 7) * 4;
+    const int col = col0 + c_in_tile;
+    grid_launch_dependents();
+    grid_dependency_wait();  // the slices are complete and visible
+    if (c_in_tile >= bn || row >= p.M || col >= p.N) return;
+    const size_t slot_floats = (size_t)tile_m * bn_full;
+    const float4 *src = reinterpret_cast<const float4 *>(p.partials + (size_t)t * p.split_k * slot_floats + ((size_t)chunk << 10)) + threadIdx.x;
+    // four slices' loads in flight at a time (they are independent), added in slice order
+    const size_t slot_vecs = slot_floats / 4;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < p.split_k; s0 += 4) {
+        float4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (s0 + i < p.split_k) v[i] = __ldcg(src + (size_t)(s0 + i) * slot_vecs);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (s0 + i < p.split_k) {
+                if (s0 + i == 0) sum = v[0];
+                else { sum.x += v[i].x; sum.y += v[i].y; sum.z += v[i].z; sum.w += v[i].w; }
+            }
+    }
+    float v[4] = {sum.x, sum.y, sum.z, sum.w};
+    const size_t off = (size_t)row * p.N + col;
+    const bool whole = col + 4 <= p.N;
+    if (p.out_fmt == 0) {
+        const float *C = static_cast<const float *>(p.C);
+        float *D = static_cast<float *>(p.D);
+        if (whole && p.N % 4 == 0 && (reinterpret_cast<uintptr_t>(D) & 15u) == 0 && (C == nullptr || (reinterpret_cast<uintptr_t>(C) & 15u) == 0)) {
+            if (C) {
+                const float4 c = *reinterpret_cast<const float4 *>(C + off);
+                v[0] += c.x; v[1] += c.y; v[2] += c.z; v[3] += c.w;
+            }
+            *reinterpret_cast<float4 *>(D + off) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+            for (int e = 0; e < 4 && col + e < p.N; ++e) D[off + e] = C ? v[e] + C[off + e] : v[e];
+        }
+    } else if (p.out_fmt == 1) {
+        const __half *C = static_cast<const __half *>(p.C);
+        __half *D = static_cast<__half *>(p.D);
+        for (int e = 0; e < 4 && col + e < p.N; ++e) D[off + e] = __float2half_rn(C ? v[e] + __half2float(C[off + e]) : v[e]);
+    } else {
+        const __nv_bfloat16 *C = static_cast<const __nv_bfloat16 *>(p.C);
+        __nv_bfloat16 *D = static_cast<__nv_bfloat16 *>(p.D);
+        for (int e = 0; e < 4 && col + e < p.N; ++e) D[off + e] = __float2bfloat16_rn(C ? v[e] + __bfloat162float(C[off + e]) : v[e]);
     }
 }
 

@@ -46,3 +46,36 @@ def test_operator_sequence_replays_from_a_cuda_graph(cuda, lib, ko, oracle):
             assert cuda.equal(got, want)
     assert lib.ko_poll_device_status() == 0
     assert oracle.max_abs_err(y.cpu().numpy(), oracle.softmax_f64(x.cpu().numpy())) <= 1e-6
+
+
+def test_sliced_gemm_in_a_graph_and_capture_without_a_scratch_lane(cuda, lib, ko, oracle):
+    """A GEMM of few tiles and long K is cut into K slices, which need the stream's scratch lane: warmed, it replays
+    from a graph bit for bit; captured on a stream that has no lane yet it may not allocate and runs unsliced."""
+    dev = "cuda"
+    a = (cuda.rand((128, 8192), device=dev) * 2 - 1).bfloat16()
+    b = (cuda.rand((128, 8192), device=dev) * 2 - 1).bfloat16()
+    d = cuda.empty((128, 128), device=dev)
+    want = a.double() @ b.double().t()
+    side = cuda.cuda.Stream()
+    with cuda.cuda.stream(side):
+        ko.gemm_tc(a, b, out=d)              # allocates this stream's lane
+        side.synchronize()
+        eager = d.clone()
+        graph = cuda.cuda.CUDAGraph()
+        with cuda.cuda.graph(graph, stream=side):
+            ko.gemm_tc(a, b, out=d)
+    d.fill_(float("nan"))
+    graph.replay()
+    cuda.cuda.synchronize()
+    assert cuda.equal(d, eager)
+    assert float((eager.double() - want).norm() / want.norm()) <= 1e-5
+    fresh = cuda.cuda.Stream()
+    with cuda.cuda.stream(fresh):
+        graph2 = cuda.cuda.CUDAGraph()
+        with cuda.cuda.graph(graph2, stream=fresh):
+            ko.gemm_tc(a, b, out=d)
+    d.fill_(float("nan"))
+    graph2.replay()
+    cuda.cuda.synchronize()
+    assert float((d.double() - want).norm() / want.norm()) <= 1e-5
+    assert lib.ko_poll_device_status() == 0

@@ -358,3 +358,69 @@ def test_two_sm_kernel_with_uneven_column_tiles(cuda, lib, oracle, kind, M, N, K
     base = _run(cuda, lib, kind, ab, bb, bn=256)
     assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=2304), base)
     assert np.array_equal(_run(cuda, lib, kind, ab, bb, bn=2304, store_mode=2), base)
+
+
+# ---- K slices: few tiles, long K (FP32 partial tiles through the context's scratch, second kernel adds them in K order)
+
+def _slices(bn, n):
+    return bn | (n << 16)
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("bn", [64, 128, 256, 512])
+@pytest.mark.parametrize("slices", [2, 3, 7])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 1024), (300, 520, 2048), (257, 72, 776), (130, 130, 136), (1, 4, 8)])
+def test_k_slices_against_the_oracle(cuda, lib, oracle, kind, bn, slices, M, N, K):
+    # more slices than K-blocks is clamped; tails in M, N and K; TMA-store epilogue where D allows it
+    _case(cuda, lib, oracle, kind, M, N, K, bn=_slices(bn, slices))
+
+
+@pytest.mark.parametrize("slices", [2, 5])
+@pytest.mark.parametrize("M,N,K", [(300, 520, 2048), (200, 37, 640)])
+def test_k_slices_with_c_direct_stores_and_odd_pitch(cuda, lib, oracle, slices, M, N, K):
+    _case(cuda, lib, oracle, "bf16", M, N, K, with_c=True, bn=_slices(256, slices), store_mode=2)
+    _case(cuda, lib, oracle, "f16", M, N, K, with_c=True, bn=_slices(128, slices))
+
+
+def test_k_slices_are_deterministic_and_close_to_the_unsliced_bits(cuda, lib, oracle):
+    M, N, K = 384, 768, 4096
+    to_bits, from_bits = _bits(oracle, "bf16")
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 5, 0)), to_bits(oracle.fill_uniform((N, K), 5, 1))
+    whole = _run(cuda, lib, "bf16", ab, bb, bn=_slices(256, 1))
+    first = _run(cuda, lib, "bf16", ab, bb, bn=_slices(256, 4))
+    again = _run(cuda, lib, "bf16", ab, bb, bn=_slices(256, 4))
+    assert np.array_equal(first, again)
+    # the slices are FP32 sums of exact products added in K order: only the summation order differs
+    assert oracle.rel_frobenius(first, whole) <= tight(K)
+    # the same slices in another tile shape see the same K ranges per output: identical bits
+    assert np.array_equal(first, _run(cuda, lib, "bf16", ab, bb, bn=_slices(128, 4)))
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_k_slices_with_16_bit_output_and_row_major_b(cuda, lib, oracle, kind):
+    M, N, K = 200, 264, 1024
+    to_bits, from_bits = _bits(oracle, kind)
+    ab, bb = to_bits(oracle.fill_uniform((M, K), 6, 0)), to_bits(oracle.fill_uniform((N, K), 6, 1))
+    cb = to_bits(oracle.fill_uniform((M, N), 6, 2))
+    want32 = _run(cuda, lib, kind, ab, bb, from_bits(cb).astype(np.float32), bn=_slices(256, 3))
+    got = _run(cuda, lib, kind, ab, bb, cb, bn=_slices(256, 3), out16=True)
+    assert np.array_equal(got, to_bits(want32))   # the FP32 sum (+ C) rounded once
+    rm = _run(cuda, lib, kind, ab, np.ascontiguousarray(bb.T), bn=_slices(256, 3), b_row_major=True)
+    assert np.array_equal(rm, _run(cuda, lib, kind, ab, bb, bn=_slices(256, 3)))
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 768, 4096), (128, 128, 8192), (1024, 1024, 8192), (64, 64, 4096)])
+def test_default_choice_for_few_tiles_and_long_k(cuda, lib, oracle, M, N, K):
+    # shapes the launcher cuts into K slices by default
+    _case(cuda, lib, oracle, "bf16", M, N, K)
+    _case(cuda, lib, oracle, "f16", M, N, K, with_c=True)
+
+
+def test_k_slices_argument_checks(cuda, lib):
+    a = cuda.zeros((256, 256), dtype=cuda.bfloat16, device="cuda")
+    d = cuda.zeros((256, 256), dtype=cuda.float32, device="cuda")
+    s = cuda.cuda.current_stream().cuda_stream
+    # not in the two-SM kernel, and at most 64 slices
+    assert lib.ko_gemm_tc_tuned(1, 0, 0, 256, 256, 256, a.data_ptr(), a.data_ptr(), None, d.data_ptr(), _slices(2048, 2), 0, s) != 0
+    assert lib.ko_gemm_tc_tuned(1, 0, 0, 256, 256, 256, a.data_ptr(), a.data_ptr(), None, d.data_ptr(), _slices(256, 65), 0, s) != 0
+    cuda.cuda.synchronize()

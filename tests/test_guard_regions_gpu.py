@@ -168,14 +168,14 @@ def test_sgemm_no_alloc_stays_inside_its_buffers(cuda, lib, oracle):
 
 
 # ------------------------------------------------------------------------------------------------
-# tcgen05 GEMM: every tile width and the two-SM kernel (bn = 2048), both epilogues (TMA store / direct), both B layouts,
-# FP32 and 16-bit D
+# tcgen05 GEMM: every tile width, the two-SM kernel (bn = 2048) and K slices, both epilogues (TMA store / direct), both
+# B layouts, FP32 and 16-bit D
 # ------------------------------------------------------------------------------------------------
 TC_SHAPES = [(1, 4, 8), (100, 36, 56), (129, 260, 136), (128, 64, 64), (256, 512, 256), (1000, 520, 200), (300, 8, 64), (200, 37, 64)]
 
 
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
-@pytest.mark.parametrize("bn", [0, 64, 128, 256, 512, 2048])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256, 512, 2048, 256 | (3 << 16)])   # the last: three K slices per tile
 @pytest.mark.parametrize("mode", ["tma_store", "direct", "plus_c", "out16", "row_major_b"])
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
 def test_tensor_core_gemm_stays_inside_its_buffers(cuda, lib, oracle, M, N, K, mode, bn, kind):
