@@ -690,6 +690,7 @@ CASES = {
     "softmax_c1": "softmax FP32 [196608,128] (benchmark config 1), 4 rotating buffer sets",
     "gemm_bf16_ffn_pair": "BF16 GEMM 16384x3072x768 on the two-SM kernel (tcgen05 cta_group::2)",
     "gemm_bf16_4096_pair": "BF16 GEMM 4096^3 on the two-SM kernel (tcgen05 cta_group::2)",
+    "gemm_bf16_few_tiles": "BF16 GEMM 1024x384x4096: 24 tiles cut into K slices, partial tiles added by a second kernel (the default for such shapes)",
 }
 
 
@@ -713,7 +714,7 @@ def run_case(args):
         launch = lambda: native.check(lib.ko_sgemm_f32(n, n, n, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s()), name)  # noqa: E731
         work, unit = 2.0 * n ** 3, "TFLOP/s"
     elif name.startswith("gemm_bf16"):
-        M, N, K = (4096, 4096, 4096) if "4096" in name else (16384, 3072, 768)
+        M, N, K = (1024, 384, 4096) if "few_tiles" in name else (4096, 4096, 4096) if "4096" in name else (16384, 3072, 768)
         a = torch.from_numpy(ko.fill_uniform((M, K), 3, 0, dtype=2).view(np.int16)).to(dev)
         b = torch.from_numpy(ko.fill_uniform((N, K), 3, 1, dtype=2).view(np.int16)).to(dev)
         d = torch.empty((M, N), device=dev)
