@@ -236,10 +236,11 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     if (pair) bn = 256;
     // K slices chosen by default (see below where they are set up): few tiles and a long K.  Modelled time in
     // microseconds of the 128-row tile in 128 or 256 columns with 1 .. SMs / tiles slices: 3.3 (ramp, first loads,
-    // epilogue) + rounds x K-blocks per slice x time per K-block (0.335 us for 128 x 256, 0.29 us for 128 x 128) and,
-    // when sliced, 3.0 for the second kernel plus the partial tiles' way through the L2 (every slice written once and
-    // read once, D written once, about 5 TB/s).  Fits the measurements within 10 %: 1024 x 384 x 4096 24.7 us unsliced,
-    // 13.9 as 24 tiles x 4 slices; 1024 x 1536 x 4096 26.8 / 22.2 (48 x 3); 256 x 256 x 16384 86.0 / 12.9 (2 x 32).
+    // epilogue) + rounds x K-blocks per slice x time per K-block (unsliced 0.31 us; sliced 0.29 us for 128 x 256,
+    // 0.25 us for 128 x 128) and, when sliced, 3.0 for the second kernel plus the partial tiles' way through the L2
+    // (every slice written once and read once, D written once, about 5 TB/s).  Fits the measurements within 10 %:
+    // 1024 x 384 x 4096 21.8 us unsliced, 12.5 sliced; 1024 x 1536 x 4096 23.8 / 21.0 (48 tiles x 3);
+    // 256 x 256 x 16384 74.3 / 12.4 (2 x 32).
     int auto_split = 1;
     if (bn == 0 && split_request == 0 && !pair) {
         const long long k_blocks = (K + ko::tc::kBK - 1) / ko::tc::kBK;
@@ -249,12 +250,11 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
         for (int width : {128, 256}) {
             if (width == 256 && N <= 128) continue;
             const long long tiles = tiles_m * ((N + width - 1) / width);
-            const double t_kb = width == 256 ? 0.335 : 0.29;
+            const double t_kb = width == 256 ? 0.29 : 0.25;
             const long long max_split = std::min<long long>(std::max<long long>(info.sm_count / tiles, 1), std::max<long long>(k_blocks / 4, 1));
             for (long long sp = 1; sp <= max_split && sp <= 64; ++sp) {
                 const long long rounds = (tiles * sp + info.sm_count - 1) / info.sm_count;
-                // (unsliced, a few tiles on an otherwise idle device take 0.35 us per K-block in either width)
-                double cost = 3.3 + (double)rounds * (double)((k_blocks + sp - 1) / sp) * (sp == 1 ? 0.35 : t_kb);
+                double cost = 3.3 + (double)rounds * (double)((k_blocks + sp - 1) / sp) * (sp == 1 ? 0.31 : t_kb);
                 if (sp > 1) cost += 3.0 + (2.0 * sp + 1.0) * (double)M * (double)N * 4.0 / 5e6;
                 if (sp == 1 && cost < unsliced) unsliced = cost;
                 if (cost < best) { best = cost; best_bn = width; best_split = (int)sp; }

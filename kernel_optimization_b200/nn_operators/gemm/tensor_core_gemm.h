@@ -130,6 +130,19 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t desc_a, uint6
         : "memory");
 }
 // the mbarrier is arrived on once every tcgen05.mma issued so far by this thread has completed
+// the same with the descriptors given as (low, high) words: the low word holds the start address (16-byte units, bits
+// 0-13) and the leading offset, so stepping through a stage is one 32-bit add on it
+__device__ __forceinline__ void umma_f16_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -501,7 +514,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t it = 0, stage = 0, fill = 0;  // K-blocks issued, ring position of the next one, times the ring went round
             bool ok = true;
             for (long long u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
                 long long t;
@@ -512,8 +525,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const CUtensorMap *b_map = (p.tiles_n && bn != p.bn_wide) ? &map_b_narrow : &map_b;  // box of bn rows
                 const uint32_t stage_bytes = (uint32_t)Cfg::kBytesA + (uint32_t)bn * (kBK * 2);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % Cfg::kStages;
-                    const uint32_t phase = (it / Cfg::kStages) & 1u;
+                    const int s = (int)stage;
+                    const uint32_t phase = fill & 1u;
+                    if (++stage == (uint32_t)Cfg::kStages) { stage = 0; ++fill; }
                     if (!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag)) {
                         if (!*abort_flag) atomicCAS(p.status, kStatusOk, kTimeoutProducer);
                         *abort_flag = 1;
@@ -547,6 +561,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             uint32_t it = 0, local_tile = 0;
+            uint32_t stage = 0, phase = 0;  // ring position of K-block `it` and the parity of its fill
+            // Shared-memory descriptors as two words (smem_desc_k_major_sw128 / smem_desc_mn_major_sw128 of the ring's
+            // first stage): the high word (stride 1024 bytes, version, 128-byte swizzle) is the same for every operand,
+            // the low word is the address in 16-byte units plus the leading offset (1 for K-major, 8192 bytes for a
+            // row-major B).  Building them per MMA cost the issuing thread about 75 cycles per instruction.
+            const uint32_t desc_hi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+            const uint32_t a_lo0 = ((ring & 0x3ffffu) >> 4) | (1u << 16);
+            const uint32_t b_lo0 = (((ring + Cfg::kBytesA) & 0x3ffffu) >> 4) | (p.b_row_major ? (uint32_t)(8192 >> 4) << 16 : 1u << 16);
+            const uint32_t b_kstep = p.b_row_major ? 2048u >> 4 : (uint32_t)(kUmmaK * 2) >> 4;
             bool ok = true;
             for (long long u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++local_tile) {
                 long long t;
@@ -561,25 +584,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % Cfg::kStages;
-                    const uint32_t phase = (it / Cfg::kStages) & 1u;
-                    if (!mbar_wait(full_bar(s), phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = ring + s * Cfg::kStageBytes, b_addr = a_addr + Cfg::kBytesA;
+                    // descriptors of this stage: the ring's plus the stage's offset in 16-byte units
+                    const uint32_t a_lo = a_lo0 + stage * (uint32_t)(Cfg::kStageBytes >> 4), b_lo = b_lo0 + stage * (uint32_t)(Cfg::kStageBytes >> 4);
+                    uint32_t accumulate = kb != kb0 ? 1u : 0u;
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
-                        // advancing K inside the swizzled row: +32 bytes per 16 elements
-                        const uint64_t da = smem_desc_k_major_sw128(a_addr + k * kUmmaK * 2);
-                        // row-major B: 16 K-rows further = two 8-row atoms = 2048 bytes
-                        const uint64_t db = p.b_row_major ? smem_desc_mn_major_sw128(b_addr + k * 2048)
-                                                          : smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
-                        umma_f16(d_tmem, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
-                        if (MT == 2) {  // rows 128..255 of the tile: 16 KB further in the stage, accumulator columns BN..2BN-1
-                            const uint64_t da1 = smem_desc_k_major_sw128(a_addr + kBM * kBK * 2 + k * kUmmaK * 2);
-                            umma_f16(d_tmem + BN, da1, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
-                        }
+                        // advancing K inside the swizzled row: +32 bytes per 16 elements (K-major); row-major B: 16 K-rows
+                        // further = two 8-row atoms = 2048 bytes
+                        umma_f16_words(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * b_kstep, desc_hi, idesc, accumulate);
+                        if (MT == 2)  // rows 128..255 of the tile: 16 KB further in the stage, accumulator columns BN..2BN-1
+                            umma_f16_words(d_tmem + BN, a_lo + (kBM * kBK * 2 >> 4) + k * 2, desc_hi, b_lo + k * b_kstep, desc_hi, idesc, accumulate);
+                        accumulate = 1u;
                     }
-                    umma_commit(empty_bar(s));  // the stage is reusable once these MMAs have read it
+                    umma_commit(empty_bar(stage));  // the stage is reusable once these MMAs have read it
+                    if (++stage == (uint32_t)Cfg::kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) umma_commit(acc_ready_bar(acc));
             }

@@ -63,13 +63,17 @@ __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t c
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
-// D[tmem of both SMs] (+)= A[both CTAs' smem] * B[both CTAs' smem]; issued by one thread of the leader CTA
-__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+// D[tmem of both SMs] (+)= A[both CTAs' smem] * B[both CTAs' smem]; issued by one thread of the leader CTA; the
+// descriptors as (low, high) words (see umma_f16_words)
+__device__ __forceinline__ void umma_f16_pair_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                    uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // arrives on the mbarrier at shared::cluster address `bar` once every tcgen05.mma issued so far by this thread has
@@ -205,6 +209,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         // ------------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && leader) {
             uint32_t it = 0, local_tile = 0;
+            uint32_t stage = 0, phase = 0;  // ring position of K-block `it` and the parity of its fill
+            // descriptor words of the ring's first stage, stepped by 32-bit adds (see the single-CTA kernel)
+            const uint32_t desc_hi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+            const uint32_t a_lo0 = ((ring & 0x3ffffu) >> 4) | (1u << 16);
+            const uint32_t b_lo0 = (((ring + Cfg::kBytesA) & 0x3ffffu) >> 4) | (p.b_row_major ? (uint32_t)(8192 >> 4) << 16 : 1u << 16);
+            const uint32_t b_kstep = p.b_row_major ? 2048u >> 4 : (uint32_t)(kUmmaK * 2) >> 4;
             bool ok = true;
             const uint32_t own_empty0 = map_to_cluster_rank(empty_bar(0), 0);
             const uint32_t peer_ready0 = map_to_cluster_rank(acc_ready_bar(0), 1), own_ready0 = map_to_cluster_rank(acc_ready_bar(0), 0);
@@ -218,21 +228,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % Cfg::kStages;
-                    const uint32_t phase = (it / Cfg::kStages) & 1u;
-                    if (!mbar_wait(full_bar(s), phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = ring + s * Cfg::kStageBytes, b_addr = a_addr + Cfg::kBytesA;
+                    const uint32_t a_lo = a_lo0 + stage * (uint32_t)(Cfg::kStageBytes >> 4), b_lo = b_lo0 + stage * (uint32_t)(Cfg::kStageBytes >> 4);
+                    uint32_t accumulate = kb != 0 ? 1u : 0u;
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
-                        const uint64_t da = smem_desc_k_major_sw128(a_addr + k * kUmmaK * 2);
-                        const uint64_t db = p.b_row_major ? smem_desc_mn_major_sw128(b_addr + k * 2048)
-                                                          : smem_desc_k_major_sw128(b_addr + k * kUmmaK * 2);
-                        umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_f16_pair_words(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * b_kstep, desc_hi, idesc, accumulate);
+                        accumulate = 1u;
                     }
                     // the stage is reusable once these MMAs have read it (in both CTAs: the commit tracks both SMs); the
                     // leader's producer passes the release on to the peer
-                    umma_commit_pair(own_empty0 + 8u * s);
+                    umma_commit_pair(own_empty0 + 8u * stage);
+                    if (++stage == (uint32_t)Cfg::kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) {
                     umma_commit_pair(own_ready0 + 8u * acc);
