@@ -229,7 +229,13 @@ int gemm_tc_dispatch(ko_context_t *handle, int fmt, int out_fmt, int b_row_major
     // Longer K goes to the single-CTA 256 x 256 tile with uneven columns (4096^3: 97.6 against 101.9 us), K <= 512 and
     // small problems to the 128-row tile (8192 x 8192 x 512: 79.5 / 82.4; 32768 x 1024 x 256: 31.8 / 37.6).
     // (row-major B, same rule: 16384 x 3072 x 768 71.0 against 76.9 us, with BF16 output 62.4 / 65.1)
-    const bool pair = bn == 2048 || bn == 2304 || (bn == 0 && K > 512 && K <= 3072 && M >= 4096 && N >= 512);
+    // Long K with many tiles too (at least three per SM as 256 x 256 tiles, so that the pairs' coarser rounds cost little):
+    // the pair's double-buffered accumulator hides the epilogue that the single-CTA 256 x 256 tile exposes -- 8192^3 762
+    // against 795 us, 8192 x 8192 x 4096 383 / 411, 16384 x 8192 x 8192 1573 / 1655, 6144^3 346 / 362 (medians of interleaved
+    // runs); 4096^3 (256 tiles) stays with the single-CTA tile and its uneven columns.
+    const long long tiles256 = ((M + 255) / 256) * ((N + 255) / 256);
+    const bool pair = bn == 2048 || bn == 2304 ||
+                      (bn == 0 && K > 512 && M >= 4096 && N >= 512 && (K <= 3072 || tiles256 >= 3LL * info.sm_count));
     KO_REQUIRE(bn != 2304 || !b_row_major, KO_ERR_SHAPE, "gemm: uneven column tiles need column-major B");
     if (bn == 1024) bn = 256;  // 128 x 256 tiles, uneven column tiles forced
     if (bn == 1280) bn = 512;  // 256 x 256 tiles, uneven column tiles forced
