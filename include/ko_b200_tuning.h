@@ -30,7 +30,8 @@ typedef struct ko_row_knobs {
                             one row per group of 8, 16 or 32 lanes, i.e. 4, 2 or 1 rows); LayerNorm reread tier:
                             1 = one row per block at a time, 2 = two (gamma / beta loaded once for both),
                             0 = two from 512 KB per row */
-    int block;           /* warp tier: threads per block (<= 256); block / resident tier: threads per row (128..1024) */
+    int block;           /* warp tier: threads per block (<= 256); block / resident tier: threads per row (128..1024, a power
+                            of two; the resident tier also takes 768 and 896: four vectors per thread through the shared-memory ring) */
     int64_t grid_cap;    /* warp / block / stream tier: upper bound on the grid (0 = one pass per warp) */
     int stage_rows;      /* staged tier: rows per bulk copy (0 = about 16-32 KB) */
     int stages;          /* staged tier: ring depth (0 = fill about 100 KB); LayerNorm resident tier: 1 = the block's next

@@ -108,6 +108,24 @@ def test_f32_resident_tier(cuda, lib, oracle, block):
             assert oracle.max_rel_err(y, oracle.layernorm_f64(x, 1e-12, gg, bb)) <= TOL_REL
 
 
+def test_resident_tier_with_768_and_896_threads(cuda, lib, oracle):
+    """Rows of 2049..3072 vectors take 768 threads with four vectors each, rows of 3073..3584 vectors 896 (the default
+    there, and block = 768 / 896 on request): exactly filled, partly filled, more rows than blocks, with and without
+    the affine parameters, in place."""
+    for block, rows, cols in ((768, 5, 12288), (768, 33, 9216), (768, 7, 8196), (768, 300, 10240), (768, 2, 12284),
+                              (896, 5, 14336), (896, 40, 12292), (896, 300, 13312)):
+        x, g, b = _inputs(oracle, rows, cols)
+        for gg, bb in ((g, b), (None, None)):
+            want = oracle.layernorm_f64(x, 1e-12, gg, bb)
+            y = _run_f32(cuda, lib, x, 1e-12, gg, bb, 0, tier=5, block=block, grid_cap=3 if rows > 100 else 0)
+            assert oracle.max_rel_err(y, want) <= TOL_REL
+            assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, gg, bb))          # the default for such rows
+            assert np.array_equal(y, _run_f32(cuda, lib, x, 1e-12, gg, bb, 0, inplace=True, tier=5, block=block))
+    # shorter rows fit too (threads without data), longer ones are refused
+    x, g, b = _inputs(oracle, 9, 4096)
+    assert oracle.max_rel_err(_run_f32(cuda, lib, x, 1e-12, g, b, 0, tier=5, block=768), oracle.layernorm_f64(x, 1e-12, g, b)) <= TOL_REL
+
+
 @pytest.mark.parametrize("lanes", [0, 4, 8, 16, 32])
 @pytest.mark.parametrize("slots", [0, 1, 2, 4])
 def test_lane_group_tier_for_short_rows(cuda, lib, oracle, lanes, slots):
