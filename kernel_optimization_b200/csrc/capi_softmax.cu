@@ -40,6 +40,12 @@ int launch_block(const float *in, float *out, long long rows, int cols, long lon
     return ko::launch_overlapped(ko::softmax_block_kernel<kVecs, kThreads>, ko::clamp_grid(rows, grid_cap), kThreads, 0, s, in, out,
                                  rows, cols);
 }
+// the same kernel (compiled for up to kBound threads; it reads its block size at run time) with `threads` per block
+template <int kVecs, int kBound>
+int launch_block_threads(int threads, const float *in, float *out, long long rows, int cols, long long grid_cap, cudaStream_t s) {
+    return ko::launch_overlapped(ko::softmax_block_kernel<kVecs, kBound>, ko::clamp_grid(rows, grid_cap), (unsigned)threads, 0, s, in, out,
+                                 rows, cols);
+}
 
 // one row per block in registers, the next row prefetched into shared memory by a bulk copy; one block per SM
 template <int kVecs, int kThreads>
@@ -158,7 +164,7 @@ int dispatch_rows(int nvec, int slots, const float *in, float *out, long long ro
 #undef KO_GO
 }
 
-// FP16 / BF16 rows: warp tier up to 2048 columns, block tier up to 16384, two passes per row beyond; scalar
+// FP16 / BF16 rows: warp tier up to 1536 columns, block tier up to 24576, two passes per row beyond; scalar
 // stream tier for rows that cannot be moved in 16-byte vectors
 template <typename T>
 int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStream_t s) {
@@ -190,23 +196,21 @@ int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStre
     if (vec_ok && nvec <= 128 * 2)
         return ko::launch_overlapped(ko::softmax16_block_kernel<T, 2, 128>, ko::clamp_grid(rows, 0), 128u, 0, s, in, out, (long long)rows,
                                      (int)cols);
-    if (vec_ok && nvec <= 512 * 4) {
-        auto block = [&](auto kernel, int threads) -> int {
-            return ko::launch_overlapped(kernel, ko::clamp_grid(rows, 0), (unsigned)threads, 0, s, in, out, (long long)rows, (int)cols);
-        };
-        // the smallest threads x vectors per thread that holds the row (padded vectors cost as much as real ones)
-        if (nvec <= 128 * 3) return block(ko::softmax16_block_kernel<T, 3, 128>, 128);
-        if (nvec <= 128 * 4) return block(ko::softmax16_block_kernel<T, 4, 128>, 128);
-        if (nvec <= 128 * 5) return block(ko::softmax16_block_kernel<T, 5, 128>, 128);
-        if (nvec <= 128 * 6) return block(ko::softmax16_block_kernel<T, 6, 128>, 128);
-        if (nvec <= 256 * 4) return block(ko::softmax16_block_kernel<T, 4, 256>, 256);
-        if (nvec <= 256 * 5) return block(ko::softmax16_block_kernel<T, 5, 256>, 256);
-        if (nvec <= 256 * 6) return block(ko::softmax16_block_kernel<T, 6, 256>, 256);
-        return block(ko::softmax16_block_kernel<T, 4, 512>, 512);
+    if (vec_ok && nvec <= 512 * 6) {
+        // Block tier up to 24576 columns: six vectors per thread (three up to 3072 columns) and exactly the threads the
+        // row needs, a multiple of 32 -- padded vectors cost as much as real ones, and six vectors in few threads beat
+        // four in many.  BF16, TB/s, against the former power-of-two blocks of 4..6 vectors: 2304 columns 5.5 -> 6.6,
+        // 7168 5.6 -> 6.4, 9216 5.3 -> 6.5, 11264 5.6 -> 6.4, 13312 4.5 -> 5.8, 15360 4.9 -> 6.1; and instead of the
+        // two-pass tier: 18432 4.5 -> 5.5, 24576 5.0 -> 5.9.
+        const int per = nvec <= 384 ? 3 : 6;
+        const unsigned threads = (unsigned)(((nvec + per - 1) / per + 31) / 32 * 32);
+        if (per == 3)
+            return ko::launch_overlapped(ko::softmax16_block_kernel<T, 3, 512>, ko::clamp_grid(rows, 0), threads, 0, s, in, out, (long long)rows, (int)cols);
+        return ko::launch_overlapped(ko::softmax16_block_kernel<T, 6, 512>, ko::clamp_grid(rows, 0), threads, 0, s, in, out, (long long)rows, (int)cols);
     }
     if (vec_ok) {
-        // beyond 16384 columns: two passes per row, the second from the L2, in 256-thread blocks so that several rows
-        // per SM are in flight (BF16 [3276,20480] 3.0 -> 4.8 TB/s, [2048,32768] 3.8 -> 4.8 against a 1024-thread block
+        // beyond 24576 columns: two passes per row, the second from the L2, in 256-thread blocks so that several rows
+        // per SM are in flight ([2048,32768] 3.8 -> 4.8 TB/s against a 1024-thread block
         // holding the row; [1024,65536] 4.2 -> 4.5 against one 1024-thread reread block per SM)
         // while at least four rows per SM fit in the L2 besides the output stream; longer rows: one 1024-thread block per
         // SM (BF16 [2048,131072]: 4.6 TB/s; 3.3 with two 256-thread blocks per SM, 4.2 with eight that overflow the L2)
@@ -249,7 +253,7 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
     KO_REQUIRE((k.tier >= 0 && k.tier <= 4) || (k.tier >= 6 && k.tier <= 8), KO_ERR_INVALID_ARG, "softmax: unknown tier %d", k.tier);
     KO_REQUIRE(k.cluster == 0 || k.cluster == 2 || k.cluster == 4 || k.cluster == 8, KO_ERR_INVALID_ARG,
                "softmax: cluster size %d not in {2,4,8}", k.cluster);
-    KO_REQUIRE(k.block >= 0 && k.block % 32 == 0 && k.block <= 1024, KO_ERR_INVALID_ARG,
+    KO_REQUIRE(k.block >= 0 && (k.block % 32 == 0 || k.block == 1) && k.block <= 1024, KO_ERR_INVALID_ARG,
                "softmax: block %d must be a multiple of 32, <= 1024", k.block);
     DeviceInfo info;
     if (int st = ko::current_device_info(&info)) return st;
@@ -319,8 +323,12 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
         KO_REQUIRE(vec_ok && nvec <= 1024 * 8, KO_ERR_SHAPE, "softmax: the block tier needs cols %% 4 == 0, cols <= 32768 and 16-byte aligned pointers");
         // three vectors per thread for 2049..3072 columns ([13107,2560] 5.7 -> 6.2 TB/s); five or six vectors in 256 or
         // 512 threads measured slower than four in twice the threads ([6553,5120] 5.4 against 5.6, [3276,10240] 4.7 / 5.4)
+        // Beyond 4096 columns the block has as many threads as the row needs with four vectors each, a multiple of 32:
+        // padded vectors cost as much as real ones ([8184,4100] 5.0 -> 6.0 TB/s, [6553,5120] 5.7 -> 6.6, [3640,9216]
+        // 5.2 -> 5.7, [3276,10240] 5.5 -> 6.0; k.block = 1: powers of two only, for comparison)
         if (nvec <= 256 * 3) return launch_block<3, 256>(in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 256 * 4) return launch_block<4, 256>(in, out, rows, cols, k.grid_cap, s);
+        if (k.block != 1 && nvec <= 1024 * 4) return launch_block_threads<4, 1024>(((nvec + 3) / 4 + 31) / 32 * 32, in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 512 * 4) return launch_block<4, 512>(in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 1024 * 4) return launch_block<4, 1024>(in, out, rows, cols, k.grid_cap, s);
         return launch_block<8, 1024>(in, out, rows, cols, k.grid_cap, s);

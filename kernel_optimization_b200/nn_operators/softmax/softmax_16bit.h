@@ -12,8 +12,9 @@
 //
 //   warp tier   a row over a group of 8, 16 or 32 lanes, up to 8 vectors (64 elements) per lane,
 //               two rows per lane group in flight; columns a multiple of 8, up to 2048
-//   block tier  one row per block of 256 or 512 threads, up to 8 vectors per thread (16384 columns)
-//   reread tier one row per block in two passes, the second from the L2: rows beyond 16384 columns
+//   block tier  one row per block of exactly the threads it needs (a multiple of 32, at most 512) with three or six
+//               vectors per thread: up to 24576 columns
+//   reread tier one row per block in two passes, the second from the L2: rows beyond 24576 columns
 //   stream tier any column count and alignment, scalar accesses, three passes
 #pragma once
 
@@ -134,7 +135,8 @@ __global__ void __launch_bounds__(256) softmax16_warp_kernel(const T *in, T *out
 }
 
 // ---------------------------------------------------------------------------------------------
-// block tier: one row per block, the row in registers
+// block tier: one row per block, the row in registers (kThreads: the most threads a block may have; the block size is read
+// at run time, so that a launch can bring exactly the threads the row needs)
 // ---------------------------------------------------------------------------------------------
 template <typename T, int kVecs, int kThreads>
 __global__ void __launch_bounds__(kThreads) softmax16_block_kernel(const T *in, T *out, long long rows, int cols) {
@@ -150,7 +152,7 @@ __global__ void __launch_bounds__(kThreads) softmax16_block_kernel(const T *in, 
         float m = kNegInf;
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
-            const int v = threadIdx.x + kThreads * j;
+            const int v = threadIdx.x + blockDim.x * j;
             if (v < nvec) {
                 Io::unpack(ld_stream(in_v + row * nvec + v), x[j]);
             } else {
@@ -168,7 +170,7 @@ __global__ void __launch_bounds__(kThreads) softmax16_block_kernel(const T *in, 
         const float inv = rcp_approx(s);
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
-            const int v = threadIdx.x + kThreads * j;
+            const int v = threadIdx.x + blockDim.x * j;
             if (v < nvec) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[j][e] *= inv;

@@ -41,7 +41,10 @@ def _softmax(cuda, lib, kind, xb, inplace=False):
 # row, more rows than blocks), odd counts (stream tier)
 SOFTMAX_SHAPES = [(1, 8), (5, 64), (7, 128), (9, 136), (33, 256), (100, 512), (64, 1024), (17, 2048), (9, 2056), (5, 4096),
                   (3, 8192), (5, 10248), (4, 12288), (3, 16384), (4, 16392), (2, 32768), (2, 40000), (3, 262152), (200, 65536),
-                  (3000, 20480), (3, 1), (5, 7), (4, 100), (3, 1001)]
+                  (3000, 20480), (3, 1), (5, 7), (4, 100), (3, 1001),
+                  # block tier with exactly the threads a row needs: three vectors per thread up to 3072 columns, six beyond,
+                  # up to 24576 columns; rows that fill the threads and rows one vector longer
+                  (5, 3072), (5, 3080), (6, 7168), (4, 11264), (3, 13320), (3, 24576), (3, 24584)]
 
 
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
