@@ -323,12 +323,16 @@ int ko_softmax_f32_tuned(const float *in, float *out, int64_t rows, int32_t cols
         KO_REQUIRE(vec_ok && nvec <= 1024 * 8, KO_ERR_SHAPE, "softmax: the block tier needs cols %% 4 == 0, cols <= 32768 and 16-byte aligned pointers");
         // three vectors per thread for 2049..3072 columns ([13107,2560] 5.7 -> 6.2 TB/s); five or six vectors in 256 or
         // 512 threads measured slower than four in twice the threads ([6553,5120] 5.4 against 5.6, [3276,10240] 4.7 / 5.4)
-        // Beyond 4096 columns the block has as many threads as the row needs with four vectors each, a multiple of 32:
+        // The block has as many threads as the row needs with four vectors each, a multiple of 32:
         // padded vectors cost as much as real ones ([8184,4100] 5.0 -> 6.0 TB/s, [6553,5120] 5.7 -> 6.6, [3640,9216]
         // 5.2 -> 5.7, [3276,10240] 5.5 -> 6.0; k.block = 1: powers of two only, for comparison)
+        // (up to 4096 columns the 256-thread blocks of three or four vectors stay where they are filled to 88 % or more:
+        // [10922,3072] 6.63 against 6.51 TB/s, [8192,4096] 6.61 / 6.51; [16352,2052] 5.7 -> 6.5 with 160 threads)
+        const int pow2_slots = nvec <= 256 * 3 ? 256 * 3 : 256 * 4;
+        const bool exact = k.block != 1 && (nvec > 256 * 4 || nvec * 100 < pow2_slots * 88);
+        if (exact && nvec <= 1024 * 4) return launch_block_threads<4, 1024>(((nvec + 3) / 4 + 31) / 32 * 32, in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 256 * 3) return launch_block<3, 256>(in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 256 * 4) return launch_block<4, 256>(in, out, rows, cols, k.grid_cap, s);
-        if (k.block != 1 && nvec <= 1024 * 4) return launch_block_threads<4, 1024>(((nvec + 3) / 4 + 31) / 32 * 32, in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 512 * 4) return launch_block<4, 512>(in, out, rows, cols, k.grid_cap, s);
         if (nvec <= 1024 * 4) return launch_block<4, 1024>(in, out, rows, cols, k.grid_cap, s);
         return launch_block<8, 1024>(in, out, rows, cols, k.grid_cap, s);

@@ -32,7 +32,7 @@ def _run(cuda, lib, x, inplace=False, **knobs):
 SHAPES = [(1, 1), (3, 1), (5, 4), (7, 100), (5, 131), (1000, 128), (37, 512), (33, 640), (64, 2048), (9, 2052),
           (11, 4096), (6, 12288), (2, 32768), (2, 32772), (3, 40000), (2, 131072),
           # block tier with exactly the threads a row needs (a multiple of 32, four vectors each)
-          (5, 4100), (7, 8196), (3, 9216), (4, 10240), (2, 16380)]
+          (5, 4100), (7, 8196), (3, 9216), (4, 10240), (2, 16380), (9, 2304), (6, 3328), (5, 2816)]
 
 
 @pytest.mark.parametrize("rows,cols", SHAPES)
