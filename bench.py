@@ -790,11 +790,12 @@ SWEEP_ROW_SHAPES = {
     # (rows, cols): the benchmark configs, the shape the reference's drivers were written for (49152 x 1024,
     # nn_operators/softmax/main.cu:78-79) and long rows for the block, reread and cluster tiers (512 rows are 3.46
     # rounds of one row per SM; 1024 and 2048 rows fill their rounds; 64 rows go to the cluster tier)
-    "softmax": {"f32": [(196608, 128), (49152, 1024), (196608, 512), (8192, 8192), (512, 65536), (1024, 65536), (2048, 131072),
-                        (64, 131072)],
-                "f16": [(196608, 128), (49152, 1024)], "bf16": [(196608, 512), (49152, 1024), (2048, 131072)]},
-    "layernorm": {"f32": [(16384, 768), (49152, 1024), (8192, 4096), (4096, 20480), (512, 65536), (1024, 65536), (2048, 131072),
-                          (64, 131072)],
+    # (9216 / 10240 / 24576 columns: between the powers of two, where a block brings exactly the threads the row needs)
+    "softmax": {"f32": [(196608, 128), (49152, 1024), (196608, 512), (8192, 8192), (3640, 9216), (512, 65536), (1024, 65536),
+                        (2048, 131072), (64, 131072)],
+                "f16": [(196608, 128), (49152, 1024)], "bf16": [(196608, 512), (49152, 1024), (7281, 9216), (2730, 24576), (2048, 131072)]},
+    "layernorm": {"f32": [(16384, 768), (49152, 1024), (8192, 4096), (3125, 10240), (4096, 20480), (512, 65536), (1024, 65536),
+                          (2048, 131072), (64, 131072)],
                   "f16": [(16384, 768), (32768, 4096)], "bf16": [(16384, 768), (32768, 4096), (32768, 5120), (2048, 131072)]},
 }
 SWEEP_SGEMM = [512, 1024, 2048, 4096]
