@@ -183,9 +183,9 @@ int softmax16_dispatch(const T *in, T *out, int64_t rows, int32_t cols, cudaStre
         // the smallest lane group x vectors per lane that holds the row: padded vectors cost as much as real ones
         // (BF16 768 columns: 4 vectors per lane 4.8 TB/s, 3 vectors per lane 5.5; 1280 columns: 8 vectors 4.5, 5 vectors 6.4)
         if (nvec <= 8) return warp(ko::softmax16_warp_kernel<T, 1, 2, 8>, 8);
-        if (nvec <= 16) return warp(ko::softmax16_warp_kernel<T, 2, 2, 8>, 8);
+        if (nvec <= 16) return warp(ko::softmax16_warp_kernel<T, 2, 1, 8>, 4);   // one row slot per lane group: FP16 [196608,128] 5.3 -> 5.6 TB/s
         if (nvec <= 24) return warp(ko::softmax16_warp_kernel<T, 3, 1, 8>, 4);
-        if (nvec <= 32) return warp(ko::softmax16_warp_kernel<T, 2, 2, 16>, 4);
+        if (nvec <= 32) return warp(ko::softmax16_warp_kernel<T, 2, 1, 16>, 2);  // [196608,256] 5.7 -> 6.0
         if (nvec <= 48) return warp(ko::softmax16_warp_kernel<T, 3, 1, 16>, 2);
         if (nvec <= 64) return warp(ko::softmax16_warp_kernel<T, 2, 1, 32>, 1);
         if (nvec <= 96) return warp(ko::softmax16_warp_kernel<T, 3, 1, 32>, 1);
