@@ -686,6 +686,7 @@ CASES = {
     "layernorm_cluster_rows": "LayerNorm FP32 [256,131072] affine, cluster tier forced: one row per cluster of 4 blocks, Welford triples exchanged through DSMEM mailboxes",
     "softmax_reread_rows": "softmax FP32 [1024,65536]: one row per block in two passes, the second served by the L2 (the default for such rows)",
     "layernorm_reread_rows": "LayerNorm FP32 [1024,131072] affine: two rows per block at a time, two passes, gamma / beta loaded once per pair (the default for such rows)",
+    "softmax_block_rows": "softmax FP32 [3640,9216]: one row per block in registers, 576 threads of four vectors (exactly what the row needs)",
     "layernorm_c2": "LayerNorm FP32 [16384,768] affine (benchmark config 2), 8 rotating buffer sets",
     "softmax_c1": "softmax FP32 [196608,128] (benchmark config 1), 4 rotating buffer sets",
     "gemm_bf16_ffn_pair": "BF16 GEMM 16384x3072x768 on the two-SM kernel (tcgen05 cta_group::2)",
@@ -723,8 +724,9 @@ def run_case(args):
         else:
             launch = lambda: native.check(lib.ko_gemm_bf16_f32(M, N, K, a.data_ptr(), b.data_ptr(), None, d.data_ptr(), s()), name)  # noqa: E731
         work, unit = 2.0 * M * N * K, "TFLOP/s"
-    elif name in ("softmax_cluster_rows", "layernorm_cluster_rows", "softmax_reread_rows", "layernorm_reread_rows", "layernorm_c2", "softmax_c1"):
-        rows, cols, nsets = {"softmax_cluster_rows": (256, 131072, 3), "layernorm_cluster_rows": (256, 131072, 3),
+    elif name in ("softmax_cluster_rows", "layernorm_cluster_rows", "softmax_reread_rows", "layernorm_reread_rows", "layernorm_c2", "softmax_c1",
+                  "softmax_block_rows"):
+        rows, cols, nsets = {"softmax_cluster_rows": (256, 131072, 3), "layernorm_cluster_rows": (256, 131072, 3), "softmax_block_rows": (3640, 9216, 3),
                              "softmax_reread_rows": (1024, 65536, 2), "layernorm_reread_rows": (1024, 131072, 2),
                              "layernorm_c2": (LN_ROWS, LN_COLS, 8), "softmax_c1": (SOFTMAX_ROWS, SOFTMAX_COLS, 4)}[name]
         knobs = native.RowKnobs(tier=6) if "cluster" in name else None
